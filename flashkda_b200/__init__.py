@@ -1,0 +1,13 @@
+"""B200-native Kimi Delta Attention prefill, behind the reference's `flash_kda.fwd` signature.
+
+Python host side of the drop-in boundary: mirrors flash_kda/__init__.py:5-41 and the argument
+checks of csrc/flash_kda.cpp:44-174 of the reference, then calls the C-ABI library
+(include/fkda.h) through ctypes with raw device pointers and torch's current CUDA stream.
+There is no CPU or PyTorch fallback: without the compiled library, or without a CUDA device,
+`fwd` raises.
+"""
+from ._binding import (FLAG_SCAN_SIMT, fwd, get_workspace_size, last_error, lib, lib_path,
+                       prepare, prologue, read_status, scan, selftest_umma, workspace_layout)
+
+__all__ = ["fwd", "get_workspace_size", "prepare", "scan", "prologue", "read_status",
+           "workspace_layout", "selftest_umma", "lib", "lib_path", "last_error", "FLAG_SCAN_SIMT"]

@@ -1,0 +1,237 @@
+// C ABI of the library (include/fkda.h): argument validation, workspace carving and launches.
+// Host-side counterpart of the reference's csrc/flash_kda.cpp (validation, dispatch) and
+// csrc/smxx/fwd_launch.cu (workspace carving, launches), without torch types.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/fkda.h"
+#include "fkda_common.cuh"
+
+namespace fkda {
+cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int* prefix, int* status, cudaStream_t stream);
+cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
+cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
+cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
+cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* g, const __nv_bfloat16* beta,
+                            const float* A_log, const float* dt_bias, float gate_scale, int64_t rows, int H, __nv_bfloat16* qn,
+                            __nv_bfloat16* kn, float* gact, float* beta_act, cudaStream_t stream);
+cudaError_t launch_umma_selftest(const __nv_bfloat16* A, const __nv_bfloat16* B, float* D, int mode, int reps, int* status,
+                                 cudaStream_t stream);
+}  // namespace fkda
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(FKDA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+struct Layout {
+  int64_t prefix_off;      // int32 [N+1]
+  int64_t records_off;
+  int64_t chunks_per_head; // records per head
+  int64_t total_bytes;
+};
+
+// `varlen` < 0: size for whichever mode needs more (the upper bound T_total/32 + N covers both).
+bool make_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq, Layout* L) {
+  if (T_total < 0 || H <= 0 || N <= 0) return false;
+  int64_t chunks;
+  if (varlen == 0) chunks = N * ((T_per_seq + fkda::kChunk - 1) / fkda::kChunk);
+  else chunks = T_total / fkda::kChunk + N;
+  if (varlen < 0) {
+    int64_t fixed_ub = (T_total + fkda::kChunk - 1) / fkda::kChunk + N;
+    chunks = fixed_ub > chunks ? fixed_ub : chunks;
+  }
+  L->prefix_off = fkda::kWsHeaderBytes;
+  int64_t prefix_bytes = ((N + 1) * 4 + 255) / 256 * 256;
+  L->records_off = L->prefix_off + prefix_bytes;
+  L->chunks_per_head = chunks;
+  L->total_bytes = L->records_off + chunks * H * static_cast<int64_t>(fkda::kRecBytes);
+  return true;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate(const fkda_fwd_params* p, Layout* L) {
+  if (!p) return fail(FKDA_ERR_INVALID_ARGUMENT, "params is NULL");
+  if (!p->q || !p->k || !p->v || !p->g || !p->beta || !p->out) return fail(FKDA_ERR_INVALID_ARGUMENT, "q, k, v, g, beta and out must be non-NULL");
+  if (!p->A_log || !p->dt_bias) return fail(FKDA_ERR_INVALID_ARGUMENT, "A_log and dt_bias must be non-NULL");
+  if (p->B <= 0 || p->H <= 0 || p->T < 0) return fail(FKDA_ERR_INVALID_ARGUMENT, "B and H must be positive and T non-negative");
+  if (p->cu_seqlens) {
+    if (p->B != 1) return fail(FKDA_ERR_INVALID_ARGUMENT, "B must be 1 when cu_seqlens is provided");
+    if (p->N <= 0) return fail(FKDA_ERR_INVALID_ARGUMENT, "cu_seqlens must have at least 2 elements");
+  } else if (p->N != p->B) {
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "N must equal B when cu_seqlens is not provided");
+  }
+  if ((p->initial_state || p->final_state) && p->state_dtype != FKDA_STATE_BF16 && p->state_dtype != FKDA_STATE_FP32)
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "state_dtype must be bf16 or fp32 when a state tensor is given");
+  if (!std::isfinite(p->scale) || !std::isfinite(p->lower_bound)) return fail(FKDA_ERR_INVALID_ARGUMENT, "scale and lower_bound must be finite");
+  if (p->lower_bound > 0.f || p->lower_bound < -5.45f)
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "lower_bound must lie in [-5.45, 0]: a 16-token sub-block decays by at most 2^126");
+  const void* ptrs[] = {p->q, p->k, p->v, p->g, p->out, p->dt_bias, p->initial_state, p->final_state};
+  for (const void* x : ptrs)
+    if (x && !aligned16(x)) return fail(FKDA_ERR_INVALID_ARGUMENT, "tensor base addresses must be 16-byte aligned");
+  const int64_t T_total = p->B * p->T;
+  if (p->H > 65535) return fail(FKDA_ERR_INVALID_ARGUMENT, "H must be at most 65535");
+  if (p->N * p->H > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "N*H exceeds 2^31-1 chains");
+  if (!make_layout(T_total, p->H, p->N, p->cu_seqlens ? 1 : 0, p->T, L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
+  if (L->chunks_per_head > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "too many chunks for one call");
+  if (!p->workspace) return fail(FKDA_ERR_INVALID_ARGUMENT, "workspace is NULL");
+  if (reinterpret_cast<uintptr_t>(p->workspace) & 255u) return fail(FKDA_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+  if (p->workspace_bytes < L->total_bytes)
+    return fail(FKDA_ERR_WORKSPACE_TOO_SMALL, "workspace has %lld bytes, %lld needed", (long long)p->workspace_bytes, (long long)L->total_bytes);
+  return FKDA_OK;
+}
+
+int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
+  uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+  int* status = reinterpret_cast<int*>(ws);
+  int* prefix = reinterpret_cast<int*>(ws + L.prefix_off);
+  cudaError_t e = cudaMemsetAsync(ws, 0, fkda::kWsHeaderBytes, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
+  if (p->cu_seqlens) {
+    e = fkda::launch_chunk_prefix(p->cu_seqlens, static_cast<int>(p->N), p->B * p->T, prefix, status, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "chunk_prefix launch");
+  }
+  fkda::PrepParams q{};
+  q.q = static_cast<const __nv_bfloat16*>(p->q);
+  q.k = static_cast<const __nv_bfloat16*>(p->k);
+  q.v = static_cast<const __nv_bfloat16*>(p->v);
+  q.g = static_cast<const __nv_bfloat16*>(p->g);
+  q.beta = static_cast<const __nv_bfloat16*>(p->beta);
+  q.A_log = p->A_log;
+  q.dt_bias = p->dt_bias;
+  q.cu_seqlens = p->cu_seqlens;
+  q.chunk_prefix = prefix;
+  q.records = ws + L.records_off;
+  q.status = status;
+  q.T = p->T;
+  q.T_total = p->B * p->T;
+  q.H = static_cast<int>(p->H);
+  q.N = static_cast<int>(p->N);
+  q.total_chunks = static_cast<int>(L.chunks_per_head);
+  q.scale = p->scale;
+  q.gate_scale = static_cast<float>(static_cast<double>(p->lower_bound) * 1.4426950408889634);
+  e = fkda::launch_prepare(q, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "prepare launch");
+  return FKDA_OK;
+}
+
+int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
+  uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+  fkda::ScanParams s{};
+  s.records = ws + L.records_off;
+  s.cu_seqlens = p->cu_seqlens;
+  s.chunk_prefix = reinterpret_cast<const int*>(ws + L.prefix_off);
+  s.initial_state = p->initial_state;
+  s.final_state = p->final_state;
+  s.out = static_cast<__nv_bfloat16*>(p->out);
+  s.status = reinterpret_cast<int*>(ws);
+  s.T = p->T;
+  s.T_total = p->B * p->T;
+  s.H = static_cast<int>(p->H);
+  s.N = static_cast<int>(p->N);
+  s.total_chunks = static_cast<int>(L.chunks_per_head);
+  s.state_fp32 = p->state_dtype == FKDA_STATE_FP32 ? 1 : 0;
+  cudaError_t e = (p->flags & FKDA_FLAG_SCAN_SIMT) ? fkda::launch_scan_simt(s, stream) : fkda::launch_scan(s, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "scan launch");
+  return FKDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* bytes) {
+  Layout L;
+  if (!bytes) return fail(FKDA_ERR_INVALID_ARGUMENT, "bytes is NULL");
+  if (!make_layout(T_total, H, N, -1, 0, &L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "T_total >= 0, H > 0 and N > 0 required");
+  *bytes = L.total_bytes;
+  return FKDA_OK;
+}
+
+int fkda_workspace_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq, int64_t* records_offset,
+                          int64_t* record_bytes, int64_t* chunks_per_head) {
+  Layout L;
+  if (!make_layout(T_total, H, N, varlen ? 1 : 0, T_per_seq, &L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
+  if (records_offset) *records_offset = L.records_off;
+  if (record_bytes) *record_bytes = fkda::kRecBytes;
+  if (chunks_per_head) *chunks_per_head = L.chunks_per_head;
+  return FKDA_OK;
+}
+
+int fkda_prepare(const fkda_fwd_params* p, void* cuda_stream) {
+  Layout L;
+  int rc = validate(p, &L);
+  if (rc != FKDA_OK) return rc;
+  return do_prepare(p, L, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int fkda_scan(const fkda_fwd_params* p, void* cuda_stream) {
+  Layout L;
+  int rc = validate(p, &L);
+  if (rc != FKDA_OK) return rc;
+  return do_scan(p, L, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream) {
+  Layout L;
+  int rc = validate(p, &L);
+  if (rc != FKDA_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  rc = do_prepare(p, L, stream);
+  if (rc != FKDA_OK) return rc;
+  return do_scan(p, L, stream);
+}
+
+int fkda_prologue(const void* q, const void* k, const void* g, const void* beta, const float* A_log, const float* dt_bias,
+                  float lower_bound, int64_t T_total, int64_t H, void* qn, void* kn, float* gate, float* beta_act,
+                  void* cuda_stream) {
+  if (!q || !k || !g || !beta || !A_log || !dt_bias || !qn || !kn || !gate || !beta_act)
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "NULL pointer");
+  if (T_total < 0 || H <= 0 || H > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
+  cudaError_t e = fkda::launch_prologue(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(g),
+      static_cast<const __nv_bfloat16*>(beta), A_log, dt_bias, static_cast<float>(static_cast<double>(lower_bound) * 1.4426950408889634),
+      T_total * H, static_cast<int>(H), static_cast<__nv_bfloat16*>(qn), static_cast<__nv_bfloat16*>(kn), gate, beta_act,
+      static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_fail(e, "prologue launch");
+  return FKDA_OK;
+}
+
+int fkda_read_status(const void* workspace, void* cuda_stream, int* status) {
+  if (!workspace || !status) return fail(FKDA_ERR_INVALID_ARGUMENT, "NULL pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaMemcpyAsync(status, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status)");
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  if (*status != 0) return fail(FKDA_ERR_DEVICE_STATUS, "device status %d (%s)", *status,
+                                *status == 1 ? "cu_seqlens not monotone inside [0, T_total]" : "a bounded wait inside a kernel gave up");
+  return FKDA_OK;
+}
+
+int fkda_selftest_umma(const void* A, const void* B, float* D, int mode, int reps, int* status, void* cuda_stream) {
+  if (!A || !B || !D || !status || mode < 0 || mode > 2 || reps < 1) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
+  cudaError_t e = fkda::launch_umma_selftest(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B), D, mode,
+                                             reps, status, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_fail(e, "selftest launch");
+  return FKDA_OK;
+}
+
+const char* fkda_last_error(void) { return g_err; }
+
+const char* fkda_version(void) { return "fkda 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,490 @@
+// Token-parallel half of the KDA prefill: one CTA per (32-token chunk, head).
+//
+// Replaces the reference's K1 (csrc/smxx/fwd_kernel1.cuh:107-586) with a chunk-32 WY
+// formulation.  Per chunk it fuses
+//   * the prologue: q/k L2 norm, gate activation and its in-chunk cumulative sum, beta sigmoid
+//     (16-byte coalesced loads straight from the [T,H,128] tensors; no beta transpose),
+//   * the decay application in two 16-token sub-blocks, so that every 2^(+-cumsum) factor stays
+//     inside the fp32/bf16 exponent range for lower_bound >= -5 (16 * 5 * log2(e) = 115.4 < 126),
+//   * the intra-chunk products A = tril(k+ k-^T,-1) * beta and M = tril(q+ k-^T), with the
+//     cross sub-block quadrant taken between "decayed from sub-block start" and "decayed to
+//     sub-block end" operands (both factors <= 1),
+//   * T = (I + A)^-1 by fp32 forward substitution (two 16x16 diagonal blocks + one merge),
+//   * w' = T diag(beta) k+ and u' = T diag(beta) v,
+// and writes one operand record (fkda_common.cuh) for the scan kernel.
+#include "fkda_common.cuh"
+
+namespace fkda {
+
+// ---- tiny scheduling kernel (varlen): chunk_prefix[n] = sum_{m<n} ceil(len_m / 32) -------------------
+// Replaces the reference's one-thread prefix kernel (fwd_kernel1.cuh:89-104) and also checks
+// that cu_seqlens is monotone and inside [0, T_total]; violations are clamped and reported
+// through the status word instead of faulting later.
+__global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int* __restrict__ prefix,
+                                    int* __restrict__ status) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) {
+    carry = 0;
+    prefix[0] = 0;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int base = 0; base < N; base += blockDim.x) {
+    int n = base + threadIdx.x;
+    int cnt = 0;
+    if (n < N) {
+      int64_t a = cu[n], b = cu[n + 1];
+      if (a < 0 || b < a || b > T_total || (n == 0 && a != 0)) {
+        atomicCAS(status, kStatusOk, kStatusBadCuSeqlens);
+        a = a < 0 ? 0 : (a > T_total ? T_total : a);
+        b = b < a ? a : (b > T_total ? T_total : b);
+      }
+      cnt = static_cast<int>((b - a + kChunk - 1) / kChunk);
+    }
+    int x = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int s = (lane < (blockDim.x >> 5)) ? warp_sums[lane] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        int y = __shfl_up_sync(0xffffffffu, s, d);
+        if (lane >= d) s += y;
+      }
+      warp_sums[lane] = s;  // inclusive over warps
+    }
+    __syncthreads();
+    int incl = x + (warp > 0 ? warp_sums[warp - 1] : 0) + carry;
+    if (n < N) prefix[n + 1] = incl;
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry = incl;
+    __syncthreads();
+  }
+}
+
+// ---- shared-memory plan of the prepare kernel (byte offsets) --------------------------------------
+constexpr int kSmKPP = kRecBytes;            // [32][128] k+ from chunk start (rows 0-15 double as sub-block operand)
+constexpr int kSmKM = kSmKPP + 8192;         // [32][128] k-, relative to own sub-block start
+constexpr int kSmKP1 = kSmKM + 8192;         // [16][128] k+ of sub-block 1 relative to its own start
+constexpr int kSmQP1 = kSmKP1 + 4096;        // [16][128] q+ of sub-block 1 relative to its own start
+constexpr int kSmKR0 = kSmQP1 + 4096;        // [16][128] k of sub-block 0 decayed to the sub-block end
+constexpr int kSmV = kSmKR0 + 4096;          // [32][128] v
+constexpr int kSmTB = kSmV + 8192;           // [32][32] bf16 T diag(beta)
+constexpr int kSmA = kSmTB + 2048;           // [32][33] fp32 A
+constexpr int kSmT = kSmA + 4224;            // [32][33] fp32 T
+constexpr int kSmX = kSmT + 4224;            // [16][17] fp32
+constexpr int kSmTot = kSmX + 1088;          // [2][128] fp32 sub-block log2 decays
+constexpr int kSmSsq = kSmTot + 1024;        // [2][32][4] fp32 partial sums of squares
+constexpr int kSmBeta = kSmSsq + 1024;       // [32] fp32 sigmoid(beta)
+constexpr int kPrepSmemBytes = kSmBeta + 128;
+
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+  f[0] = bf_lo(w.x); f[1] = bf_hi(w.x); f[2] = bf_lo(w.y); f[3] = bf_hi(w.y);
+  f[4] = bf_lo(w.z); f[5] = bf_hi(w.z); f[6] = bf_lo(w.w); f[7] = bf_hi(w.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+
+// 16x16x128 product of two core-layout operands (rows of A times rows of B), fp32 accumulators
+// in the mma.sync C layout: acc[nt][0..1] -> (row lane/4, col 8nt + 2(lane%4) + {0,1}), acc[nt][2..3] -> row + 8.
+__device__ __forceinline__ void block16_product(uint32_t a_base, uint32_t b_base, int lane, float (&acc)[2][4]) {
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+  const int mi = lane >> 3, r = lane & 7;
+  const uint32_t a_lane = a_base + (mi & 1) * 2048 + (mi >> 1) * 128 + r * 16;
+  const uint32_t b_lane = b_base + (mi >> 1) * 2048 + (mi & 1) * 128 + r * 16;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+    ldsm_x4(a_lane + ks * 256, a0, a1, a2, a3);
+    ldsm_x4(b_lane + ks * 256, b0, b1, b2, b3);
+    mma_bf16_16816(acc[0], a0, a1, a2, a3, b0, b1);
+    mma_bf16_16816(acc[1], a0, a1, a2, a3, b2, b3);
+  }
+}
+
+__global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.y;
+  const int gc = blockIdx.x;
+
+  // ---- chunk -> (sequence, first token, valid length) -------------------------------------------
+  int64_t t0;
+  int len;
+  if (p.cu_seqlens != nullptr) {
+    if (gc >= p.chunk_prefix[p.N]) return;
+    int lo = 0, hi = p.N - 1;
+    while (lo < hi) {
+      int mid = (lo + hi + 1) >> 1;
+      if (p.chunk_prefix[mid] <= gc) lo = mid; else hi = mid - 1;
+    }
+    int64_t bos = p.cu_seqlens[lo], eos = p.cu_seqlens[lo + 1];
+    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
+    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
+    t0 = bos + static_cast<int64_t>(gc - p.chunk_prefix[lo]) * kChunk;
+    int64_t rem = eos - t0;
+    len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  } else {
+    const int cps = static_cast<int>((p.T + kChunk - 1) / kChunk);
+    const int n = gc / cps, lc = gc - n * cps;
+    t0 = static_cast<int64_t>(n) * p.T + static_cast<int64_t>(lc) * kChunk;
+    int64_t rem = p.T - static_cast<int64_t>(lc) * kChunk;
+    len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  }
+
+  // ---- thread -> two (row, 8-column) items of one sub-block ------------------------------------------
+  const int r8 = tid & 7;
+  const int cm = tid >> 3;
+  const int j = cm & 15;        // 8-column group: channels 8j .. 8j+7
+  const int sb = cm >> 4;       // sub-block (tokens 16sb .. 16sb+15); warps 0-3 -> 0, warps 4-7 -> 1
+  const int row0 = sb * 16 + r8, row1 = row0 + 8;
+
+  float* s_tot = reinterpret_cast<float*>(smem + kSmTot);
+  float* s_ssq = reinterpret_cast<float*>(smem + kSmSsq);
+  float* s_beta = reinterpret_cast<float*>(smem + kSmBeta);
+  float* s_A = reinterpret_cast<float*>(smem + kSmA);
+  float* s_T = reinterpret_cast<float*>(smem + kSmT);
+  float* s_X = reinterpret_cast<float*>(smem + kSmX);
+
+  // ---- P1: loads, partial sums of squares, v tile, beta -------------------------------------------
+  uint4 qw[2], kw[2], gw[2];
+  {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;
+      const bool valid = row < len;
+      const size_t off = (static_cast<size_t>(t0 + row) * p.H + h) * kD + 8 * j;
+      qw[hf] = valid ? __ldg(reinterpret_cast<const uint4*>(p.q + off)) : z;
+      kw[hf] = valid ? __ldg(reinterpret_cast<const uint4*>(p.k + off)) : z;
+      gw[hf] = valid ? __ldg(reinterpret_cast<const uint4*>(p.g + off)) : z;
+      const uint4 vw = valid ? __ldg(reinterpret_cast<const uint4*>(p.v + off)) : z;
+      *reinterpret_cast<uint4*>(smem + kSmV + core_off(row, 8 * j, kD)) = vw;
+    }
+  }
+  if (tid < kChunk) {
+    float b = 0.f;
+    if (tid < len) b = sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(t0 + tid) * p.H + h]));
+    s_beta[tid] = b;
+  }
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    float f[8], sq = 0.f, sk = 0.f;
+    unpack8(qw[hf], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sq = fmaf(f[i], f[i], sq);
+    unpack8(kw[hf], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sk = fmaf(f[i], f[i], sk);
+    // lanes sharing r8 inside the warp hold 4 different column groups of the same row
+    sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+    sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+    sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+    if (lane < 8) {
+      const int row = hf ? row1 : row0;
+      s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
+      s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
+    }
+  }
+  __syncthreads();
+
+  // ---- P2: norms, gate, in-sub-block cumulative sum, sub-block-relative operands ----------------------
+  const float a_gate = ex2f(__ldg(p.A_log + h) * kLog2e);
+  float bias[8];
+  {
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+    bias[0] = b0.x; bias[1] = b0.y; bias[2] = b0.z; bias[3] = b0.w;
+    bias[4] = b1.x; bias[5] = b1.y; bias[6] = b1.z; bias[7] = b1.w;
+  }
+  float G[2][8];      // log2 cumulative decay relative to the sub-block start
+  float kh[2][8];     // normalised k
+  float qh[2][8];     // normalised q * scale
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int row = hf ? row1 : row0;
+    const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
+    const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
+    const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
+    const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
+    float f[8];
+    unpack8(qw[hf], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qh[hf][i] = f[i] * rq;
+    unpack8(kw[hf], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) kh[hf][i] = f[i] * rk;
+    unpack8(gw[hf], f);
+    const bool valid = row < len;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float x = valid ? p.gate_scale * sigmoid_fast(a_gate * (f[i] + bias[i])) : 0.f;
+      // inclusive scan over the 8 rows held by the 8 lanes of this group
+#pragma unroll
+      for (int d = 1; d < 8; d <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
+        if (r8 >= d) x += y;
+      }
+      G[hf][i] = x;
+    }
+  }
+  float tot[8];       // log2 decay of the whole sub-block
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float first_half = __shfl_sync(0xffffffffu, G[0][i], 7, 8);
+    G[1][i] += first_half;
+    tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
+  }
+  if (r8 == 0) {
+    *reinterpret_cast<float4*>(s_tot + sb * kD + 8 * j) = make_float4(tot[0], tot[1], tot[2], tot[3]);
+    *reinterpret_cast<float4*>(s_tot + sb * kD + 8 * j + 4) = make_float4(tot[4], tot[5], tot[6], tot[7]);
+  }
+  float khp[2][8], khr[2][8], qhp[2][8];
+  {
+    float esb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) esb[i] = ex2f(tot[i]);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;      // chunk row
+      const int lrow = row - sb * 16;        // row inside the sub-block
+      float km[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float pw = ex2f(G[hf][i]), ipw = ex2f(-G[hf][i]);
+        khp[hf][i] = kh[hf][i] * pw;
+        qhp[hf][i] = qh[hf][i] * pw;
+        km[i] = kh[hf][i] * ipw;
+        khr[hf][i] = km[i] * esb[i];
+      }
+      *reinterpret_cast<uint4*>(smem + kSmKM + core_off(row, 8 * j, kD)) = pack8(km);
+      if (sb == 0) {
+        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(khp[hf]);
+        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(qhp[hf]);
+        *reinterpret_cast<uint4*>(smem + kSmKR0 + core_off(lrow, 8 * j, kD)) = pack8(khr[hf]);
+      } else {
+        *reinterpret_cast<uint4*>(smem + kSmKP1 + core_off(lrow, 8 * j, kD)) = pack8(khp[hf]);
+        *reinterpret_cast<uint4*>(smem + kSmQP1 + core_off(lrow, 8 * j, kD)) = pack8(qhp[hf]);
+        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(khr[hf]);
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- P3: chunk-relative operands (need the other sub-block's total) ---------------------------------
+  {
+    float eo[8], to[8];
+    const float4 t0v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j);
+    const float4 t1v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j + 4);
+    to[0] = t0v.x; to[1] = t0v.y; to[2] = t0v.z; to[3] = t0v.w;
+    to[4] = t1v.x; to[5] = t1v.y; to[6] = t1v.z; to[7] = t1v.w;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) eo[i] = ex2f(to[i]);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;
+      float a[8], b[8];
+      if (sb == 0) {   // decay to the chunk end = decay to sub-block end, then through sub-block 1
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = khr[hf][i] * eo[i];
+        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(a);
+      } else {         // decay from the chunk start = through sub-block 0, then from sub-block start
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          a[i] = khp[hf][i] * eo[i];
+          b[i] = qhp[hf][i] * eo[i];
+        }
+        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(a);
+        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(b);
+      }
+    }
+    if (sb == 0 && r8 == 0) {
+      float* e = reinterpret_cast<float*>(smem + kRecE) + 8 * j;
+      *reinterpret_cast<float4*>(e) = make_float4(ex2f(tot[0] + to[0]), ex2f(tot[1] + to[1]), ex2f(tot[2] + to[2]), ex2f(tot[3] + to[3]));
+      *reinterpret_cast<float4*>(e + 4) = make_float4(ex2f(tot[4] + to[4]), ex2f(tot[5] + to[5]), ex2f(tot[6] + to[6]), ex2f(tot[7] + to[7]));
+    }
+  }
+  __syncthreads();
+
+  // ---- P4: the six 16x16x128 intra-chunk products (one warp each) --------------------------------------
+  const uint32_t sbase = smem_u32(smem);
+  if (warp < 6) {
+    const int which = warp % 3;            // 0: (0,0) block, 1: (1,1) block, 2: (1,0) block
+    const bool is_m = warp >= 3;           // q-side (M) instead of k-side (A)
+    uint32_t a_base, b_base;
+    if (which == 0) {
+      a_base = sbase + (is_m ? kRecQP : kSmKPP);
+      b_base = sbase + kSmKM;
+    } else {
+      a_base = sbase + (is_m ? kSmQP1 : kSmKP1);
+      b_base = sbase + (which == 1 ? kSmKM + 4096 : kSmKR0);
+    }
+    float acc[2][4];
+    block16_product(a_base, b_base, lane, acc);
+    const int rbase = (which == 0) ? 0 : 16, cbase = (which == 1) ? 16 : 0;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int lr = (lane >> 2) + half * 8, lc = nt * 8 + (lane & 3) * 2;
+        const int r = rbase + lr, c = cbase + lc;
+        float x0 = acc[nt][half * 2], x1 = acc[nt][half * 2 + 1];
+        if (!is_m) {
+          const float br = s_beta[r];
+          if (which != 2) {               // strictly lower triangle of a diagonal block
+            x0 = (lc < lr) ? x0 * br : 0.f;
+            x1 = (lc + 1 < lr) ? x1 * br : 0.f;
+          } else {
+            x0 *= br;
+            x1 *= br;
+          }
+          s_A[r * 33 + c] = x0;
+          s_A[r * 33 + c + 1] = x1;
+        } else {
+          if (which != 2) {               // lower triangle including the diagonal
+            x0 = (lc <= lr) ? x0 : 0.f;
+            x1 = (lc + 1 <= lr) ? x1 : 0.f;
+          }
+          *reinterpret_cast<uint32_t*>(smem + kRecMQK + core_off(r, c, kChunk)) = pack_bf16(x0, x1);
+        }
+      }
+  } else if (warp == 6) {
+    // upper-right quadrant of M (rows 0-15, cols 16-31) is zero: two 8-row groups x two column blocks
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = lane + 32 * i;       // 128 uint32 = 512 B: blocks (rg 0..1, cb 2..3), 128 B each
+      const int blk = idx >> 5, w = idx & 31;
+      const int rg = blk >> 1, cb = 2 + (blk & 1);
+      *reinterpret_cast<uint32_t*>(smem + kRecMQK + rg * 512 + cb * 128 + w * 4) = 0u;
+    }
+  }
+  __syncthreads();
+
+  // ---- P5: T = (I + A)^-1 -------------------------------------------------------------------------------
+  if (warp == 0) {
+    // forward substitution, one column of one diagonal block per lane: x_i = [i==c] - sum_{j<i} A_ij x_j
+    const int b = lane >> 4, c = lane & 15;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float acc = (i == c) ? 1.f : 0.f;
+#pragma unroll
+      for (int jj = 0; jj < i; ++jj) acc = fmaf(-s_A[(b * 16 + i) * 33 + b * 16 + jj], x[jj], acc);
+      x[i] = acc;
+      s_T[(b * 16 + i) * 33 + b * 16 + c] = acc;
+    }
+  }
+  __syncthreads();
+  {
+    const int i = tid >> 4, c = tid & 15;   // X = A_10 T_00
+    float acc = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) acc = fmaf(s_A[(16 + i) * 33 + jj], s_T[jj * 33 + c], acc);
+    s_X[i * 17 + c] = acc;
+  }
+  __syncthreads();
+  {
+    const int i = tid >> 4, c = tid & 15;   // T_10 = -T_11 X
+    float acc = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) acc = fmaf(-s_T[(16 + i) * 33 + 16 + jj], s_X[jj * 17 + c], acc);
+    s_T[(16 + i) * 33 + c] = acc;
+  }
+  __syncthreads();
+  {
+    // TB = T diag(beta) as a bf16 core-layout A operand; 4 consecutive columns per thread
+    const int i = tid >> 3, c4 = (tid & 7) * 4;
+    float t[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int c = c4 + e;
+      const bool nz = (c <= i) && !(i < 16 && c >= 16);
+      t[e] = nz ? s_T[i * 33 + c] * s_beta[c] : 0.f;
+    }
+    *reinterpret_cast<uint2*>(smem + kSmTB + core_off(i, c4, kChunk)) = make_uint2(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]));
+  }
+  __syncthreads();
+
+  // ---- P6: w' = TB k+ (warps 0-3), u' = TB v (warps 4-7); 32 output columns per warp ----------------------
+  {
+    const bool is_u = warp >= 4;
+    const int nb = (warp & 3) * 4;           // first 8-column tile of this warp
+    const uint32_t b_arr = sbase + (is_u ? kSmV : kSmKPP);
+    const int mi = lane >> 3, r = lane & 7;
+    float acc[2][4][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        ldsm_x4(sbase + kSmTB + (2 * mt + (mi & 1)) * 512 + (2 * ks + (mi >> 1)) * 128 + r * 16, a[mt][0], a[mt][1], a[mt][2],
+                a[mt][3]);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        // transposed loads: matrices (token group 2ks + (mi&1), column tile nb + 2np + (mi>>1))
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_trans(b_arr + (2 * ks + (mi & 1)) * 2048 + (nb + 2 * np + (mi >> 1)) * 128 + r * 16, b0, b1, b2, b3);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma_bf16_16816(acc[mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+          mma_bf16_16816(acc[mt][2 * np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+        }
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int row = mt * 16 + (lane >> 2) + half * 8;
+          const int col = (nb + nt) * 8 + (lane & 3) * 2;
+          const uint32_t val = pack_bf16(acc[mt][nt][half * 2], acc[mt][nt][half * 2 + 1]);
+          if (is_u)
+            *reinterpret_cast<uint32_t*>(smem + kRecUP + row * 256 + col * 2) = val;
+          else
+            *reinterpret_cast<uint32_t*>(smem + kRecWP + core_off(row, col, kD)) = val;
+        }
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0) {
+    uint8_t* dst = p.records + (static_cast<size_t>(h) * p.total_chunks + gc) * kRecBytes;
+    bulk_s2g(dst, sbase, kRecBytes);
+    bulk_commit();
+    bulk_wait_read0();
+  }
+}
+
+cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int* prefix, int* status, cudaStream_t stream) {
+  chunk_prefix_kernel<<<1, 256, 0, stream>>>(cu, N, T_total, prefix, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes);
+  if (e != cudaSuccess) return e;
+  if (p.total_chunks == 0 || p.H == 0) return cudaSuccess;
+  dim3 grid(p.total_chunks, p.H);
+  prepare_kernel<<<grid, 256, kPrepSmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace fkda

@@ -1,0 +1,388 @@
+// Inter-chunk recurrence of the KDA prefill: one CTA walks the chunks of one (sequence, head)
+// chain, with the 128x128 fp32 state resident in tensor memory for the whole chain.
+//
+// Replaces the reference's K2 (csrc/smxx/fwd_kernel2.cuh:115-839).  Per 32-token chunk, with S
+// the state at the chunk start held as S^T [v lanes][k columns]:
+//     W^T  = S^T wp^T                  tcgen05.mma  M=128 (v), N=32 (tokens), K=128
+//     O^T  = S^T qp^T                  tcgen05.mma  M=128, N=32, K=128
+//     U^T  = up^T - W^T                warps: TMEM -> registers -> bf16 operand in shared memory
+//     S^T  = S^T diag(e) + U^T kr      tcgen05.mma  M=128, N=128 (k), K=32, accumulating in TMEM
+//     O^T += U^T mqk^T                 tcgen05.mma  M=128, N=32, K=32
+// The decay diag(e) and the bf16 operand copy of S are produced by one TMEM round trip per
+// chunk.  Operand records arrive by bulk async copies through a 3-stage mbarrier ring.
+//
+// Warp roles (320 threads): warp 0 = copy producer, warp 1 = MMA issuer (+ TMEM owner),
+// warps 2-5 = state warps (U and S epilogues), warps 6-9 = output warps.  Each group of four
+// consecutive warps covers the four TMEM lane quadrants (quadrant = warp index mod 4).
+// Every wait is bounded; a wait that gives up raises an abort flag, records a status code and
+// lets all roles fall through to the common exit, where TMEM is released.
+#include "fkda_common.cuh"
+
+namespace fkda {
+
+constexpr int kStages = 3;
+constexpr int kScanThreads = 320;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColW = 128, kColO = 160;
+
+// shared-memory plan (byte offsets from a 1024-byte aligned base)
+constexpr int kSmStage = 0;                                  // kStages records
+constexpr int kSmSb = kSmStage + kStages * kRecBytes;        // [128 v][128 k] bf16 operand copy of S (core layout)
+constexpr int kSmUt = kSmSb + 32768;                         // [128 v][32 tok] bf16 U^T (core layout)
+constexpr int kSmStateStg = kSmUt + 8192;                    // 4 warps x [32][33] fp32 staging for state I/O
+constexpr int kSmOutStg = kSmStateStg + 4 * 4224;            // 4 warps x [32 tok][32 v] bf16 staging for out
+constexpr int kSmBars = kSmOutStg + 4 * 2048;                // mbarriers
+constexpr int kSmMisc = kSmBars + 128;                       // tmem base, abort flag
+constexpr int kScanSmemBytes = kSmMisc + 64 + 1024;          // + slack for manual 1024-byte alignment
+
+// mbarrier slots
+enum { BAR_FULL = 0, BAR_EMPTY = 3, BAR_WFULL = 6, BAR_OFULL, BAR_SFULL, BAR_UREADY, BAR_SBREADY, BAR_OFREE, BAR_COUNT };
+
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const bool ok = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
+
+__global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
+
+  // ---- chain -> tokens and records ---------------------------------------------------------------------
+  const int chain = blockIdx.x;
+  const int n = chain / p.H, h = chain - n * p.H;
+  int64_t bos, eos;
+  int chunk_base;
+  if (p.cu_seqlens != nullptr) {
+    bos = p.cu_seqlens[n];
+    eos = p.cu_seqlens[n + 1];
+    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
+    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
+    chunk_base = p.chunk_prefix[n];
+  } else {
+    bos = static_cast<int64_t>(n) * p.T;
+    eos = bos + p.T;
+    chunk_base = n * static_cast<int>((p.T + kChunk - 1) / kChunk);
+  }
+  int nchunks = static_cast<int>((eos - bos + kChunk - 1) / kChunk);
+  {  // never read past the records of this head, whatever cu_seqlens claims
+    const int avail = p.total_chunks > chunk_base ? p.total_chunks - chunk_base : 0;
+    if (nchunks > avail) nchunks = avail;
+  }
+  const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + chunk_base) * kRecBytes;
+
+  // ---- setup -----------------------------------------------------------------------------------------------
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(BAR_FULL + s), 1);
+      mbar_init(bar(BAR_EMPTY + s), 1 + 4);   // MMA commit + one arrival per state warp
+    }
+    mbar_init(bar(BAR_WFULL), 1);
+    mbar_init(bar(BAR_OFULL), 1);
+    mbar_init(bar(BAR_SFULL), 1);
+    mbar_init(bar(BAR_UREADY), 4);
+    mbar_init(bar(BAR_SBREADY), 4);
+    mbar_init(bar(BAR_OFREE), 4);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  bool failed = false;
+
+  if (warp == 0) {
+    // ===== copy producer: one bulk copy per chunk record ===================================================
+    if (lane == 0) {
+      int issued = 0;
+      for (int c = 0; c < nchunks; ++c) {
+        const int s = c % kStages, k = c / kStages;
+        if (k > 0 && !mbar_wait(bar(BAR_EMPTY + s), (k - 1) & 1, abort_flag)) { failed = true; break; }
+        mbar_arrive_expect_tx(bar(BAR_FULL + s), kRecBytes);
+        bulk_g2s(sbase + kSmStage + s * kRecBytes, rec0 + static_cast<size_t>(c) * kRecBytes, kRecBytes, bar(BAR_FULL + s));
+        issued = c + 1;
+      }
+      if (failed || *abort_flag) {
+        // wait (bounded) for copies still in flight so that the CTA does not exit under them
+        for (int c = issued > kStages ? issued - kStages : 0; c < issued; ++c) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(bar(BAR_FULL + c % kStages), (c / kStages) & 1))
+            if (globaltimer_ns() - t0 > 20000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer ==========================================================================================
+    if (lane == 0) {
+      constexpr uint32_t idesc_n32 = umma_idesc_bf16(128, 32, 0, 0);
+      constexpr uint32_t idesc_n128_bmn = umma_idesc_bf16(128, 128, 0, 1);
+      const uint32_t sb_addr = sbase + kSmSb, ut_addr = sbase + kSmUt;
+      for (int c = 0; c < nchunks; ++c) {
+        const int s = c % kStages, k = c / kStages;
+        const uint32_t rec = sbase + kSmStage + s * kRecBytes;
+        if (!mbar_wait(bar(BAR_FULL + s), k & 1, abort_flag)) { failed = true; break; }
+        if (!mbar_wait(bar(BAR_SBREADY), c & 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        // W^T = Sb wp^T : A = Sb [128][128] K-major, B = WP [32][128] K-major; 8 k-steps of 16
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss(tmem + kColW, umma_desc(sb_addr + ks * 256, 128, 2048), umma_desc(rec + kRecWP + ks * 256, 128, 2048),
+                  idesc_n32, ks > 0);
+        umma_commit(bar(BAR_WFULL));
+        if (c > 0 && !mbar_wait(bar(BAR_OFREE), (c - 1) & 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss(tmem + kColO, umma_desc(sb_addr + ks * 256, 128, 2048), umma_desc(rec + kRecQP + ks * 256, 128, 2048),
+                  idesc_n32, ks > 0);
+        if (!mbar_wait(bar(BAR_UREADY), c & 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        // S^T += U^T kr : A = Ut [128][32] K-major (8-row groups 512 B apart), B = KR [32 tok][128 k] read
+        // MN-major: core matrices adjacent along k 128 B apart, 8-token groups 2048 B apart
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+          umma_ss(tmem + kColS, umma_desc(ut_addr + ks * 256, 128, 512), umma_desc(rec + kRecKR + ks * 4096, 2048, 128),
+                  idesc_n128_bmn, 1);
+        umma_commit(bar(BAR_SFULL));
+        // O^T += U^T mqk^T : B = MQK [32][32] K-major (8-row groups 512 B apart)
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+          umma_ss(tmem + kColO, umma_desc(ut_addr + ks * 256, 128, 512), umma_desc(rec + kRecMQK + ks * 256, 128, 512),
+                  idesc_n32, 1);
+        umma_commit(bar(BAR_OFULL));
+        umma_commit(bar(BAR_EMPTY + s));
+      }
+      // the last commit's arrival must have landed in shared memory before the CTA may exit
+      if (!failed && nchunks > 0) {
+        const int c = nchunks - 1;
+        if (!mbar_wait(bar(BAR_EMPTY + c % kStages), (c / kStages) & 1, abort_flag)) failed = true;
+      }
+    }
+  } else if (warp < 6) {
+    // ===== state warps: own TMEM lanes [32q, 32q+32) = state rows v ==========================================
+    const int qd = warp & 3;
+    const int v = qd * 32 + lane;
+    const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
+    float* stg = reinterpret_cast<float*>(smem + kSmStateStg + qd * 4224);
+    const size_t state_off = (static_cast<size_t>(n) * p.H + h) * kD * kD + static_cast<size_t>(qd) * 32 * kD;
+    uint8_t* sb_row = smem + kSmSb + (v >> 3) * 2048 + (v & 7) * 16;   // + 128 * (k / 8)
+    uint8_t* ut_row = smem + kSmUt + (v >> 3) * 512 + (v & 7) * 16;    // + 128 * (tok / 8)
+
+    // ---- initial state -> TMEM (pre-decayed by the first chunk's e) and bf16 operand copy ----------------
+    bool ok = true;
+    if (nchunks > 0) ok = warp_wait(bar(BAR_FULL + 0), 0, abort_flag);
+    if (ok) {
+      const float* e0 = reinterpret_cast<const float*>(smem + kSmStage + kRecE);
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t x[32];
+        if (p.initial_state != nullptr) {
+          // coalesced: 8 lanes cover one 128-byte row segment (fp32) / 4 lanes one 64-byte segment (bf16)
+          if (p.state_fp32) {
+            const float* src = reinterpret_cast<const float*>(p.initial_state) + state_off + cb * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+              const float4 f = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(r) * kD + c4));
+              stg[r * 33 + c4] = f.x; stg[r * 33 + c4 + 1] = f.y; stg[r * 33 + c4 + 2] = f.z; stg[r * 33 + c4 + 3] = f.w;
+            }
+          } else {
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + state_off + cb * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
+              const uint4 w = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * kD + c8));
+              float* d = stg + r * 33 + c8;
+              d[0] = bf_lo(w.x); d[1] = bf_hi(w.x); d[2] = bf_lo(w.y); d[3] = bf_hi(w.y);
+              d[4] = bf_lo(w.z); d[5] = bf_hi(w.z); d[6] = bf_lo(w.w); d[7] = bf_hi(w.w);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(stg[lane * 33 + i]);
+          __syncwarp();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = 0u;
+        }
+        if (nchunks > 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(sb_row + (cb * 4 + i) * 128) =
+                make_uint4(pack_bf16(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
+                           pack_bf16(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
+                           pack_bf16(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
+                           pack_bf16(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e0[cb * 32 + i]);
+        }
+        tmem_st32(tq + kColS + cb * 32, x);
+      }
+      tmem_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_SBREADY));
+    } else {
+      failed = true;
+    }
+
+    for (int c = 0; c < nchunks && !failed; ++c) {
+      const int s = c % kStages;
+      const uint8_t* rec = smem + kSmStage + s * kRecBytes;
+      // ---- U epilogue -------------------------------------------------------------------------------------
+      if (!warp_wait(bar(BAR_WFULL), c & 1, abort_flag)) { failed = true; break; }
+      tc_fence_after();
+      {
+        uint32_t w[32];
+        tmem_ld32(tq + kColW, w);
+        tmem_wait_ld();
+        const __nv_bfloat16* up = reinterpret_cast<const __nv_bfloat16*>(rec + kRecUP) + v;
+        float u[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) u[i] = __bfloat162float(up[i * kD]) - __uint_as_float(w[i]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(ut_row + i * 128) =
+              make_uint4(pack_bf16(u[8 * i], u[8 * i + 1]), pack_bf16(u[8 * i + 2], u[8 * i + 3]),
+                         pack_bf16(u[8 * i + 4], u[8 * i + 5]), pack_bf16(u[8 * i + 6], u[8 * i + 7]));
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(BAR_UREADY));
+        mbar_arrive(bar(BAR_EMPTY + s));   // this warp is done reading up[] of the stage
+      }
+      // ---- S epilogue: bf16 operand copy of the new state, then pre-decay for the next chunk ------------
+      if (c + 1 == nchunks) break;          // the last state is only read back once, below
+      if (!warp_wait(bar(BAR_SFULL), c & 1, abort_flag)) { failed = true; break; }
+      if (!warp_wait(bar(BAR_FULL + (c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag)) { failed = true; break; }
+      tc_fence_after();
+      {
+        const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE);
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t x[32];
+          tmem_ld32(tq + kColS + cb * 32, x);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(sb_row + (cb * 4 + i) * 128) =
+                make_uint4(pack_bf16(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
+                           pack_bf16(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
+                           pack_bf16(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
+                           pack_bf16(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e[cb * 32 + i]);
+          tmem_st32(tq + kColS + cb * 32, x);
+        }
+      }
+      tmem_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_SBREADY));
+    }
+
+    // ---- final state -> global -------------------------------------------------------------------------------
+    if (!failed && p.final_state != nullptr) {
+      bool ok2 = true;
+      if (nchunks > 0) ok2 = warp_wait(bar(BAR_SFULL), (nchunks - 1) & 1, abort_flag);
+      if (ok2) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t x[32];
+          tmem_ld32(tq + kColS + cb * 32, x);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(x[i]);
+          __syncwarp();
+          if (p.state_fp32) {
+            float* dst = reinterpret_cast<float*>(p.final_state) + state_off + cb * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+              const float* sp = stg + r * 33 + c4;
+              *reinterpret_cast<float4*>(dst + static_cast<size_t>(r) * kD + c4) = make_float4(sp[0], sp[1], sp[2], sp[3]);
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.final_state) + state_off + cb * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
+              const float* sp = stg + r * 33 + c8;
+              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * kD + c8) =
+                  make_uint4(pack_bf16(sp[0], sp[1]), pack_bf16(sp[2], sp[3]), pack_bf16(sp[4], sp[5]), pack_bf16(sp[6], sp[7]));
+            }
+          }
+          __syncwarp();
+        }
+      } else {
+        failed = true;
+      }
+    }
+  } else {
+    // ===== output warps: O^T (TMEM lanes = v, columns = tokens) -> out[token][h][v] ===========================
+    const int qd = warp & 3;
+    const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
+    __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + kSmOutStg + qd * 2048);   // [32 tok][32 v]
+    for (int c = 0; c < nchunks; ++c) {
+      if (!warp_wait(bar(BAR_OFULL), c & 1, abort_flag)) { failed = true; break; }
+      tc_fence_after();
+      uint32_t o[32];
+      tmem_ld32(tq + kColO, o);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_OFREE));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) stg[i * 32 + lane] = __float2bfloat16_rn(__uint_as_float(o[i]));
+      __syncwarp();
+      const int64_t tok0 = bos + static_cast<int64_t>(c) * kChunk;
+      const int valid = (eos - tok0) < kChunk ? static_cast<int>(eos - tok0) : kChunk;
+      // each token row of this warp's 32 v-columns is 64 contiguous bytes: 4 lanes x 16 B, 8 rows per pass
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
+        if (r < valid) {
+          const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 32 + c8);
+          *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(tok0 + r) * p.H + h) * kD + qd * 32 + c8) = val;
+        }
+      }
+      __syncwarp();
+    }
+  }
+
+  if (failed || *abort_flag) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+
+  // ---- common exit: every thread arrives here, TMEM goes back ------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int64_t chains = static_cast<int64_t>(p.N) * p.H;
+  if (chains == 0) return cudaSuccess;
+  scan_kernel<<<static_cast<unsigned>(chains), kScanThreads, kScanSmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace fkda

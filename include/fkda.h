@@ -1,0 +1,109 @@
+/*
+ * fkda.h -- C ABI of the B200 (sm_100a) Kimi Delta Attention prefill.
+ *
+ * This is the drop-in boundary for the reference's one operator, `flash_kda.fwd`.  It replaces
+ * the reference's host op `fwd(...)` (csrc/flash_kda.cpp:28-217), its workspace sizing
+ * `get_workspace_size` (csrc/flash_kda.cpp:5-26) and the templated launch layer `launch_fwd`
+ * (csrc/fwd.h:6-27, csrc/smxx/fwd_launch.cu:7-217), with the template booleans (state in / state
+ * out / fp32 state / varlen) turned into run-time fields.  Plain pointers and sizes only: no torch
+ * types, nothing is allocated, nothing synchronises, nothing throws.  All work is enqueued on the
+ * CUDA stream passed in; all pointers are device pointers on the current device.
+ *
+ * Every function returns 0 on success or a negative fkda_error; fkda_last_error() then holds a
+ * message for the calling thread.  Argument errors are reported before anything is launched,
+ * as the reference does with TORCH_CHECK (csrc/flash_kda.cpp:44-174).
+ */
+#ifndef FKDA_H_
+#define FKDA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fkda_error {
+  FKDA_OK = 0,
+  FKDA_ERR_INVALID_ARGUMENT = -1,
+  FKDA_ERR_WORKSPACE_TOO_SMALL = -2,
+  FKDA_ERR_CUDA = -3,
+  FKDA_ERR_DEVICE_STATUS = -4
+} fkda_error;
+
+typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_STATE_FP32 = 2 } fkda_state_dtype;
+
+/* flags */
+#define FKDA_FLAG_SCAN_SIMT 0x1u /* evaluate the recurrence on CUDA cores (verification aid, slow) */
+
+typedef struct fkda_fwd_params {
+  /* bf16 [B*T][H][128], contiguous (reference: q,k,v,g of csrc/flash_kda.cpp:28-33) */
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* g;
+  const void* beta;          /* bf16 [B*T][H] logits; no transposed copy is needed            */
+  void* out;                 /* bf16 [B*T][H][128], every valid row is written                  */
+  const float* A_log;        /* fp32 [H]                                                        */
+  const float* dt_bias;      /* fp32 [H][128]                                                   */
+  const void* initial_state; /* [N][H][128 v][128 k] of state_dtype, or NULL (start from zero) */
+  void* final_state;         /* same shape and dtype, or NULL                                   */
+  const int64_t* cu_seqlens; /* device int64 [N+1], or NULL for B equal-length sequences        */
+  void* workspace;           /* >= fkda_get_workspace_size bytes, 256-byte aligned              */
+  int64_t workspace_bytes;
+  int64_t B;                 /* batch; must be 1 when cu_seqlens is given                       */
+  int64_t T;                 /* tokens per batch row (total tokens when cu_seqlens is given)    */
+  int64_t H;                 /* heads                                                           */
+  int64_t N;                 /* sequences: B, or len(cu_seqlens)-1                              */
+  float scale;               /* applied to q (reference passes K^-0.5)                          */
+  float lower_bound;         /* gate lower bound, expected in [-5, 0]                           */
+  int32_t state_dtype;       /* fkda_state_dtype of initial_state / final_state                 */
+  uint32_t flags;
+} fkda_fwd_params;
+
+/* Bytes of scratch the forward pass needs (replaces get_workspace_size, csrc/flash_kda.cpp:5-26).
+ * T_total = B*T.  The figure differs from the reference's: one 35328-byte operand record per
+ * (head, 32-token chunk) plus a small header. */
+int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* bytes);
+
+/* The whole operator (replaces fwd(), csrc/flash_kda.cpp:28-217): prepare + scan on `stream`. */
+int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream);
+
+/* The two stages on their own, for tests and profiling.  fkda_prepare fills the workspace
+ * (reference K1, csrc/smxx/fwd_kernel1.cuh:107); fkda_scan consumes it (reference K2,
+ * csrc/smxx/fwd_kernel2.cuh:115).  fkda_fwd == fkda_prepare followed by fkda_scan. */
+int fkda_prepare(const fkda_fwd_params* p, void* cuda_stream);
+int fkda_scan(const fkda_fwd_params* p, void* cuda_stream);
+
+/* Token-wise prologue alone (the gate / L2-norm / sigmoid part of reference K1,
+ * csrc/smxx/fwd_kernel1.cuh:265-339): qn,kn bf16 [rows][128] normalised q,k; gate fp32
+ * [rows][128] = lower_bound*log2(e)*sigmoid(exp(A_log)*(g+dt_bias)); beta_act fp32 [rows].
+ * rows = B*T*H laid out [token][head]. */
+int fkda_prologue(const void* q, const void* k, const void* g, const void* beta, const float* A_log,
+                  const float* dt_bias, float lower_bound, int64_t T_total, int64_t H, void* qn, void* kn,
+                  float* gate, float* beta_act, void* cuda_stream);
+
+/* Byte offset and size of the operand record of (head, chunk) inside the workspace, and the
+ * number of records per head, so that a test can inspect what fkda_prepare wrote. */
+int fkda_workspace_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq,
+                          int64_t* records_offset, int64_t* record_bytes, int64_t* chunks_per_head);
+
+/* Reads the device status word of a workspace after synchronising `stream`: 0 = fine,
+ * 1 = cu_seqlens was not monotone inside [0, T_total], 2 = a bounded wait inside a kernel gave up.
+ * The only call here that blocks the host. */
+int fkda_read_status(const void* workspace, void* cuda_stream, int* status);
+
+/* One-CTA tcgen05 products in the descriptor flavours of the scan kernel (mode 0,1,2; see
+ * fkda_aux.cu).  A, B bf16 row-major, D fp32 row-major, all device pointers; status int32. */
+int fkda_selftest_umma(const void* A, const void* B, float* D, int mode, int reps, int* status,
+                       void* cuda_stream);
+
+/* Message of the last error on this thread ("" if none). */
+const char* fkda_last_error(void);
+
+/* Library version string. */
+const char* fkda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FKDA_H_ */

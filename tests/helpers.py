@@ -56,3 +56,31 @@ def rel_fro(a, b):
     """||a-b|| / ||b|| with b the trusted side."""
     b = b.double()
     return ((a.double() - b).norm() / (b.norm() + 1e-30)).item()
+
+
+# ---- operand-record decoding (layout defined in flashkda_b200/csrc/fkda_common.cuh) ----
+REC = dict(WP=0, QP=8192, KR=16384, UP=24576, MQK=32768, E=34816, BYTES=35328)
+
+
+def _core_index(rows, cols):
+    r = torch.arange(rows).view(-1, 1)
+    c = torch.arange(cols).view(1, -1)
+    return ((r // 8) * (cols * 16) + (c // 8) * 128 + (r % 8) * 16 + (c % 8) * 2) // 2
+
+
+def decode_record(rec_u8):
+    """rec_u8: CPU uint8 tensor of one 35328-byte record -> dict of float64 matrices."""
+    def bf(off, nbytes):
+        return rec_u8[off:off + nbytes].view(torch.bfloat16)
+    idx = _core_index(32, 128)
+    out = {}
+    for name in ("WP", "QP", "KR"):
+        out[name.lower()] = bf(REC[name], 8192)[idx].double()
+    out["up"] = bf(REC["UP"], 8192).view(32, 128).double()
+    out["mqk"] = bf(REC["MQK"], 2048)[_core_index(32, 32)].double()
+    out["ec"] = rec_u8[REC["E"]:REC["E"] + 512].view(torch.float32).double()
+    return out
+
+
+def to_cuda(x):
+    return {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in x.items()}

@@ -1,0 +1,206 @@
+"""GPU parity of `flash_kda.fwd` (through the C ABI) against the CPU oracle.
+
+Tolerances are the contract's: bf16 `out` max-abs error <= 2e-2 and final-state relative
+(Frobenius) error <= 1e-2, both against the fp64 per-token recurrence.  The distance to the
+reference's own chunk-16/bf16 algorithm (golden vectors, or its C port) is printed alongside.
+The shape / state-variant matrix follows the reference's tests/test_fwd_full.py:48-205.
+"""
+import pytest
+import torch
+
+import flash_kda
+import flashkda_b200 as F
+import oracle
+from flashkda_b200.workloads import Workload, baseline_workload, make_inputs
+from helpers import OUT_MAX_ABS, STATE_REL, golden_names, load_golden, max_abs, rel_fro, to_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gpu(x, fin_dtype, flags=0, check_status=True):
+    xc = to_cuda(x)
+    out = torch.full_like(xc["v"], float("nan"))
+    fin = None
+    if fin_dtype is not None:
+        N = x["cu_seqlens"].numel() - 1 if x["cu_seqlens"] is not None else x["q"].shape[0]
+        fin = torch.full((N, x["q"].shape[2], 128, 128), float("nan"), dtype=fin_dtype, device="cuda")
+    init = xc["initial_state"]
+    init_copy = None if init is None else init.clone()
+    B, T, H = x["q"].shape[:3]
+    N = x["cu_seqlens"].numel() - 1 if x["cu_seqlens"] is not None else B
+    ws = torch.empty(F.get_workspace_size(B * T, H, N), dtype=torch.uint8, device="cuda")
+    flash_kda.fwd(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], x["scale"], out, xc["A_log"], xc["dt_bias"],
+                  x["lower_bound"], initial_state=init, final_state=fin, cu_seqlens=xc["cu_seqlens"],
+                  workspace=ws, flags=flags)
+    if check_status:
+        assert F.read_status(ws) == 0
+    torch.cuda.synchronize()
+    if init is not None:
+        assert torch.equal(init, init_copy), "initial_state was modified"
+    return out.cpu(), None if fin is None else fin.cpu()
+
+
+def check_against_f64(x, out, fin, tag, big_state=False):
+    o64, s64 = oracle.recurrence_f64(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["A_log"],
+                                     x["dt_bias"], x["lower_bound"], initial_state=x["initial_state"],
+                                     cu_seqlens=x["cu_seqlens"])
+    assert not torch.isnan(out.float()).any(), f"{tag}: some out rows were not written"
+    e_out = max_abs(out, o64)
+    e_st = rel_fro(fin, s64) if fin is not None else 0.0
+    print(f"{tag}: out max-abs {e_out:.3e} (|out| max {o64.abs().max():.2f}), state rel {e_st:.3e}")
+    if big_state:
+        assert rel_fro(out, o64) <= 1e-2
+    else:
+        assert e_out <= OUT_MAX_ABS, f"{tag}: out max-abs error {e_out}"
+    if fin is not None:
+        assert not torch.isnan(fin.float()).any()
+        assert e_st <= STATE_REL, f"{tag}: final-state relative error {e_st}"
+    return o64, s64
+
+
+@pytest.mark.parametrize("flags", [F.FLAG_SCAN_SIMT, 0], ids=["simt_checker", "tcgen05"])
+@pytest.mark.parametrize("name", golden_names())
+def test_golden_cases(name, flags):
+    x, ref_out, ref_fin = load_golden(name)
+    fin_dtype = None if ref_fin is None else ref_fin.dtype
+    out, fin = run_gpu(x, fin_dtype, flags)
+    big = x["initial_state"] is not None and x["initial_state"].float().abs().max() > 100
+    check_against_f64(x, out, fin, f"{name}[{flags}]", big_state=big)
+    # distance to the reference's own (chunk-16, bf16-state) results
+    d_out = rel_fro(out, ref_out) if big else max_abs(out, ref_out)
+    d_st = rel_fro(fin, ref_fin) if fin is not None else 0.0
+    print(f"{name}[{flags}]: vs reference vectors: out {d_out:.3e}, state rel {d_st:.3e}")
+    assert d_out <= (1e-2 if big else OUT_MAX_ABS) and d_st <= STATE_REL
+
+
+STATE_IO = [(True, True), (True, False), (False, True), (False, False)]
+
+
+@pytest.mark.parametrize("T", [16, 64, 256, 1024, 17, 37, 97, 1, 31, 32, 33])
+@pytest.mark.parametrize("state", ["bf16", "fp32"])
+@pytest.mark.parametrize("has_in,has_out", STATE_IO, ids=["in+out", "in_only", "out_only", "no_state"])
+def test_fixed_length_matrix(T, state, has_in, has_out):
+    H = 4 if T <= 256 else 2
+    w = Workload("m", H=H, B=1, T=T, state_in=state if has_in else None, state_out=state if has_out else None,
+                 state_std=0.5, seed=T)
+    x = make_inputs(w)
+    fin_dtype = None if not has_out else (torch.bfloat16 if state == "bf16" else torch.float32)
+    out, fin = run_gpu(x, fin_dtype)
+    check_against_f64(x, out, fin, f"T{T}-{state}-{has_in}-{has_out}")
+
+
+VARLEN = [[16], [16, 16], [4, 8, 12], [64, 128, 256], [1300, 547, 2048, 963, 271, 3063], [1024] * 8,
+          [20, 50, 100], [17, 33, 65], [1, 1, 1, 40]]
+
+
+@pytest.mark.parametrize("seq_lens", VARLEN, ids=lambda s: "seqs" + "_".join(map(str, s)))
+@pytest.mark.parametrize("state", ["bf16", "fp32"])
+def test_varlen_matrix(seq_lens, state):
+    H = 2 if sum(seq_lens) > 2000 else 4
+    w = Workload("v", H=H, seq_lens=seq_lens, state_in=state, state_out=state, state_std=0.5, seed=len(seq_lens))
+    x = make_inputs(w)
+    out, fin = run_gpu(x, torch.bfloat16 if state == "bf16" else torch.float32)
+    check_against_f64(x, out, fin, f"varlen{seq_lens}-{state}")
+
+
+@pytest.mark.parametrize("B,T", [(2, 64), (2, 1024), (4, 256), (8, 128), (64, 16)])
+def test_batched(B, T):
+    w = Workload("b", H=4, B=B, T=T, state_in="fp32", state_out="fp32", seed=B)
+    x = make_inputs(w)
+    out, fin = run_gpu(x, torch.float32)
+    check_against_f64(x, out, fin, f"B{B}xT{T}")
+
+
+@pytest.mark.parametrize("regime", ["g=-8", "g=8", "g=U(-8,8)", "bias=+-8", "lb=-2", "H32"])
+def test_gate_regimes(regime):
+    """Gate sweeps in the spirit of the reference's accuracy tests (tests/test_fwd.py:45-68)."""
+    H = 32 if regime == "H32" else 2
+    w = Workload("g", H=H, B=1, T=512, state_in="fp32", state_out="fp32", state_std=1.0, seed=7,
+                 lower_bound=-2.0 if regime == "lb=-2" else -5.0)
+    x = make_inputs(w)
+    gen = torch.Generator().manual_seed(3)
+    if regime == "g=-8":
+        x["g"] = torch.full_like(x["g"], -8.0)
+    elif regime == "g=8":
+        x["g"] = torch.full_like(x["g"], 8.0)
+    elif regime == "g=U(-8,8)":
+        x["g"] = (torch.rand(x["g"].shape, generator=gen) * 16 - 8).bfloat16()
+    elif regime == "bias=+-8":
+        x["g"] = torch.zeros_like(x["g"])
+        x["dt_bias"] = torch.where(torch.rand(x["dt_bias"].shape, generator=gen) < 0.5, -8.0, 8.0)
+    if regime in ("g=-8", "g=8", "g=U(-8,8)", "bias=+-8"):
+        x["A_log"] = torch.zeros_like(x["A_log"])
+    out, fin = run_gpu(x, torch.float32)
+    check_against_f64(x, out, fin, regime)
+
+
+def test_state_handoff_split_equals_unsplit():
+    """Prefill 160 tokens at once, or 96 then 64 with final_state fed back as initial_state."""
+    w = Workload("s", H=2, B=1, T=160, state_in="fp32", state_out="fp32", seed=21)
+    x = make_inputs(w)
+    o_all, s_all = run_gpu(x, torch.float32)
+    cut = lambda a, b: {k: (v[:, a:b].contiguous() if k in ("q", "k", "v", "g", "beta") else v) for k, v in x.items()}
+    xa = cut(0, 96)
+    o1, s1 = run_gpu(xa, torch.float32)
+    xb = cut(96, 160)
+    xb["initial_state"] = s1
+    o2, s2 = run_gpu(xb, torch.float32)
+    assert max_abs(torch.cat([o1, o2], 1), o_all) <= 2e-2
+    assert rel_fro(s2, s_all) <= 2e-3
+
+
+def test_deterministic_and_tail_rows_untouched():
+    w = Workload("d", H=2, seq_lens=[45, 3], state_in="bf16", state_out="bf16", seed=4)
+    x = make_inputs(w)
+    o1, s1 = run_gpu(x, torch.bfloat16)
+    o2, s2 = run_gpu(x, torch.bfloat16)
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16)) and torch.equal(s1.view(torch.int16), s2.view(torch.int16))
+
+
+def test_bad_cu_seqlens_reports_status_instead_of_faulting():
+    w = Workload("c", H=2, seq_lens=[40, 24], seed=9)
+    x = make_inputs(w)
+    x["cu_seqlens"] = torch.tensor([0, 50, 40], dtype=torch.int64)     # not monotone
+    xc = to_cuda(x)
+    ws = torch.empty(F.get_workspace_size(64, 2, 2), dtype=torch.uint8, device="cuda")
+    flash_kda.fwd(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], x["scale"], xc["out"], xc["A_log"],
+                  xc["dt_bias"], x["lower_bound"], cu_seqlens=xc["cu_seqlens"], workspace=ws)
+    with pytest.raises(RuntimeError, match="cu_seqlens"):
+        F.read_status(ws)
+
+
+def test_argument_errors_raise_before_launch():
+    w = Workload("e", H=2, B=1, T=32, seed=1)
+    xc = to_cuda(make_inputs(w))
+    call = lambda **kw: flash_kda.fwd(*[kw.get(n, xc[n]) for n in ("q", "k", "v", "g", "beta", "scale", "out", "A_log",
+                                                                    "dt_bias", "lower_bound")],
+                                      **{n: kw[n] for n in ("initial_state", "final_state", "cu_seqlens") if n in kw})
+    with pytest.raises(RuntimeError, match="q must be bfloat16"):
+        call(q=xc["q"].float())
+    with pytest.raises(RuntimeError, match="contiguous"):
+        call(k=xc["k"].transpose(1, 2))
+    with pytest.raises(RuntimeError, match="A_log must be"):
+        call(A_log=xc["A_log"][:1])
+    with pytest.raises(RuntimeError, match="same dtype"):
+        call(initial_state=torch.zeros(1, 2, 128, 128, device="cuda"),
+             final_state=torch.zeros(1, 2, 128, 128, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match=r"\[N, H, D, D\]"):
+        call(final_state=torch.zeros(2, 2, 128, 128, device="cuda"))
+    with pytest.raises(RuntimeError, match="int64"):
+        call(cu_seqlens=torch.tensor([0, 32], dtype=torch.int32, device="cuda"))
+    with pytest.raises(RuntimeError, match="D == 128"):
+        z = torch.zeros(1, 32, 2, 64, dtype=torch.bfloat16, device="cuda")
+        flash_kda.fwd(z, z, z, z, xc["beta"], 0.1, z.clone(), xc["A_log"], torch.zeros(2, 64, device="cuda"), -5.0)
+
+
+def test_baseline_config0_through_default_allocation():
+    """BASELINE config 0 (B=1, T=1024, H=4, fp32 final state) with the per-call workspace
+    allocation of the plain `flash_kda.fwd` signature."""
+    x = make_inputs(baseline_workload(0))
+    xc = to_cuda(x)
+    out = torch.empty_like(xc["v"])
+    fin = torch.empty(1, 4, 128, 128, device="cuda")
+    flash_kda.fwd(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], x["scale"], out, A_log=xc["A_log"],
+                  dt_bias=xc["dt_bias"], lower_bound=x["lower_bound"], final_state=fin)
+    torch.cuda.synchronize()
+    check_against_f64(x, out.cpu(), fin.cpu(), "C0")

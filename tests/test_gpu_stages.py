@@ -1,0 +1,89 @@
+"""GPU: the building blocks one at a time -- tcgen05 descriptor flavours, the prologue kernel,
+and the prepare kernel's operand records against the fp64 chunk operands of the oracle."""
+import math
+
+import pytest
+import torch
+
+import flashkda_b200 as F
+import oracle
+from flashkda_b200.workloads import Workload, make_inputs
+from helpers import decode_record, to_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("reps", [1, 2])
+def test_umma_descriptor_flavours(mode, reps):
+    g = torch.Generator().manual_seed(mode)
+    ka = 128 if mode == 0 else 32
+    A = torch.randn(128, ka, generator=g).bfloat16()
+    B = (torch.randn(32, 128, generator=g) if mode == 1 else torch.randn(32, ka, generator=g)).bfloat16()
+    ref = A.double() @ (B.double() if mode == 1 else B.double().t())
+    D = F.selftest_umma(A.cuda(), B.cuda(), mode, reps).cpu().double()
+    err = (D - reps * ref).abs().max().item()
+    assert err < 1e-3 * max(1.0, ref.abs().max().item()), \
+        f"mode {mode} reps {reps}: max err {err}; D[0,:4]={D[0,:4].tolist()} ref[0,:4]={(reps*ref)[0,:4].tolist()}"
+
+
+def test_prologue_kernel():
+    w = Workload("p", H=3, B=2, T=37, seed=5)
+    x = make_inputs(w)
+    xc = to_cuda(x)
+    qn, kn, gate, bact = F.prologue(xc["q"], xc["k"], xc["g"], xc["beta"], xc["A_log"], xc["dt_bias"], -5.0)
+    torch.cuda.synchronize()
+    q64, k64 = x["q"].double(), x["k"].double()
+    qr = q64 * torch.rsqrt((q64 * q64).sum(-1, keepdim=True) + 1e-6)
+    kr = k64 * torch.rsqrt((k64 * k64).sum(-1, keepdim=True) + 1e-6)
+    gr = -5.0 * math.log2(math.e) * torch.sigmoid(
+        torch.exp(x["A_log"].double()).view(1, 1, -1, 1) * (x["g"].double() + x["dt_bias"].double()))
+    br = torch.sigmoid(x["beta"].double())
+    assert (qn.cpu().double() - qr).abs().max() < 4e-3       # bf16 rounding of values <= 1
+    assert (kn.cpu().double() - kr).abs().max() < 4e-3
+    assert (gate.cpu().double() - gr).abs().max() < 8e-3     # tanh.approx: ~2^-11 relative on |g| <= 7.2
+    assert (bact.cpu().double() - br).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("case", ["fixed", "varlen", "strong_decay"])
+def test_prepare_records_match_fp64_operands(case):
+    if case == "fixed":
+        w = Workload("f", H=2, B=2, T=80, seed=11)
+    elif case == "varlen":
+        w = Workload("v", H=2, seq_lens=[17, 33, 64, 5], seed=12)
+    else:
+        w = Workload("s", H=2, B=1, T=64, seed=13)
+    x = make_inputs(w)
+    if case == "strong_decay":      # push the gate to its floor: g large, A_log large
+        x["g"] = torch.full_like(x["g"], 8.0)
+        x["A_log"] = torch.full_like(x["A_log"], 2.0)
+    xc = to_cuda(x)
+    ws = F.prepare(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], xc["scale"], xc["out"], xc["A_log"],
+                   xc["dt_bias"], xc["lower_bound"], cu_seqlens=xc["cu_seqlens"])
+    assert F.read_status(ws) == 0
+    ws = ws.cpu()
+    B, T = x["q"].shape[:2]
+    T_total, H, N = B * T, w.H, w.N
+    rec_off, rec_bytes, per_head = F.workspace_layout(T_total, H, N, x["cu_seqlens"] is not None, T)
+    lens = w.seq_lens if w.seq_lens is not None else [w.T] * w.B
+    flat = {k: x[k].reshape(1, T_total, *x[k].shape[2:]).contiguous() for k in ("q", "k", "v", "g", "beta")}
+    worst = {}
+    gc, t_seq = 0, 0
+    for L in lens:
+        for t0 in range(0, L, 32):
+            n = min(32, L - t0)
+            for h in range(H):
+                o = rec_off + (h * per_head + gc) * rec_bytes
+                got = decode_record(ws[o:o + rec_bytes])
+                exp = oracle.chunk_operands(flat["q"], flat["k"], flat["v"], flat["g"], flat["beta"], x["scale"],
+                                            x["A_log"], x["dt_bias"], x["lower_bound"], h, t_seq + t0, n, 32)
+                for key, e in (("wp", exp["wp"]), ("qp", exp["qpp"]), ("kr", exp["kr"]), ("up", exp["up"]),
+                               ("mqk", exp["mqk"]), ("ec", exp["ec"])):
+                    err = (got[key] - e).abs().max().item() / max(e.abs().max().item(), 1e-3)
+                    worst[key] = max(worst.get(key, 0.0), err)
+            gc += 1
+        t_seq += L
+    print("prepare", case, {k: f"{v:.2e}" for k, v in worst.items()})
+    # bf16 operands: relative to the tile's largest entry; products of bf16-rounded factors ~1e-2
+    assert worst["qp"] < 6e-3 and worst["kr"] < 6e-3 and worst["ec"] < 2e-3, worst
+    assert worst["mqk"] < 2e-2 and worst["wp"] < 3e-2 and worst["up"] < 3e-2, worst

@@ -1,0 +1,95 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports what include/fkda.h
+declares, sizes are sane, and argument errors surface as RuntimeError before any launch."""
+import ctypes
+import math
+import os
+import re
+
+import pytest
+import torch
+
+import flash_kda
+import flashkda_b200 as F
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "fkda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fkda_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_functions()
+    assert "fkda_fwd" in names and "fkda_get_workspace_size" in names and len(names) >= 8
+    L = ctypes.CDLL(F.lib_path())
+    for n in names:
+        assert hasattr(L, n), f"libfkda.so does not export {n}"
+
+
+def test_params_struct_matches_header_field_order():
+    text = open(os.path.join(ROOT, "include", "fkda.h")).read()
+    body = text[text.index("typedef struct fkda_fwd_params {"):text.index("} fkda_fwd_params;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = re.findall(r"\b([A-Za-z_]+);", body)
+    from flashkda_b200._binding import FwdParams
+    assert fields == [f[0] for f in FwdParams._fields_]
+
+
+def test_workspace_size():
+    a = F.get_workspace_size(32768, 32, 4)
+    assert a == 256 + 256 + (32768 // 32 + 4) * 32 * 35328
+    assert F.get_workspace_size(0, 1, 1) > 0
+    assert F.get_workspace_size(64, 2, 1) < F.get_workspace_size(128, 2, 1)
+    with pytest.raises(RuntimeError):
+        F.get_workspace_size(16, 0, 1)
+    off, rec, per_head = F.workspace_layout(8192 * 4, 32, 4, 0, 8192)
+    assert rec == 35328 and per_head == 4 * 256 and off % 256 == 0
+    off, rec, per_head = F.workspace_layout(100, 2, 3, 1, 0)
+    assert per_head == 100 // 32 + 3
+
+
+def test_drop_in_module_surface():
+    import inspect
+    sig = inspect.signature(flash_kda.fwd)
+    names = list(sig.parameters)
+    assert names[:13] == ["q", "k", "v", "g", "beta", "scale", "out", "A_log", "dt_bias", "lower_bound",
+                          "initial_state", "final_state", "cu_seqlens"]
+    for n in ("initial_state", "final_state", "cu_seqlens"):
+        assert sig.parameters[n].default is None
+    assert callable(flash_kda.get_workspace_size)
+
+
+def _cpu_args(B=1, T=16, H=2):
+    z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt)
+    return dict(q=z(B, T, H, 128), k=z(B, T, H, 128), v=z(B, T, H, 128), g=z(B, T, H, 128), beta=z(B, T, H),
+                scale=1 / math.sqrt(128), out=z(B, T, H, 128), A_log=z(H, dt=torch.float32),
+                dt_bias=z(H, 128, dt=torch.float32), lower_bound=-5.0)
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    # no CPU path: the product must refuse, not fall back
+    with pytest.raises(RuntimeError, match="CUDA"):
+        flash_kda.fwd(**_cpu_args())
+
+
+def test_c_abi_rejects_bad_params_without_a_gpu():
+    from flashkda_b200._binding import FwdParams
+    L = F.lib()
+    p = FwdParams()
+    assert L.fkda_fwd(ctypes.byref(p), None) == -1 and "non-NULL" in F.last_error()
+    assert L.fkda_fwd(None, None) == -1
+    # plausible pointers but inconsistent sizes: still rejected before any CUDA call
+    p = FwdParams(*([0x1000] * 8), None, None, 0x2000, 0x3000, 1 << 40, 2, 16, 2, 2, 0.1, -5.0, 0, 0)
+    assert L.fkda_fwd(ctypes.byref(p), None) == -1 and "B must be 1" in F.last_error()
+    p = FwdParams(*([0x1000] * 8), None, None, None, 0x3000, 1 << 40, 2, 16, 2, 3, 0.1, -5.0, 0, 0)
+    assert L.fkda_fwd(ctypes.byref(p), None) == -1 and "N must equal B" in F.last_error()
+    p = FwdParams(*([0x1000] * 8), None, None, None, 0x3000, 1 << 40, 2, 16, 2, 2, 0.1, -7.0, 0, 0)
+    assert L.fkda_fwd(ctypes.byref(p), None) == -1 and "lower_bound" in F.last_error()
+    p = FwdParams(*([0x1000] * 8), 0x5000, None, None, 0x3000, 1 << 40, 2, 16, 2, 2, 0.1, -5.0, 0, 0)
+    assert L.fkda_fwd(ctypes.byref(p), None) == -1 and "state_dtype" in F.last_error()
+    p = FwdParams(*([0x1000] * 8), None, None, None, 0x3000, 1024, 2, 16, 2, 2, 0.1, -5.0, 0, 0)
+    assert L.fkda_fwd(ctypes.byref(p), None) == -2 and "workspace" in F.last_error()
+    p = FwdParams(0x1001, *([0x1000] * 7), None, None, None, 0x3000, 1 << 40, 2, 16, 2, 2, 0.1, -5.0, 0, 0)
+    assert L.fkda_fwd(ctypes.byref(p), None) == -1 and "aligned" in F.last_error()
