@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of `flash_kda.fwd` (Kimi Delta Attention prefill) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 1|2|3|4] [--shard seq|head]
+    python bench.py --impl reference            # the CPU restatement of the reference on host cores
+
+One "step" is one `flash_kda.fwd` call over the whole synthetic batch.  At N=1 the workload is
+the configuration the headline metric is quoted on: fixed-length prefill B=4, T=8192, H=32,
+K=V=128, fp32 initial and final state.  With N ranks (one process per GPU, launched by
+torch.distributed.run) every rank runs that workload on its own 4 sequences of a global batch
+of 4N sequences: the operator has no cross-sequence or cross-head term, so ranks exchange
+nothing on the data path (NCCL carries only the timing reduction) and the run is weak scaling.
+`--shard head` instead splits the heads of the fixed N=1 workload over the ranks (strong scaling).
+
+The JSON line carries:
+  value        tokens/s over all ranks, inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e          tokens/s through the same public call with HOST (pinned) buffers: host->device
+               copies of q,k,v,g,beta,state and device->host copies of out and final_state
+               inside the timed region
+  roofline     dominant kernel: algorithmic bytes of the call / that kernel's mean duration,
+               against the measured HBM copy bandwidth; `roofline_call` is the same for the
+               whole call (all kernels)
+  cpu_baseline the oracle's C port of the reference algorithm on this box's host cores, on a
+               bounded sample of the same workload
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from flashkda_b200.workloads import (Workload, algorithmic_bytes, baseline_workload,  # noqa: E402
+                                     make_inputs)
+
+METRIC = "flash_kda.fwd tokens/s at H=32,K=V=128"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.samples, self.proc, self.thread, self.gpu = [], None, None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), [p.strip() for p in line.split(",")]))
+
+    def stop(self, t_begin, t_end):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.samples if t_begin - 0.05 <= t <= t_end + 0.15 and len(r) >= 6]
+        if not rows:
+            rows = [r for _, r in self.samples if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": int(rows[0][1]) if rows[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def cpu_baseline_sample(w: Workload, target_s=12.0, nthreads=0):
+    """Times the oracle's C port of the reference's chunk-16 algorithm (oracle/kda_oracle.c,
+    restating tests/torch_ref.py of the reference) on the first tokens of sequence 0, all heads,
+    of the same workload.  Returns (tokens_per_s, cores, description)."""
+    import oracle
+    cores = oracle.max_threads() if nthreads <= 0 else nthreads
+
+    def run(B, T):
+        ww = Workload("cpu_sample", H=w.H, B=B, T=T, lower_bound=w.lower_bound, state_in=w.state_in,
+                      state_out=w.state_out, state_std=w.state_std, seed=w.seed)
+        x = make_inputs(ww)
+        fin_dtype = None if x["final_state"] is None else x["final_state"].dtype
+        t0 = time.perf_counter()
+        oracle.chunk16(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["A_log"], x["dt_bias"],
+                       x["lower_bound"], initial_state=x["initial_state"], final_state_dtype=fin_dtype,
+                       nthreads=cores)
+        return time.perf_counter() - t0
+
+    run(1, 64)                              # load the library, warm the threads
+    pilot_T = 512
+    pilot = run(1, pilot_T)
+    want = pilot_T * target_s / max(pilot, 1e-6)        # tokens that would take target_s
+    T_seq = w.T if w.seq_lens is None else 8192
+    B_max = w.B if w.seq_lens is None else 4
+    if want <= T_seq:
+        B, T = 1, int(max(256, want) // 256 * 256)
+    else:
+        B, T = int(min(B_max, want // T_seq)), T_seq     # at most the whole workload
+    dt = run(B, T)
+    return B * T / dt, cores, f"{B} x {T} tokens (first sequences of the workload), all {w.H} heads, {w.state_in or 'no'} state in"
+
+
+def reference_arm(args, w, rank):
+    """`--impl reference`: the reference's algorithm on the host cores (it has no CPU
+    implementation of its own -- tests/torch_ref.py is GPU-only Python -- so this is the C port in
+    oracle/, kind "port"), all host threads, on a bounded sample per step."""
+    if rank != 0:
+        return
+    per_step = max(2.0, 40.0 / max(1, args.steps + args.warmup))
+    vals = []
+    desc, cores = "", 1
+    for i in range(args.warmup + args.steps):
+        v, cores, desc = cpu_baseline_sample(w, target_s=per_step)
+        if i >= args.warmup:
+            vals.append(v)
+    value = sum(vals) / len(vals)
+    sample_T = int(desc.split()[0]) * int(desc.split()[2])
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sample_T / value,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": w.name, "B": w.B, "T": w.T, "H": w.H, "state": w.state_in},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_cuda(fn, steps, stream):
+    """Mean milliseconds per call of `fn` over `steps` back-to-back calls, CUDA events on `stream`."""
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record(stream)
+    for _ in range(steps):
+        fn()
+    b.record(stream)
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="fkda", choices=["fkda", "reference"])
+    ap.add_argument("--config", type=int, default=1, help="BASELINE configuration index (1..4)")
+    ap.add_argument("--shard", default="seq", choices=["seq", "head"])
+    ap.add_argument("--shape", default=None, help="B,T,H override of the fixed-length workload (profiling on a small case)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "fkda" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    w = baseline_workload(args.config)
+    if args.shape:
+        b_, t_, h_ = (int(v) for v in args.shape.split(","))
+        w = Workload(f"custom_B{b_}_T{t_}_H{h_}", H=h_, B=b_, T=t_, lower_bound=w.lower_bound, state_in=w.state_in,
+                     state_out=w.state_out, state_std=w.state_std)
+
+    if args.impl == "reference":
+        reference_arm(args, w, rank)
+        return
+
+    import flash_kda
+    import flashkda_b200 as F
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: flash_kda has no CPU path")
+    F.lib()   # fail loudly if the CUDA library is missing
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- this rank's shard ------------------------------------------------------------------------
+    heads = None
+    if args.shard == "head" and world > 1:
+        per = w.H // world
+        heads = range(rank * per, (rank + 1) * per)
+        w_local = w
+        tokens_global = w.total_tokens
+        scaling = "strong"
+    else:
+        w_local = Workload(w.name, H=w.H, B=w.B, T=w.T, seq_lens=w.seq_lens, lower_bound=w.lower_bound,
+                           state_in=w.state_in, state_out=w.state_out, state_std=w.state_std, seed=w.seed + rank)
+        tokens_global = w.total_tokens * world
+        scaling = "weak"
+    x = make_inputs(w_local, device=dev, heads=heads)
+    H_local = x["q"].shape[2]
+    B, T = x["q"].shape[:2]
+    N = w.N
+    ws = torch.empty(F.get_workspace_size(B * T, H_local, N), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def call():
+        flash_kda.fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["out"], x["A_log"], x["dt_bias"],
+                      x["lower_bound"], initial_state=x["initial_state"], final_state=x["final_state"],
+                      cu_seqlens=x["cu_seqlens"], workspace=ws)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        call()
+    assert F.read_status(ws) == 0
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    t_begin = time.time()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        call()
+    ev1.record(stream)
+    barrier()
+    t_end = time.time()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+    assert F.read_status(ws) == 0
+
+    # ---- per-kernel durations (same stream, CUDA events), for the roofline of the dominant kernel ----
+    kw = dict(initial_state=x["initial_state"], final_state=x["final_state"], cu_seqlens=x["cu_seqlens"], workspace=ws)
+    pos = (x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["out"], x["A_log"], x["dt_bias"], x["lower_bound"])
+    ksteps = max(3, min(args.steps, 10))
+    ms_prepare = time_cuda(lambda: F.prepare(*pos, **kw), ksteps, stream)
+    ms_scan = time_cuda(lambda: F.scan(*pos, **kw), ksteps, stream)
+
+    # ---- end to end from host buffers ----------------------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        names_in = ["q", "k", "v", "g", "beta"] + (["initial_state"] if x["initial_state"] is not None else [])
+        names_out = ["out"] + (["final_state"] if x["final_state"] is not None else [])
+        host = {n: x[n].cpu().pin_memory() for n in names_in + names_out}
+        h2d = sum(host[n].numel() * host[n].element_size() for n in names_in)
+        d2h = sum(host[n].numel() * host[n].element_size() for n in names_out)
+
+        def e2e_step():
+            for n in names_in:
+                x[n].copy_(host[n], non_blocking=True)
+            call()
+            for n in names_out:
+                host[n].copy_(x[n], non_blocking=True)
+
+        e_steps = max(2, min(args.steps, 5))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(e_steps):
+            e2e_step()
+        b.record(stream)
+        barrier()
+        e2e = (a.elapsed_time(b) / e_steps, h2d, d2h)
+
+    # ---- reduce over ranks: max time -------------------------------------------------------------------
+    vals = torch.tensor([ms, ms_prepare, ms_scan, e2e[0] if e2e else 0.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms, ms_prepare, ms_scan, ms_e2e = vals.tolist()
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        alg = algorithmic_bytes(B * T, H_local, N, w.state_in, w.state_out)      # per rank, per call
+        dom_name, dom_ms = ("scan", ms_scan) if ms_scan >= ms_prepare else ("prepare", ms_prepare)
+        ach = alg / (dom_ms * 1e-3) / 1e9
+        ach_call = alg / (ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": tokens_global / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w.name, "B_per_gpu": B, "T": T, "H_per_gpu": H_local, "K": 128, "V": 128,
+                       "N_per_gpu": N, "state": f"{w.state_in} in / {w.state_out} out", "lower_bound": w.lower_bound,
+                       "sharding": f"{args.shard} x{world}, no data-path collective",
+                       "l2": "inputs + outputs per call (%.2f GB) larger than the 126 MB L2; no explicit flush" % (alg / 1e9),
+                       "chunk": 32},
+            "gpu_launches": (2 + (1 if x["cu_seqlens"] is not None else 0)) * args.steps,
+            "kernels_ms": {"prepare": ms_prepare, "scan": ms_scan},
+            "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": ach, "peak": peak, "unit": "GB/s",
+                         "frac": ach / peak, "peak_source": peak_kind, "algorithmic_bytes": alg,
+                         "traffic": TRAFFIC_BYTES_PER_TOKEN_HEAD.get(dom_name) and
+                         TRAFFIC_BYTES_PER_TOKEN_HEAD[dom_name] * B * T * H_local},
+            "roofline_call": {"achieved": ach_call, "peak": peak, "unit": "GB/s", "frac": ach_call / peak},
+            "clocks": clocks,
+        }
+        if e2e:
+            line["e2e"] = {"value": tokens_global / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                           "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2]}
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, desc = cpu_baseline_sample(w)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes per token-head of each kernel, from ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum per launch / token-heads of the captured case).
+TRAFFIC_BYTES_PER_TOKEN_HEAD = {"prepare": None, "scan": None}
+
+if __name__ == "__main__":
+    main()
