@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) scan_simt_kernel(const ScanParams p) {
         w = fmaf(rec_bf(rec, kRecWP + core_off(tok, kk, kD)), s, w);
         oo = fmaf(rec_bf(rec, kRecQP + core_off(tok, kk, kD)), s, oo);
       }
-      U[tok * kD + v] = rec_bf(rec, kRecUP + tok * 256 + v * 2) - w;
+      U[tok * kD + v] = rec_bf(rec, kRecUP + core_off(v, tok, kChunk)) - w;
       o[t] = oo;
     }
     __syncthreads();

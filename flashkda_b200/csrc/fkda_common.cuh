@@ -17,18 +17,19 @@ constexpr float kLog2e = 1.4426950408889634f;
 // All bf16 matrices use the core-matrix layout below, so that a record is at the same time
 // (a) what ldmatrix wants in the prepare kernel and (b) a no-swizzle tcgen05 operand tile that
 // the scan kernel can bring into shared memory with one bulk copy.
-//   WP  [32 tok][128 k]  T diag(beta) k+      (k+ = khat * decay from chunk start)
-//   QP  [32 tok][128 k]  qhat * decay from chunk start * scale
 //   KR  [32 tok][128 k]  khat * decay to chunk end
-//   UP  [32 tok][128 v]  T diag(beta) v        (row-major, not an MMA operand)
 //   MQK [32 tok][32 tok] tril(q+ k-^T)
 //   E   [128] fp32       whole-chunk decay per channel
-constexpr int kRecWP = 0;
-constexpr int kRecQP = 8192;
-constexpr int kRecKR = 16384;
-constexpr int kRecUP = 24576;
-constexpr int kRecMQK = 32768;
-constexpr int kRecE = 34816;
+//   WP  [32 tok][128 k]  T diag(beta) k+      (k+ = khat * decay from chunk start)
+//   QP  [32 tok][128 k]  qhat * decay from chunk start * scale   (directly after WP: the two
+//                        form one [64][128] operand tile)
+//   UP  [128 v][32 tok]  (T diag(beta) v)^T   (core layout; read row-wise by the scan's U epilogue)
+constexpr int kRecKR = 0;
+constexpr int kRecMQK = 8192;
+constexpr int kRecE = 10240;
+constexpr int kRecWP = 10752;
+constexpr int kRecQP = 18944;
+constexpr int kRecUP = 27136;
 constexpr int kRecBytes = 35328;
 
 // workspace header (bytes): [0,64) status words, [256, 256+4*(N+1)) chunk prefix, records after
@@ -213,6 +214,10 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                : "r"(addr));
+}
+__device__ __forceinline__ void stsm_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
 }
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"

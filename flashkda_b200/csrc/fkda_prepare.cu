@@ -69,11 +69,13 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
 }
 
 // ---- shared-memory plan of the prepare kernel (byte offsets) --------------------------------------
+// The record under construction occupies [0, kRecBytes).  Its WP and UP regions are written last,
+// so until the intra-chunk products are done they hold three temporaries.
+constexpr int kSmKM = kRecWP;                // [32][128] k-, relative to own sub-block start   (dead after P4)
+constexpr int kSmKP1 = kRecUP;               // [16][128] k+ of sub-block 1 rel. to its own start (dead after P4)
+constexpr int kSmQP1 = kRecUP + 4096;        // [16][128] q+ of sub-block 1 rel. to its own start (dead after P4)
 constexpr int kSmKPP = kRecBytes;            // [32][128] k+ from chunk start (rows 0-15 double as sub-block operand)
-constexpr int kSmKM = kSmKPP + 8192;         // [32][128] k-, relative to own sub-block start
-constexpr int kSmKP1 = kSmKM + 8192;         // [16][128] k+ of sub-block 1 relative to its own start
-constexpr int kSmQP1 = kSmKP1 + 4096;        // [16][128] q+ of sub-block 1 relative to its own start
-constexpr int kSmKR0 = kSmQP1 + 4096;        // [16][128] k of sub-block 0 decayed to the sub-block end
+constexpr int kSmKR0 = kSmKPP + 8192;        // [16][128] k of sub-block 0 decayed to the sub-block end
 constexpr int kSmV = kSmKR0 + 4096;          // [32][128] v
 constexpr int kSmTB = kSmV + 8192;           // [32][32] bf16 T diag(beta)
 constexpr int kSmA = kSmTB + 2048;           // [32][33] fp32 A
@@ -83,6 +85,7 @@ constexpr int kSmTot = kSmX + 1088;          // [2][128] fp32 sub-block log2 dec
 constexpr int kSmSsq = kSmTot + 1024;        // [2][32][4] fp32 partial sums of squares
 constexpr int kSmBeta = kSmSsq + 1024;       // [32] fp32 sigmoid(beta)
 constexpr int kPrepSmemBytes = kSmBeta + 128;
+static_assert(kPrepSmemBytes * 3 + 3 * 1024 <= 228 * 1024, "three CTAs per SM");
 
 __device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
   f[0] = bf_lo(w.x); f[1] = bf_hi(w.x); f[2] = bf_lo(w.y); f[3] = bf_hi(w.y);
@@ -112,7 +115,7 @@ __device__ __forceinline__ void block16_product(uint32_t a_base, uint32_t b_base
   }
 }
 
-__global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
+__global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.y;
@@ -156,9 +159,11 @@ __global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
   float* s_T = reinterpret_cast<float*>(smem + kSmT);
   float* s_X = reinterpret_cast<float*>(smem + kSmX);
 
-  // ---- P1: loads, partial sums of squares, v tile, beta -------------------------------------------
-  uint4 qw[2], kw[2], gw[2];
+  // ---- P1: loads, partial sums of squares, v tile, beta, gate and its in-sub-block running sum ------
+  uint4 qw[2], kw[2];
+  float G[2][8];      // log2 cumulative decay relative to the sub-block start
   {
+    uint4 gw[2];
     const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
@@ -171,75 +176,56 @@ __global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
       const uint4 vw = valid ? __ldg(reinterpret_cast<const uint4*>(p.v + off)) : z;
       *reinterpret_cast<uint4*>(smem + kSmV + core_off(row, 8 * j, kD)) = vw;
     }
-  }
-  if (tid < kChunk) {
-    float b = 0.f;
-    if (tid < len) b = sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(t0 + tid) * p.H + h]));
-    s_beta[tid] = b;
-  }
+    if (tid < kChunk) {
+      float b = 0.f;
+      if (tid < len) b = sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(t0 + tid) * p.H + h]));
+      s_beta[tid] = b;
+    }
+    // gate: gamma = gate_scale * sigmoid(a (g + bias)) = hgs * tanh(ha g + ha bias) + hgs
+    const float ha = 0.5f * ex2f(__ldg(p.A_log + h) * kLog2e);
+    const float hgs = 0.5f * p.gate_scale;
+    float hab[8];
+    {
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
+      const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+      hab[0] = ha * b0.x; hab[1] = ha * b0.y; hab[2] = ha * b0.z; hab[3] = ha * b0.w;
+      hab[4] = ha * b1.x; hab[5] = ha * b1.y; hab[6] = ha * b1.z; hab[7] = ha * b1.w;
+    }
 #pragma unroll
-  for (int hf = 0; hf < 2; ++hf) {
-    float f[8], sq = 0.f, sk = 0.f;
-    unpack8(qw[hf], f);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sq = fmaf(f[i], f[i], sq);
-    unpack8(kw[hf], f);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sk = fmaf(f[i], f[i], sk);
-    // lanes sharing r8 inside the warp hold 4 different column groups of the same row
-    sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-    sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-    sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-    sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-    if (lane < 8) {
+    for (int hf = 0; hf < 2; ++hf) {
       const int row = hf ? row1 : row0;
-      s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
-      s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
-    }
-  }
-  __syncthreads();
-
-  // ---- P2: norms, gate, in-sub-block cumulative sum, sub-block-relative operands ----------------------
-  const float a_gate = ex2f(__ldg(p.A_log + h) * kLog2e);
-  float bias[8];
-  {
-    const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
-    const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
-    bias[0] = b0.x; bias[1] = b0.y; bias[2] = b0.z; bias[3] = b0.w;
-    bias[4] = b1.x; bias[5] = b1.y; bias[6] = b1.z; bias[7] = b1.w;
-  }
-  float G[2][8];      // log2 cumulative decay relative to the sub-block start
-  float kh[2][8];     // normalised k
-  float qh[2][8];     // normalised q * scale
+      float f[8], sq = 0.f, sk = 0.f;
+      unpack8(qw[hf], f);
 #pragma unroll
-  for (int hf = 0; hf < 2; ++hf) {
-    const int row = hf ? row1 : row0;
-    const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
-    const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
-    const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
-    const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
-    float f[8];
-    unpack8(qw[hf], f);
+      for (int i = 0; i < 8; ++i) sq = fmaf(f[i], f[i], sq);
+      unpack8(kw[hf], f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qh[hf][i] = f[i] * rq;
-    unpack8(kw[hf], f);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) kh[hf][i] = f[i] * rk;
-    unpack8(gw[hf], f);
-    const bool valid = row < len;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float x = valid ? p.gate_scale * sigmoid_fast(a_gate * (f[i] + bias[i])) : 0.f;
-      // inclusive scan over the 8 rows held by the 8 lanes of this group
-#pragma unroll
-      for (int d = 1; d < 8; d <<= 1) {
-        const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
-        if (r8 >= d) x += y;
+      for (int i = 0; i < 8; ++i) sk = fmaf(f[i], f[i], sk);
+      // lanes sharing r8 inside the warp hold 4 different column groups of the same row
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+      if (lane < 8) {
+        s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
+        s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
       }
-      G[hf][i] = x;
+      unpack8(gw[hf], f);
+      const bool valid = row < len;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float x = valid ? fmaf(tanh_approx(fmaf(f[i], ha, hab[i])), hgs, hgs) : 0.f;
+        // inclusive scan over the 8 rows held by the 8 lanes of this group
+#pragma unroll
+        for (int d = 1; d < 8; d <<= 1) {
+          const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
+          if (r8 >= d) x += y;
+        }
+        G[hf][i] = x;
+      }
     }
   }
-  float tot[8];       // log2 decay of the whole sub-block
+  float tot[8];       // log2 decay of this thread's whole sub-block
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const float first_half = __shfl_sync(0xffffffffu, G[0][i], 7, 8);
@@ -250,69 +236,70 @@ __global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
     *reinterpret_cast<float4*>(s_tot + sb * kD + 8 * j) = make_float4(tot[0], tot[1], tot[2], tot[3]);
     *reinterpret_cast<float4*>(s_tot + sb * kD + 8 * j + 4) = make_float4(tot[4], tot[5], tot[6], tot[7]);
   }
-  float khp[2][8], khr[2][8], qhp[2][8];
+  __syncthreads();
+
+  // ---- P2: norms and every decayed operand ------------------------------------------------------------
   {
-    float esb[8];
+    // per-channel factors: fa = 2^(own sub-block total), fb = 2^(other sub-block total)
+    float fa[8], fb[8], fab[8];
+    {
+      const float4 t0v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j);
+      const float4 t1v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j + 4);
+      const float to[8] = {t0v.x, t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) esb[i] = ex2f(tot[i]);
+      for (int i = 0; i < 8; ++i) {
+        fa[i] = ex2f(tot[i]);
+        fb[i] = ex2f(to[i]);
+        fab[i] = fa[i] * fb[i];
+      }
+      if (sb == 0 && r8 == 0) {
+        float* e = reinterpret_cast<float*>(smem + kRecE) + 8 * j;
+        *reinterpret_cast<float4*>(e) = make_float4(ex2f(tot[0] + to[0]), ex2f(tot[1] + to[1]), ex2f(tot[2] + to[2]), ex2f(tot[3] + to[3]));
+        *reinterpret_cast<float4*>(e + 4) = make_float4(ex2f(tot[4] + to[4]), ex2f(tot[5] + to[5]), ex2f(tot[6] + to[6]), ex2f(tot[7] + to[7]));
+      }
+    }
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       const int row = hf ? row1 : row0;      // chunk row
       const int lrow = row - sb * 16;        // row inside the sub-block
-      float km[8];
+      const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
+      const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
+      const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
+      const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
+      float qf[8], kf[8], kp[8], qp[8], km[8], t[8];
+      unpack8(qw[hf], qf);
+      unpack8(kw[hf], kf);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float pw = ex2f(G[hf][i]), ipw = ex2f(-G[hf][i]);
-        khp[hf][i] = kh[hf][i] * pw;
-        qhp[hf][i] = qh[hf][i] * pw;
-        km[i] = kh[hf][i] * ipw;
-        khr[hf][i] = km[i] * esb[i];
+        const float kh = kf[i] * rk, qh = qf[i] * rq;
+        kp[i] = kh * pw;       // decayed from the sub-block start (<= |khat|)
+        qp[i] = qh * pw;
+        km[i] = kh * ipw;      // inverse decay, up to 2^115 for lower_bound = -5
       }
       *reinterpret_cast<uint4*>(smem + kSmKM + core_off(row, 8 * j, kD)) = pack8(km);
       if (sb == 0) {
-        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(khp[hf]);
-        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(qhp[hf]);
-        *reinterpret_cast<uint4*>(smem + kSmKR0 + core_off(lrow, 8 * j, kD)) = pack8(khr[hf]);
+        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(kp);
+        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(qp);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = km[i] * fa[i];      // decayed to the sub-block end
+        *reinterpret_cast<uint4*>(smem + kSmKR0 + core_off(lrow, 8 * j, kD)) = pack8(t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = km[i] * fab[i];     // ... and on through sub-block 1
+        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(t);
       } else {
-        *reinterpret_cast<uint4*>(smem + kSmKP1 + core_off(lrow, 8 * j, kD)) = pack8(khp[hf]);
-        *reinterpret_cast<uint4*>(smem + kSmQP1 + core_off(lrow, 8 * j, kD)) = pack8(qhp[hf]);
-        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(khr[hf]);
+        *reinterpret_cast<uint4*>(smem + kSmKP1 + core_off(lrow, 8 * j, kD)) = pack8(kp);
+        *reinterpret_cast<uint4*>(smem + kSmQP1 + core_off(lrow, 8 * j, kD)) = pack8(qp);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = km[i] * fa[i];      // decayed to the chunk end
+        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = kp[i] * fb[i];      // decayed from the chunk start
+        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = qp[i] * fb[i];
+        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(t);
       }
-    }
-  }
-  __syncthreads();
-
-  // ---- P3: chunk-relative operands (need the other sub-block's total) ---------------------------------
-  {
-    float eo[8], to[8];
-    const float4 t0v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j);
-    const float4 t1v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j + 4);
-    to[0] = t0v.x; to[1] = t0v.y; to[2] = t0v.z; to[3] = t0v.w;
-    to[4] = t1v.x; to[5] = t1v.y; to[6] = t1v.z; to[7] = t1v.w;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) eo[i] = ex2f(to[i]);
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const int row = hf ? row1 : row0;
-      float a[8], b[8];
-      if (sb == 0) {   // decay to the chunk end = decay to sub-block end, then through sub-block 1
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] = khr[hf][i] * eo[i];
-        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(a);
-      } else {         // decay from the chunk start = through sub-block 0, then from sub-block start
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          a[i] = khp[hf][i] * eo[i];
-          b[i] = qhp[hf][i] * eo[i];
-        }
-        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(a);
-        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(b);
-      }
-    }
-    if (sb == 0 && r8 == 0) {
-      float* e = reinterpret_cast<float*>(smem + kRecE) + 8 * j;
-      *reinterpret_cast<float4*>(e) = make_float4(ex2f(tot[0] + to[0]), ex2f(tot[1] + to[1]), ex2f(tot[2] + to[2]), ex2f(tot[3] + to[3]));
-      *reinterpret_cast<float4*>(e + 4) = make_float4(ex2f(tot[4] + to[4]), ex2f(tot[5] + to[5]), ex2f(tot[6] + to[6]), ex2f(tot[7] + to[7]));
     }
   }
   __syncthreads();
@@ -403,7 +390,7 @@ __global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
   }
   __syncthreads();
   {
-    // TB = T diag(beta) as a bf16 core-layout A operand; 4 consecutive columns per thread
+    // TB = T diag(beta) as a bf16 core-layout operand; 4 consecutive columns per thread
     const int i = tid >> 3, c4 = (tid & 7) * 4;
     float t[4];
 #pragma unroll
@@ -416,11 +403,8 @@ __global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
   }
   __syncthreads();
 
-  // ---- P6: w' = TB k+ (warps 0-3), u' = TB v (warps 4-7); 32 output columns per warp ----------------------
+  // ---- P6: w' = TB k+ (warps 0-3, 32 k-columns each) ; u'^T = v^T TB^T (warps 4-7, 32 v-rows each) -----
   {
-    const bool is_u = warp >= 4;
-    const int nb = (warp & 3) * 4;           // first 8-column tile of this warp
-    const uint32_t b_arr = sbase + (is_u ? kSmV : kSmKPP);
     const int mi = lane >> 3, r = lane & 7;
     float acc[2][4][4];
 #pragma unroll
@@ -429,39 +413,64 @@ __global__ void __launch_bounds__(256, 2) prepare_kernel(const PrepParams p) {
       for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+    if (warp < 4) {
+      const int nb = warp * 4;             // first 8-column tile of this warp
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
-      uint32_t a[2][4];
+      for (int ks = 0; ks < 2; ++ks) {
+        uint32_t a[2][4];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-        ldsm_x4(sbase + kSmTB + (2 * mt + (mi & 1)) * 512 + (2 * ks + (mi >> 1)) * 128 + r * 16, a[mt][0], a[mt][1], a[mt][2],
-                a[mt][3]);
+        for (int mt = 0; mt < 2; ++mt)
+          ldsm_x4(sbase + kSmTB + (2 * mt + (mi & 1)) * 512 + (2 * ks + (mi >> 1)) * 128 + r * 16, a[mt][0], a[mt][1], a[mt][2],
+                  a[mt][3]);
 #pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        // transposed loads: matrices (token group 2ks + (mi&1), column tile nb + 2np + (mi>>1))
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4_trans(b_arr + (2 * ks + (mi & 1)) * 2048 + (nb + 2 * np + (mi >> 1)) * 128 + r * 16, b0, b1, b2, b3);
+        for (int np = 0; np < 2; ++np) {
+          // transposed loads: matrices (token group 2ks + (mi&1), column tile nb + 2np + (mi>>1))
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_trans(sbase + kSmKPP + (2 * ks + (mi & 1)) * 2048 + (nb + 2 * np + (mi >> 1)) * 128 + r * 16, b0, b1, b2, b3);
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-          mma_bf16_16816(acc[mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
-          mma_bf16_16816(acc[mt][2 * np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16_16816(acc[mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+            mma_bf16_16816(acc[mt][2 * np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+          }
         }
       }
-    }
+      // fragments -> core matrices of WP [32 tok][128 k]
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+        for (int np = 0; np < 2; ++np)
+          stsm_x4(sbase + kRecWP + (2 * mt + (mi & 1)) * 2048 + (nb + 2 * np + (mi >> 1)) * 128 + r * 16,
+                  pack_bf16(acc[mt][2 * np][0], acc[mt][2 * np][1]), pack_bf16(acc[mt][2 * np][2], acc[mt][2 * np][3]),
+                  pack_bf16(acc[mt][2 * np + 1][0], acc[mt][2 * np + 1][1]), pack_bf16(acc[mt][2 * np + 1][2], acc[mt][2 * np + 1][3]));
+    } else {
+      const int vc0 = (warp & 3) * 4;      // first 8-wide v tile of this warp's 32 rows
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int row = mt * 16 + (lane >> 2) + half * 8;
-          const int col = (nb + nt) * 8 + (lane & 3) * 2;
-          const uint32_t val = pack_bf16(acc[mt][nt][half * 2], acc[mt][nt][half * 2 + 1]);
-          if (is_u)
-            *reinterpret_cast<uint32_t*>(smem + kRecUP + row * 256 + col * 2) = val;
-          else
-            *reinterpret_cast<uint32_t*>(smem + kRecWP + core_off(row, col, kD)) = val;
+      for (int ks = 0; ks < 2; ++ks) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)     // A = v^T: transposed loads of (token group 2ks + (mi>>1), v tile vc0 + 2mt + (mi&1))
+          ldsm_x4_trans(sbase + kSmV + (2 * ks + (mi >> 1)) * 2048 + (vc0 + 2 * mt + (mi & 1)) * 128 + r * 16, a[mt][0], a[mt][1],
+                        a[mt][2], a[mt][3]);
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {   // B = TB^T: plain loads of (token group 2np + (mi>>1), k tile 2ks + (mi&1))
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(sbase + kSmTB + (2 * np + (mi >> 1)) * 512 + (2 * ks + (mi & 1)) * 128 + r * 16, b0, b1, b2, b3);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16_16816(acc[mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+            mma_bf16_16816(acc[mt][2 * np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+          }
         }
+      }
+      // fragments -> core matrices of UP [128 v][32 tok]
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int np = 0; np < 2; ++np)
+          stsm_x4(sbase + kRecUP + (vc0 + 2 * mt + (mi & 1)) * 512 + (2 * np + (mi >> 1)) * 128 + r * 16,
+                  pack_bf16(acc[mt][2 * np][0], acc[mt][2 * np][1]), pack_bf16(acc[mt][2 * np][2], acc[mt][2 * np][3]),
+                  pack_bf16(acc[mt][2 * np + 1][0], acc[mt][2 * np + 1][1]), pack_bf16(acc[mt][2 * np + 1][2], acc[mt][2 * np + 1][3]));
+    }
   }
   fence_proxy_async_smem();
   __syncthreads();

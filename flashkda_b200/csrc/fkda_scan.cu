@@ -247,10 +247,20 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams 
         uint32_t w[32];
         tmem_ld32(tq + kColW, w);
         tmem_wait_ld();
-        const __nv_bfloat16* up = reinterpret_cast<const __nv_bfloat16*>(rec + kRecUP) + v;
+        const uint8_t* up_row = rec + kRecUP + (v >> 3) * 512 + (v & 7) * 16;   // row v of UP [128 v][32 tok]
         float u[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) u[i] = __bfloat162float(up[i * kD]) - __uint_as_float(w[i]);
+        for (int i = 0; i < 4; ++i) {
+          const uint4 t = *reinterpret_cast<const uint4*>(up_row + i * 128);
+          u[8 * i + 0] = bf_lo(t.x) - __uint_as_float(w[8 * i + 0]);
+          u[8 * i + 1] = bf_hi(t.x) - __uint_as_float(w[8 * i + 1]);
+          u[8 * i + 2] = bf_lo(t.y) - __uint_as_float(w[8 * i + 2]);
+          u[8 * i + 3] = bf_hi(t.y) - __uint_as_float(w[8 * i + 3]);
+          u[8 * i + 4] = bf_lo(t.z) - __uint_as_float(w[8 * i + 4]);
+          u[8 * i + 5] = bf_hi(t.z) - __uint_as_float(w[8 * i + 5]);
+          u[8 * i + 6] = bf_lo(t.w) - __uint_as_float(w[8 * i + 6]);
+          u[8 * i + 7] = bf_hi(t.w) - __uint_as_float(w[8 * i + 7]);
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           *reinterpret_cast<uint4*>(ut_row + i * 128) =

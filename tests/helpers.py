@@ -59,7 +59,7 @@ def rel_fro(a, b):
 
 
 # ---- operand-record decoding (layout defined in flashkda_b200/csrc/fkda_common.cuh) ----
-REC = dict(WP=0, QP=8192, KR=16384, UP=24576, MQK=32768, E=34816, BYTES=35328)
+REC = dict(KR=0, MQK=8192, E=10240, WP=10752, QP=18944, UP=27136, BYTES=35328)
 
 
 def _core_index(rows, cols):
@@ -76,7 +76,7 @@ def decode_record(rec_u8):
     out = {}
     for name in ("WP", "QP", "KR"):
         out[name.lower()] = bf(REC[name], 8192)[idx].double()
-    out["up"] = bf(REC["UP"], 8192).view(32, 128).double()
+    out["up"] = bf(REC["UP"], 8192)[_core_index(128, 32)].t().double()     # stored transposed: [128 v][32 tok]
     out["mqk"] = bf(REC["MQK"], 2048)[_core_index(32, 32)].double()
     out["ec"] = rec_u8[REC["E"]:REC["E"] + 512].view(torch.float32).double()
     return out
