@@ -97,6 +97,21 @@ int fkda_read_status(const void* workspace, void* cuda_stream, int* status);
 int fkda_selftest_umma(const void* A, const void* B, float* D, int mode, int reps, int* status,
                        void* cuda_stream);
 
+/* The forward pass with built-in scratch, for callers that cannot allocate device memory (a
+ * server whose memory pool was fixed at start-up, a plugin living inside another component's
+ * budget).  No counterpart in the reference, whose Python wrapper allocates a workspace per call.
+ * Same parameter block as fkda_fwd; `workspace` and `workspace_bytes` are ignored.  The scratch
+ * is a 64 MiB array inside the library image (fkda_static_ws_capacity()), held by every GPU the
+ * library is loaded on; problems that need more are rejected with FKDA_ERR_WORKSPACE_TOO_SMALL.
+ * The first call on a device looks the array's address up, so issue it outside stream capture.
+ * All calls on a device share the array: calls that overlap on the GPU race and must be
+ * serialised by the caller.  Allocates nothing.  fkda_static_ws_read_status is
+ * fkda_read_status for the built-in scratch of the current device. */
+int fkda_fwd_static_ws(const fkda_fwd_params* p, void* cuda_stream);
+int64_t fkda_static_ws_capacity(void);
+int fkda_static_ws_read_status(void* cuda_stream, int* status);
+const char* fkda_static_ws_last_error(void);
+
 /* Message of the last error on this thread ("" if none). */
 const char* fkda_last_error(void);
 
