@@ -15,6 +15,7 @@ _LIB_PATH = os.path.join(_HERE, "libfkda.so")
 _lib = None
 
 FLAG_SCAN_SIMT = 0x1
+FLAG_SCAN_PLAIN = 0x2
 _STATE_NONE, _STATE_BF16, _STATE_FP32 = 0, 1, 2
 
 
@@ -233,7 +234,7 @@ def read_status(workspace) -> int:
 
 def selftest_umma(A, B, mode, reps=1):
     """Runs one tcgen05 product flavour of the scan kernel on one CTA; returns D (fp32)."""
-    n = 128 if mode == 1 else 32
+    n = 128 if mode in (1, 4) else 32
     D = torch.zeros(128, n, dtype=torch.float32, device=A.device)
     status = torch.zeros(1, dtype=torch.int32, device=A.device)
     with torch.cuda.device(A.device):

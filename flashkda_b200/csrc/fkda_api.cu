@@ -13,6 +13,9 @@ cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int* 
 cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
+cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
+void set_scan_trace(unsigned long long* buf);
+cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
 cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* g, const __nv_bfloat16* beta,
                             const float* A_log, const float* dt_bias, float gate_scale, int64_t rows, int H, __nv_bfloat16* qn,
                             __nv_bfloat16* kn, float* gact, float* beta_act, cudaStream_t stream);
@@ -144,7 +147,10 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   s.N = static_cast<int>(p->N);
   s.total_chunks = static_cast<int>(L.chunks_per_head);
   s.state_fp32 = p->state_dtype == FKDA_STATE_FP32 ? 1 : 0;
-  cudaError_t e = (p->flags & FKDA_FLAG_SCAN_SIMT) ? fkda::launch_scan_simt(s, stream) : fkda::launch_scan(s, stream);
+  cudaError_t e;
+  if (p->flags & FKDA_FLAG_SCAN_SIMT) e = fkda::launch_scan_simt(s, stream);
+  else if (p->flags & FKDA_FLAG_SCAN_PLAIN) e = fkda::launch_scan(s, stream);
+  else e = fkda::launch_scan2(s, stream);
   if (e != cudaSuccess) return cuda_fail(e, "scan launch");
   return FKDA_OK;
 }
@@ -223,10 +229,22 @@ int fkda_read_status(const void* workspace, void* cuda_stream, int* status) {
 }
 
 int fkda_selftest_umma(const void* A, const void* B, float* D, int mode, int reps, int* status, void* cuda_stream) {
-  if (!A || !B || !D || !status || mode < 0 || mode > 2 || reps < 1) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
+  if (!A || !B || !D || !status || mode < 0 || mode > 4 || reps < 1) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
   cudaError_t e = fkda::launch_umma_selftest(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B), D, mode,
                                              reps, status, static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) return cuda_fail(e, "selftest launch");
+  return FKDA_OK;
+}
+
+int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream) {
+  if (nwarps < 1 || nwarps > 16 || reps < 1 || !out) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
+  cudaError_t e = fkda::launch_tmem_bench(nwarps, reps, static_cast<long long*>(out), static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_fail(e, "tmem bench launch");
+  return FKDA_OK;
+}
+
+int fkda_debug_set_scan_trace(void* device_buffer) {
+  fkda::set_scan_trace(static_cast<unsigned long long*>(device_buffer));
   return FKDA_OK;
 }
 

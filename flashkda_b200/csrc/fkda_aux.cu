@@ -174,9 +174,11 @@ cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream) {
 }
 
 // ---- tcgen05 descriptor self-test -------------------------------------------------------------------
-// mode 0: D[128][32]  = A[128][128] B[32][128]^T      (both K-major, 8-row groups 2048 B apart)
+// mode 0: D[128][32]  = A[128][128] B[32][128]^T      (both K-major in shared memory, 8-row groups 2048 B apart)
 // mode 1: D[128][128] = A[128][32]  B[32][128]         (A K-major 512 B groups; B read MN-major)
 // mode 2: D[128][32]  = A[128][32]  B[32][32]^T        (both K-major, 512 B groups)
+// mode 3: as mode 0 with A read from tensor memory (bf16 pairs per column)
+// mode 4: as mode 1 with A read from tensor memory
 // Inputs are row-major bf16 in global memory; `reps` > 1 re-issues the product with accumulation
 // (result = reps * product).  D is written row-major fp32.  status[0] = 1 on a wait timeout.
 __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ B,
@@ -187,13 +189,15 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int ka = (mode == 0) ? 128 : 32;                 // K extent
-  const int nn = (mode == 1) ? 128 : 32;                 // N extent
+  const bool a_in_tmem = mode >= 3;
+  const int shape = a_in_tmem ? mode - 3 : mode;         // 0: K=128,N=32   1: K=32,N=128 (B MN-major)   2: K=32,N=32
+  const int ka = (shape == 0) ? 128 : 32;                // K extent
+  const int nn = (shape == 1) ? 128 : 32;                // N extent
   for (int i = tid; i < 128 * ka; i += 128) {
     const int r = i / ka, c = i % ka;
     *reinterpret_cast<__nv_bfloat16*>(sA + core_off(r, c, ka)) = A[i];
   }
-  if (mode == 1) {       // B given as [32 k][128 n], kept in that orientation (core layout of a [32][128] tile)
+  if (shape == 1) {      // B given as [32 k][128 n], kept in that orientation (core layout of a [32][128] tile)
     for (int i = tid; i < 32 * 128; i += 128) *reinterpret_cast<__nv_bfloat16*>(sB + core_off(i / 128, i % 128, 128)) = B[i];
   } else {               // B given as [32 n][ka k]
     for (int i = tid; i < 32 * ka; i += 128) *reinterpret_cast<__nv_bfloat16*>(sB + core_off(i / ka, i % ka, ka)) = B[i];
@@ -204,7 +208,7 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
     fence_mbar_init();
   }
   if (warp == 0) {
-    tmem_alloc(smem_u32(&tmem_slot), 128);
+    tmem_alloc(smem_u32(&tmem_slot), 256);
     tmem_relinquish();
   }
   fence_proxy_async_smem();
@@ -212,21 +216,35 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  const uint32_t a_tm = tmem + 128;                      // A operand columns when read from tensor memory
+  if (a_in_tmem) {
+    // row `tid` of A -> TMEM lane `tid`, 16 columns (32 bf16) at a time
+    for (int cb = 0; cb < ka / 32; ++cb) {
+      uint32_t y[16];
+      for (int i = 0; i < 16; ++i) {
+        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(A + tid * ka + cb * 32 + 2 * i);
+        y[i] = *reinterpret_cast<const uint32_t*>(&v2);
+      }
+      tmem_st16(a_tm + (static_cast<uint32_t>(warp * 32) << 16) + cb * 16, y);
+    }
+    tmem_wait_st();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
   if (tid == 0) {
     const uint32_t a_addr = smem_u32(sA), b_addr = smem_u32(sB);
     for (int rep = 0; rep < reps; ++rep) {
-      if (mode == 0) {
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tmem, umma_desc(a_addr + ks * 256, 128, 2048), umma_desc(b_addr + ks * 256, 128, 2048),
-                  umma_idesc_bf16(128, 32, 0, 0), (rep > 0 || ks > 0) ? 1u : 0u);
-      } else if (mode == 1) {
-        for (int ks = 0; ks < 2; ++ks)
-          umma_ss(tmem, umma_desc(a_addr + ks * 256, 128, 512), umma_desc(b_addr + ks * 4096, 2048, 128),
-                  umma_idesc_bf16(128, 128, 0, 1), (rep > 0 || ks > 0) ? 1u : 0u);
-      } else {
-        for (int ks = 0; ks < 2; ++ks)
-          umma_ss(tmem, umma_desc(a_addr + ks * 256, 128, 512), umma_desc(b_addr + ks * 256, 128, 512),
-                  umma_idesc_bf16(128, 32, 0, 0), (rep > 0 || ks > 0) ? 1u : 0u);
+      const int ksteps = ka / 16;
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const uint32_t acc = (rep > 0 || ks > 0) ? 1u : 0u;
+        uint64_t bdesc;
+        uint32_t idesc;
+        if (shape == 0) { bdesc = umma_desc(b_addr + ks * 256, 128, 2048); idesc = umma_idesc_bf16(128, 32, 0, 0); }
+        else if (shape == 1) { bdesc = umma_desc(b_addr + ks * 4096, 2048, 128); idesc = umma_idesc_bf16(128, 128, 0, 1); }
+        else { bdesc = umma_desc(b_addr + ks * 256, 128, 512); idesc = umma_idesc_bf16(128, 32, 0, 0); }
+        if (a_in_tmem) umma_ts(tmem, a_tm + ks * 8, bdesc, idesc, acc);
+        else umma_ss(tmem, umma_desc(a_addr + ks * 256, 128, shape == 0 ? 2048 : 512), bdesc, idesc, acc);
       }
     }
     umma_commit(smem_u32(&mbar));
@@ -247,8 +265,71 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem, 128);
+    tmem_dealloc(tmem, 256);
   }
+}
+
+// Micro-benchmark of tensor-memory access (tuning aid): `nwarps` warps each move `reps` x 32 columns between
+// registers and their TMEM lane quadrant; out[warp*4 + {0,1,2,3}] = cycles for {ld, st, st16-packed, ld+st} loops.
+__global__ void __launch_bounds__(512) tmem_bench_kernel(int reps, long long* out) {
+  __shared__ uint32_t tmem_slot;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tq = tmem_slot + (static_cast<uint32_t>((warp & 3) * 32) << 16) + (warp >> 2) * 128;
+  uint32_t x[32];
+  uint32_t y[16];
+  for (int i = 0; i < 32; ++i) x[i] = lane + i;
+  for (int i = 0; i < 16; ++i) y[i] = lane * 3 + i;
+  for (int i = 0; i < 4; ++i) tmem_st32(tq + 32 * i, x);
+  tmem_wait_st();
+  __syncthreads();
+  long long t0 = clock64();
+  for (int r = 0; r < reps; ++r) tmem_ld32(tq + 32 * (r & 3), x);
+  tmem_wait_ld();
+  long long t1 = clock64();
+  __syncthreads();
+  long long t2 = clock64();
+  for (int r = 0; r < reps; ++r) tmem_st32(tq + 32 * (r & 3), x);
+  tmem_wait_st();
+  long long t3 = clock64();
+  __syncthreads();
+  long long t4 = clock64();
+  for (int r = 0; r < reps; ++r) tmem_st16(tq + 16 * (r & 7), y);
+  tmem_wait_st();
+  long long t5 = clock64();
+  __syncthreads();
+  long long t6 = clock64();
+  for (int r = 0; r < reps; ++r) {
+    tmem_ld32(tq + 32 * (r & 3), x);
+    tmem_wait_ld();
+    for (int i = 0; i < 32; ++i) x[i] += 1;
+    tmem_st32(tq + 32 * (r & 3), x);
+  }
+  tmem_wait_st();
+  long long t7 = clock64();
+  if (lane == 0) {
+    out[warp * 4 + 0] = t1 - t0;
+    out[warp * 4 + 1] = t3 - t2;
+    out[warp * 4 + 2] = t5 - t4;
+    out[warp * 4 + 3] = t7 - t6 + (x[5] == 0xdeadbeef);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_slot, 512);
+  }
+}
+
+cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream) {
+  tmem_bench_kernel<<<1, nwarps * 32, 0, stream>>>(reps, out);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_umma_selftest(const __nv_bfloat16* A, const __nv_bfloat16* B, float* D, int mode, int reps, int* status,

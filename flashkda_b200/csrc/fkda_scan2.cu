@@ -1,0 +1,523 @@
+// Inter-chunk recurrence of the KDA prefill, look-ahead form: one CTA walks the chunks of one
+// (sequence, head) chain with the 128x128 fp32 state resident in tensor memory.
+//
+// Replaces the reference's K2 (csrc/smxx/fwd_kernel2.cuh:115-839).  With S_c the state after chunk c
+// (held as S^T: TMEM lanes = v, columns = k) and Sd_c = diag(e_{c+1}) S_c its pre-decayed form,
+//     S_c     = Sd_{c-1} + kr_c^T U_c
+//     W_{c+1} = wp_{c+1} S_c = wp_{c+1} Sd_{c-1} + X_{c+1} U_c ,   X_{c+1} = wp_{c+1} kr_c^T   (32x32)
+//     O_{c+1} = qp_{c+1} Sd_{c-1} + Y_{c+1} U_c + mqk_{c+1} U_{c+1} , Y_{c+1} = qp_{c+1} kr_c^T
+//     U_c     = up_c - W_c
+// so the serial chain per chunk is only  U_c -> (tiny K=32 MMA) -> W_{c+1} -> U_{c+1};  the state
+// update, its decay and the refresh of its bf16 operand copy run beside that chain, and X, Y are
+// products of operand records only and are computed ahead of time.  All products are tcgen05.mma
+// with M = 128; U^T and the bf16 copy of Sd are MMA A-operands read from tensor memory.
+//
+// Warp roles (640 threads): 0 = bulk-copy producer; 1, 2, 3 = one MMA-issuing thread each (products on
+// U / on the decayed state / X,Y), ordered among each other through tcgen05.commit + mbarriers;
+// 4-7 = U warps (critical chain); 8-15 = state warps (two groups of four, 64 state columns each);
+// 16-19 = output warps (two of them also turn X, Y into bf16 operands).  Every wait is bounded; a wait that gives up raises an abort flag, records a
+// status code and lets all roles fall through to the common exit, where TMEM is released.
+#include "fkda_common.cuh"
+
+namespace fkda {
+namespace scan2 {
+
+// Optional timeline trace (bring-up / tuning aid): when a buffer has been registered with
+// fkda_debug_set_scan_trace, CTA 0 records clock64() at a few points of each role for its first
+// 32 chunks: entry [(role * 32 + chunk) * 8 + event].  No effect when no buffer is registered.
+static unsigned long long* g_trace = nullptr;
+#define FKDA_TRACE(role, c, ev)                                                                         \
+  do {                                                                                                  \
+    if (trace != nullptr && (c) < 32) trace[((role) * 32 + (c)) * 8 + (ev)] = static_cast<unsigned long long>(clock64()); \
+  } while (0)
+
+constexpr int kStages = 5;
+constexpr int kThreads = 20 * 32;
+constexpr uint32_t kTmemCols = 512;
+// tensor-memory columns
+constexpr uint32_t kColS = 0;                   // 128: state accumulator S^T [v][k], fp32
+constexpr uint32_t kColWO = 128;                // 2 x 64: [W^T | O^T], each [v][tok] of 32 columns
+constexpr uint32_t kColW = kColWO;              //   W of buffer b at kColW + 64 b
+constexpr uint32_t kColO = kColWO + 32;         //   O of buffer b at kColO + 64 b
+constexpr uint32_t kColXA = 256;                // 2 x 32: [X;Y] accumulator, lanes 0-31 X rows, 32-63 Y rows
+constexpr uint32_t kColSbd = 320;               // 2 x 64: bf16 copy of Sd [v][k], two k per column
+constexpr uint32_t kColUt = 448;                // 2 x 16: bf16 U^T [v][tok], two tokens per column
+
+// shared memory (byte offsets from a 1024-byte aligned base)
+constexpr int kSmStage = 0;
+constexpr int kSmXY = kSmStage + kStages * kRecBytes;   // 2 x [64][32] bf16 (core layout): rows 0-31 X, 32-63 Y
+constexpr int kSmOutStg = kSmXY + 2 * 4096;             // 4 warps x [32 tok][32 v] bf16
+constexpr int kSmBars = kSmOutStg + 4 * 2048;
+constexpr int kSmMisc = kSmBars + 256;
+constexpr int kSmemBytes = kSmMisc + 64 + 1024;
+
+enum {
+  BAR_FULL = 0,                    // [kStages] record landed
+  BAR_EMPTY = BAR_FULL + kStages,  // [kStages] record no longer needed
+  BAR_WFULL = BAR_EMPTY + kStages, // [2] W buffer complete
+  BAR_OFULL = BAR_WFULL + 2,       // [2] O buffer complete
+  BAR_XFULL = BAR_OFULL + 2,       // [2] X/Y accumulator complete
+  BAR_XREADY = BAR_XFULL + 2,      // [2] X/Y bf16 operands in shared memory
+  BAR_OFREE = BAR_XREADY + 2,      // [2] O buffer drained
+  BAR_AFULL = BAR_OFREE + 2,       // [2] products on the decayed state have landed in the W/O buffer
+  BAR_WFREE = BAR_AFULL + 2,       // [2] W buffer read by the U warps
+  BAR_XYFREE = BAR_WFREE + 2,      // [2] products that read the X/Y operands of a buffer are complete
+  BAR_SFULL = BAR_XYFREE + 2,      // state update of a chunk complete
+  BAR_UREADY,                      // U^T of a chunk in tensor memory
+  BAR_SBDREADY,                    // decayed state + its bf16 copy ready
+  BAR_COUNT
+};
+static_assert(BAR_COUNT * 8 <= 256, "barrier area");
+
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const bool ok = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
+// use count of the X/Y buffers: chunk c >= 1 uses buffer c & 1
+__device__ __forceinline__ uint32_t xy_use(int c) { return (c & 1) ? (c >> 1) : (c >> 1) - 1; }
+
+__device__ __forceinline__ void pack32(const uint32_t (&x)[32], uint32_t (&y)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
+}
+
+__global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, unsigned long long* trace_buf) {
+  unsigned long long* trace = (blockIdx.x == 0) ? trace_buf : nullptr;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
+  auto full_bar = [&](int c) { return bar(BAR_FULL + c % kStages); };
+  auto full_par = [&](int c) { return static_cast<uint32_t>((c / kStages) & 1); };
+
+  // ---- chain -> tokens and records ---------------------------------------------------------------------
+  const int chain = blockIdx.x;
+  const int n = chain / p.H, h = chain - n * p.H;
+  int64_t bos, eos;
+  int chunk_base;
+  if (p.cu_seqlens != nullptr) {
+    bos = p.cu_seqlens[n];
+    eos = p.cu_seqlens[n + 1];
+    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
+    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
+    chunk_base = p.chunk_prefix[n];
+  } else {
+    bos = static_cast<int64_t>(n) * p.T;
+    eos = bos + p.T;
+    chunk_base = n * static_cast<int>((p.T + kChunk - 1) / kChunk);
+  }
+  int nchunks = static_cast<int>((eos - bos + kChunk - 1) / kChunk);
+  {  // never read past the records of this head, whatever cu_seqlens claims
+    const int avail = p.total_chunks > chunk_base ? p.total_chunks - chunk_base : 0;
+    if (nchunks > avail) nchunks = avail;
+  }
+  const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + chunk_base) * kRecBytes;
+
+  // ---- setup -----------------------------------------------------------------------------------------------
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(BAR_FULL + s), 1);
+      mbar_init(bar(BAR_EMPTY + s), 1 + 4 + 8);   // MMA commit + U warps + state warps
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(BAR_WFULL + b), 1);
+      mbar_init(bar(BAR_OFULL + b), 1);
+      mbar_init(bar(BAR_XFULL + b), 1);
+      mbar_init(bar(BAR_XREADY + b), 2);
+      mbar_init(bar(BAR_OFREE + b), 4);
+      mbar_init(bar(BAR_AFULL + b), 1);
+      mbar_init(bar(BAR_WFREE + b), 4);
+      mbar_init(bar(BAR_XYFREE + b), 1);
+    }
+    mbar_init(bar(BAR_SFULL), 1);
+    mbar_init(bar(BAR_UREADY), 4);
+    mbar_init(bar(BAR_SBDREADY), 8);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  bool failed = false;
+
+  if (warp == 0) {
+    // ===== copy producer: one bulk copy per chunk record ===================================================
+    if (lane == 0) {
+      int issued = 0;
+      for (int c = 0; c < nchunks; ++c) {
+        const int s = c % kStages, k = c / kStages;
+        if (k > 0 && !mbar_wait(bar(BAR_EMPTY + s), (k - 1) & 1, abort_flag)) { failed = true; break; }
+        FKDA_TRACE(4, c, 0);
+        mbar_arrive_expect_tx(bar(BAR_FULL + s), kRecBytes);
+        bulk_g2s(sbase + kSmStage + s * kRecBytes, rec0 + static_cast<size_t>(c) * kRecBytes, kRecBytes, bar(BAR_FULL + s));
+        issued = c + 1;
+      }
+      if (failed || *abort_flag) {
+        // wait (bounded) for copies still in flight so that the CTA does not exit under them
+        for (int c = issued > kStages ? issued - kStages : 0; c < issued; ++c) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(bar(BAR_FULL + c % kStages), (c / kStages) & 1))
+            if (globaltimer_ns() - t0 > 20000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer 1: products on U_c (finish W_{c+1} first: it is the serial chain) =====================
+    if (lane == 0) {
+      constexpr uint32_t idesc_n32 = umma_idesc_bf16(128, 32, 0, 0);
+      constexpr uint32_t idesc_n64 = umma_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t idesc_n128_bmn = umma_idesc_bf16(128, 128, 0, 1);
+      for (int c = 0; c < nchunks; ++c) {
+        const uint32_t rec = sbase + kSmStage + (c % kStages) * kRecBytes;
+        const uint32_t ut = tmem + kColUt + 16 * (c & 1);
+        const bool more = c + 1 < nchunks;
+        if (!mbar_wait(bar(BAR_SBDREADY), c & 1, abort_flag)) { failed = true; break; }
+        if (!mbar_wait(bar(BAR_UREADY), c & 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        FKDA_TRACE(0, c, 0);
+        {  // S^T += U^T kr : kr [32 tok][128 k] read MN-major (k-adjacent core matrices 128 B apart, token groups 2048 B)
+          const uint64_t bk = umma_desc(rec + kRecKR, 2048, 128);
+          umma_ts(tmem + kColS, ut, bk, idesc_n128_bmn, 1);
+          umma_ts(tmem + kColS, ut + 8, bk + 256, idesc_n128_bmn, 1);
+          umma_commit(bar(BAR_SFULL));
+        }
+        if (more) {
+          // [W_{c+1} | O_{c+1}] += U_c^T [X_{c+1}; Y_{c+1}]^T : one N = 64 product per k-step, on top of the
+          // products on the decayed state that issuer 2 placed there
+          if (!mbar_wait(bar(BAR_AFULL + ((c + 1) & 1)), ((c + 1) >> 1) & 1, abort_flag)) { failed = true; break; }
+          if (!mbar_wait(bar(BAR_XREADY + ((c + 1) & 1)), xy_use(c + 1) & 1u, abort_flag)) { failed = true; break; }
+          tc_fence_after();
+          const uint64_t bx = umma_desc(sbase + kSmXY + 4096 * ((c + 1) & 1), 128, 512);
+          umma_ts(tmem + kColWO + 64 * ((c + 1) & 1), ut, bx, idesc_n64, 1);
+          umma_ts(tmem + kColWO + 64 * ((c + 1) & 1), ut + 8, bx + 16, idesc_n64, 1);
+          umma_commit(bar(BAR_WFULL + ((c + 1) & 1)));
+        } else if (!mbar_wait(bar(BAR_AFULL + (c & 1)), (c >> 1) & 1, abort_flag)) { failed = true; break; }
+        {  // O_c += U_c^T mqk_c^T (O_c's other terms were issued in earlier iterations / by issuer 2)
+          const uint64_t bm = umma_desc(rec + kRecMQK, 128, 512);
+          umma_ts(tmem + kColO + 64 * (c & 1), ut, bm, idesc_n32, 1);
+          umma_ts(tmem + kColO + 64 * (c & 1), ut + 8, bm + 16, idesc_n32, 1);
+          umma_commit(bar(BAR_OFULL + (c & 1)));
+        }
+        if (more) umma_commit(bar(BAR_XYFREE + ((c + 1) & 1)));
+        umma_commit(bar(BAR_EMPTY + c % kStages));
+        FKDA_TRACE(0, c, 1);
+      }
+      // the last commit's arrival must have landed in shared memory before the CTA may exit
+      if (!failed && nchunks > 0) {
+        const int c = nchunks - 1;
+        if (!mbar_wait(bar(BAR_EMPTY + c % kStages), (c / kStages) & 1, abort_flag)) failed = true;
+      }
+    }
+  } else if (warp == 2) {
+    // ===== MMA issuer 2: [W_c | O_c] = Sd_{c-2} [wp_c; qp_c]^T (A from tensor memory, N = 64) ==============
+    if (lane == 0) {
+      constexpr uint32_t idesc_n64 = umma_idesc_bf16(128, 64, 0, 0);
+      for (int c = 0; c < nchunks; ++c) {
+        if (!mbar_wait(full_bar(c), full_par(c), abort_flag)) { failed = true; break; }
+        if (c >= 2) {   // the buffer's previous contents have been consumed
+          if (!mbar_wait(bar(BAR_WFREE + (c & 1)), ((c - 2) >> 1) & 1, abort_flag)) { failed = true; break; }
+          if (!mbar_wait(bar(BAR_OFREE + (c & 1)), ((c - 2) >> 1) & 1, abort_flag)) { failed = true; break; }
+        }
+        if (!mbar_wait(bar(BAR_SBDREADY), (c < 2 ? 0 : c - 1) & 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        FKDA_TRACE(0, c, 2);
+        const uint32_t sbd = tmem + kColSbd + 64 * (c & 1);
+        const uint64_t b = umma_desc(sbase + kSmStage + (c % kStages) * kRecBytes + kRecWP, 128, 2048);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_ts(tmem + kColWO + 64 * (c & 1), sbd + ks * 8, b + ks * 16, idesc_n64, ks > 0);
+        umma_commit(bar(BAR_AFULL + (c & 1)));
+        if (c == 0) umma_commit(bar(BAR_WFULL + 0));
+        FKDA_TRACE(0, c, 3);
+      }
+    }
+  } else if (warp == 3) {
+    // ===== MMA issuer 3: [X_c; Y_c] = [wp_c; qp_c] kr_{c-1}^T (records only, runs ahead) ======================
+    if (lane == 0) {
+      constexpr uint32_t idesc_n32 = umma_idesc_bf16(128, 32, 0, 0);
+      for (int c = 1; c < nchunks; ++c) {
+        if (!mbar_wait(full_bar(c - 1), full_par(c - 1), abort_flag)) { failed = true; break; }
+        if (!mbar_wait(full_bar(c), full_par(c), abort_flag)) { failed = true; break; }
+        if (c >= 3) {   // accumulator read by the X/Y epilogue of chunk c-2, its operands consumed by the U products
+          if (!mbar_wait(bar(BAR_XREADY + (c & 1)), xy_use(c - 2) & 1u, abort_flag)) { failed = true; break; }
+          if (!mbar_wait(bar(BAR_XYFREE + (c & 1)), xy_use(c - 2) & 1u, abort_flag)) { failed = true; break; }
+        }
+        tc_fence_after();
+        FKDA_TRACE(0, c, 4);
+        const uint64_t a = umma_desc(sbase + kSmStage + (c % kStages) * kRecBytes + kRecWP, 128, 2048);
+        const uint64_t b = umma_desc(sbase + kSmStage + ((c - 1) % kStages) * kRecBytes + kRecKR, 128, 2048);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_ss(tmem + kColXA + 32 * (c & 1), a + ks * 16, b + ks * 16, idesc_n32, ks > 0);
+        umma_commit(bar(BAR_XFULL + (c & 1)));
+        FKDA_TRACE(0, c, 5);
+      }
+    }
+  } else if (warp < 8) {
+    // ===== U warps: U^T = up^T - W^T, as a bf16 A operand in tensor memory (the serial chain) =============
+    const int qd = warp & 3;
+    const int v = qd * 32 + lane;
+    const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
+    for (int c = 0; c < nchunks; ++c) {
+      const uint8_t* rec = smem + kSmStage + (c % kStages) * kRecBytes;
+      if (!warp_wait(full_bar(c), full_par(c), abort_flag)) { failed = true; break; }
+      if (!warp_wait(bar(BAR_WFULL + (c & 1)), (c >> 1) & 1, abort_flag)) { failed = true; break; }
+      tc_fence_after();
+      if (warp == 4 && lane == 0) FKDA_TRACE(1, c, 0);
+      uint32_t w[32], y[16];
+      tmem_ld32(tq + kColW + 64 * (c & 1), w);
+      const uint8_t* up_row = rec + kRecUP + (v >> 3) * 512 + (v & 7) * 16;   // row v of UP [128 v][32 tok]
+      uint4 t[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) t[i] = *reinterpret_cast<const uint4*>(up_row + i * 128);
+      tmem_wait_ld();
+      if (warp == 4 && lane == 0) FKDA_TRACE(1, c, 1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        y[4 * i + 0] = pack_bf16(bf_lo(t[i].x) - __uint_as_float(w[8 * i + 0]), bf_hi(t[i].x) - __uint_as_float(w[8 * i + 1]));
+        y[4 * i + 1] = pack_bf16(bf_lo(t[i].y) - __uint_as_float(w[8 * i + 2]), bf_hi(t[i].y) - __uint_as_float(w[8 * i + 3]));
+        y[4 * i + 2] = pack_bf16(bf_lo(t[i].z) - __uint_as_float(w[8 * i + 4]), bf_hi(t[i].z) - __uint_as_float(w[8 * i + 5]));
+        y[4 * i + 3] = pack_bf16(bf_lo(t[i].w) - __uint_as_float(w[8 * i + 6]), bf_hi(t[i].w) - __uint_as_float(w[8 * i + 7]));
+      }
+      tmem_st16(tq + kColUt + 16 * (c & 1), y);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (warp == 4) FKDA_TRACE(1, c, 2);
+        mbar_arrive(bar(BAR_UREADY));
+        mbar_arrive(bar(BAR_WFREE + (c & 1)));
+        mbar_arrive(bar(BAR_EMPTY + c % kStages));   // this warp is done reading up[] of the record
+      }
+    }
+  } else if (warp < 16) {
+    // ===== state warps: two groups of four; group g owns state columns k in [64g, 64g+64) =====================
+    const int grp = (warp - 8) >> 2;
+    const int qd = warp & 3;
+    const int v = qd * 32 + lane;
+    const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
+    const size_t row_off = ((static_cast<size_t>(n) * p.H + h) * kD + v) * kD;   // row v of this chain's state
+
+    // ---- initial state: S <- e_0 S_init; bf16 copies of S_init (buffer 0) and e_0 S_init (buffer 1) --------
+    bool ok = true;
+    if (nchunks > 0) ok = warp_wait(full_bar(0), 0, abort_flag);
+    if (ok) {
+      const float* e0 = reinterpret_cast<const float*>(smem + kSmStage + kRecE);
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        const int cb = 2 * grp + half;     // 32-column block
+        uint32_t x[32], y[16];
+        if (p.initial_state != nullptr) {
+          if (p.state_fp32) {
+            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.initial_state) + row_off + cb * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 f = __ldg(src + i);
+              x[4 * i] = __float_as_uint(f.x); x[4 * i + 1] = __float_as_uint(f.y);
+              x[4 * i + 2] = __float_as_uint(f.z); x[4 * i + 3] = __float_as_uint(f.w);
+            }
+          } else {
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + row_off + cb * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 w = __ldg(src + i);
+              x[8 * i] = w.x << 16; x[8 * i + 1] = w.x & 0xffff0000u; x[8 * i + 2] = w.y << 16; x[8 * i + 3] = w.y & 0xffff0000u;
+              x[8 * i + 4] = w.z << 16; x[8 * i + 5] = w.z & 0xffff0000u; x[8 * i + 6] = w.w << 16; x[8 * i + 7] = w.w & 0xffff0000u;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = 0u;
+        }
+        if (nchunks > 0) {
+          pack32(x, y);
+          tmem_st16(tq + kColSbd + 0 + cb * 16, y);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e0[cb * 32 + i]);
+          pack32(x, y);
+          tmem_st16(tq + kColSbd + 64 + cb * 16, y);
+        }
+        tmem_st32(tq + kColS + cb * 32, x);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(BAR_SBDREADY));
+        if (nchunks > 0) mbar_arrive(bar(BAR_EMPTY + 0));   // done with e of record 0
+      }
+    } else {
+      failed = true;
+    }
+
+    // ---- per chunk: decay the updated state for the next chunk and refresh its bf16 copy ------------------
+    for (int c = 0; c + 1 < nchunks && !failed; ++c) {
+      if (!warp_wait(full_bar(c + 1), full_par(c + 1), abort_flag)) { failed = true; break; }
+      if (!warp_wait(bar(BAR_SFULL), c & 1, abort_flag)) { failed = true; break; }
+      const int trole = (warp == 8) ? 2 : 5;
+      const bool tr_on = (warp == 8 || warp == 12) && lane == 0;
+      if (tr_on) FKDA_TRACE(trole, c, 0);
+      tc_fence_after();
+      if (tr_on) FKDA_TRACE(trole, c, 1);
+      const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 64 * grp;
+      uint32_t x0[32], x1[32], y[16];
+      tmem_ld32(tq + kColS + 64 * grp, x0);
+      tmem_ld32(tq + kColS + 64 * grp + 32, x1);
+      tmem_wait_ld();
+      if (tr_on) FKDA_TRACE(trole, c, 2);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 f = *reinterpret_cast<const float4*>(e + 4 * i);
+        x0[4 * i] = __float_as_uint(__uint_as_float(x0[4 * i]) * f.x);
+        x0[4 * i + 1] = __float_as_uint(__uint_as_float(x0[4 * i + 1]) * f.y);
+        x0[4 * i + 2] = __float_as_uint(__uint_as_float(x0[4 * i + 2]) * f.z);
+        x0[4 * i + 3] = __float_as_uint(__uint_as_float(x0[4 * i + 3]) * f.w);
+      }
+      if (tr_on) FKDA_TRACE(trole, c, 6);
+      tmem_st32(tq + kColS + 64 * grp, x0);
+      pack32(x0, y);
+      tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp, y);
+      if (tr_on) FKDA_TRACE(trole, c, 7);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 f = *reinterpret_cast<const float4*>(e + 32 + 4 * i);
+        x1[4 * i] = __float_as_uint(__uint_as_float(x1[4 * i]) * f.x);
+        x1[4 * i + 1] = __float_as_uint(__uint_as_float(x1[4 * i + 1]) * f.y);
+        x1[4 * i + 2] = __float_as_uint(__uint_as_float(x1[4 * i + 2]) * f.z);
+        x1[4 * i + 3] = __float_as_uint(__uint_as_float(x1[4 * i + 3]) * f.w);
+      }
+      tmem_st32(tq + kColS + 64 * grp + 32, x1);
+      pack32(x1, y);
+      tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp + 16, y);
+      if (tr_on) FKDA_TRACE(trole, c, 4);
+      tmem_wait_st();
+      if (tr_on) FKDA_TRACE(trole, c, 5);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (tr_on) FKDA_TRACE(trole, c, 3);
+        mbar_arrive(bar(BAR_SBDREADY));
+        mbar_arrive(bar(BAR_EMPTY + (c + 1) % kStages));    // done with e of record c+1
+      }
+    }
+
+    // ---- final state -> global -------------------------------------------------------------------------------
+    if (!failed && p.final_state != nullptr) {
+      bool ok2 = true;
+      if (nchunks > 0) ok2 = warp_wait(bar(BAR_SFULL), (nchunks - 1) & 1, abort_flag);
+      if (ok2) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          const int cb = 2 * grp + half;
+          uint32_t x[32];
+          tmem_ld32(tq + kColS + cb * 32, x);
+          tmem_wait_ld();
+          if (p.state_fp32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.final_state) + row_off + cb * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]), __uint_as_float(x[4 * i + 2]),
+                                   __uint_as_float(x[4 * i + 3]));
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.final_state) + row_off + cb * 32);
+            uint32_t y[16];
+            pack32(x, y);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
+          }
+        }
+      } else {
+        failed = true;
+      }
+    }
+  } else {
+    // ===== output warps: O^T (TMEM lanes = v, columns = tokens) -> out[token][h][v]; X/Y -> bf16 operands ======
+    const int qd = warp & 3;
+    const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
+    __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + kSmOutStg + qd * 2048);   // [32 tok][32 v]
+    auto xy_epilogue = [&](int c) -> bool {     // accumulator lanes 0-31 = X rows, 32-63 = Y rows (warps on quadrants 0, 1)
+      if (qd >= 2) return true;
+      if (!warp_wait(bar(BAR_XFULL + (c & 1)), xy_use(c) & 1u, abort_flag)) return false;
+      tc_fence_after();
+      if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 0);
+      uint32_t x[32], y[16];
+      tmem_ld32(tq + kColXA + 32 * (c & 1), x);
+      tmem_wait_ld();
+      pack32(x, y);
+      const int r = qd * 32 + lane;
+      uint8_t* row = smem + kSmXY + 4096 * (c & 1) + (r >> 3) * 512 + (r & 7) * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(row + i * 128) = make_uint4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (warp == 16) FKDA_TRACE(3, c, 1);
+        mbar_arrive(bar(BAR_XREADY + (c & 1)));
+      }
+      return true;
+    };
+    for (int c = 0; c < nchunks; ++c) {
+      if (c == 0 && nchunks > 1 && !xy_epilogue(1)) { failed = true; break; }
+      if (c + 2 < nchunks && !xy_epilogue(c + 2)) { failed = true; break; }
+      if (!warp_wait(bar(BAR_OFULL + (c & 1)), (c >> 1) & 1, abort_flag)) { failed = true; break; }
+      tc_fence_after();
+      if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 2);
+      uint32_t o[32];
+      tmem_ld32(tq + kColO + 64 * (c & 1), o);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_OFREE + (c & 1)));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) stg[i * 32 + lane] = __float2bfloat16_rn(__uint_as_float(o[i]));
+      __syncwarp();
+      const int64_t tok0 = bos + static_cast<int64_t>(c) * kChunk;
+      const int valid = (eos - tok0) < kChunk ? static_cast<int>(eos - tok0) : kChunk;
+      // each token row of this warp's 32 v-columns is 64 contiguous bytes: 4 lanes x 16 B, 8 rows per pass
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
+        if (r < valid) {
+          const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 32 + c8);
+          *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(tok0 + r) * p.H + h) * kD + qd * 32 + c8) = val;
+        }
+      }
+      __syncwarp();
+      if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 3);
+    }
+  }
+
+  if (failed || *abort_flag) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+
+  // ---- common exit: every thread arrives here, TMEM goes back ------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace scan2
+
+cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(scan2::scan2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan2::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int64_t chains = static_cast<int64_t>(p.N) * p.H;
+  if (chains == 0) return cudaSuccess;
+  scan2::scan2_kernel<<<static_cast<unsigned>(chains), scan2::kThreads, scan2::kSmemBytes, stream>>>(p, scan2::g_trace);
+  return cudaGetLastError();
+}
+
+void set_scan_trace(unsigned long long* buf) { scan2::g_trace = buf; }
+
+}  // namespace fkda

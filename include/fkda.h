@@ -34,6 +34,7 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 
 /* flags */
 #define FKDA_FLAG_SCAN_SIMT 0x1u /* evaluate the recurrence on CUDA cores (verification aid, slow) */
+#define FKDA_FLAG_SCAN_PLAIN 0x2u /* tcgen05 recurrence without look-ahead (kept for cross-checking) */
 
 typedef struct fkda_fwd_params {
   /* bf16 [B*T][H][128], contiguous (reference: q,k,v,g of csrc/flash_kda.cpp:28-33) */
@@ -96,6 +97,14 @@ int fkda_read_status(const void* workspace, void* cuda_stream, int* status);
  * fkda_aux.cu).  A, B bf16 row-major, D fp32 row-major, all device pointers; status int32. */
 int fkda_selftest_umma(const void* A, const void* B, float* D, int mode, int reps, int* status,
                        void* cuda_stream);
+
+/* Tuning aid: registers (or, with NULL, removes) a device buffer of 6*32*8 uint64 into which CTA 0 of
+ * the scan kernel records clock64() at a few points of each warp role for its first 32 chunks. */
+int fkda_debug_set_scan_trace(void* device_buffer);
+
+/* Tuning aid: one CTA of `nwarps` (<= 16) warps times `reps` 32-column TMEM loads / stores per warp;
+ * out = int64[nwarps][4] cycles for {loads, stores, 16-column stores, load+store round trips}. */
+int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream);
 
 /* The forward pass with built-in scratch, for callers that cannot allocate device memory (a
  * server whose memory pool was fixed at start-up, a plugin living inside another component's

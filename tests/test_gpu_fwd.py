@@ -58,7 +58,7 @@ def check_against_f64(x, out, fin, tag, big_state=False):
     return o64, s64
 
 
-@pytest.mark.parametrize("flags", [F.FLAG_SCAN_SIMT, 0], ids=["simt_checker", "tcgen05"])
+@pytest.mark.parametrize("flags", [F.FLAG_SCAN_SIMT, F.FLAG_SCAN_PLAIN, 0], ids=["simt_checker", "tcgen05_plain", "tcgen05_lookahead"])
 @pytest.mark.parametrize("name", golden_names())
 def test_golden_cases(name, flags):
     x, ref_out, ref_fin = load_golden(name)

@@ -13,14 +13,16 @@ from helpers import decode_record, to_cuda
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("reps", [1, 2])
 def test_umma_descriptor_flavours(mode, reps):
+    """Modes 0-2: both operands in shared memory; 3, 4: A operand read from tensor memory."""
     g = torch.Generator().manual_seed(mode)
-    ka = 128 if mode == 0 else 32
+    shape = mode - 3 if mode >= 3 else mode
+    ka = 128 if shape == 0 else 32
     A = torch.randn(128, ka, generator=g).bfloat16()
-    B = (torch.randn(32, 128, generator=g) if mode == 1 else torch.randn(32, ka, generator=g)).bfloat16()
-    ref = A.double() @ (B.double() if mode == 1 else B.double().t())
+    B = (torch.randn(32, 128, generator=g) if shape == 1 else torch.randn(32, ka, generator=g)).bfloat16()
+    ref = A.double() @ (B.double() if shape == 1 else B.double().t())
     D = F.selftest_umma(A.cuda(), B.cuda(), mode, reps).cpu().double()
     err = (D - reps * ref).abs().max().item()
     assert err < 1e-3 * max(1.0, ref.abs().max().item()), \
