@@ -204,18 +204,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     # ---- this rank's shard ------------------------------------------------------------------------
-    heads = None
-    if args.shard == "head" and world > 1:
-        per = w.H // world
-        heads = range(rank * per, (rank + 1) * per)
-        w_local = w
-        tokens_global = w.total_tokens
-        scaling = "strong"
-    else:
-        w_local = Workload(w.name, H=w.H, B=w.B, T=w.T, seq_lens=w.seq_lens, lower_bound=w.lower_bound,
-                           state_in=w.state_in, state_out=w.state_out, state_std=w.state_std, seed=w.seed + rank)
-        tokens_global = w.total_tokens * world
-        scaling = "weak"
+    from flashkda_b200.sharding import plan, reduce_max_ms
+    shard = plan(w, world, rank, args.shard)
+    w_local, heads, tokens_global, scaling = shard.workload, shard.heads, shard.tokens_global, shard.scaling
     x = make_inputs(w_local, device=dev, heads=heads)
     H_local = x["q"].shape[2]
     B, T = x["q"].shape[:2]
@@ -291,10 +282,7 @@ def main():
         e2e = (a.elapsed_time(b) / e_steps, h2d, d2h)
 
     # ---- reduce over ranks: max time -------------------------------------------------------------------
-    vals = torch.tensor([ms, ms_prepare, ms_scan, e2e[0] if e2e else 0.0], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    ms, ms_prepare, ms_scan, ms_e2e = vals.tolist()
+    ms, ms_prepare, ms_scan, ms_e2e = reduce_max_ms([ms, ms_prepare, ms_scan, e2e[0] if e2e else 0.0], world, dev)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
