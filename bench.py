@@ -100,7 +100,8 @@ def cpu_baseline_sample(w: Workload, target_s=12.0, nthreads=0):
     restating tests/torch_ref.py of the reference) on the first tokens of sequence 0, all heads,
     of the same workload.  Returns (tokens_per_s, cores, description)."""
     import oracle
-    cores = oracle.max_threads() if nthreads <= 0 else nthreads
+    # all host threads this process may use (torchrun pins OMP_NUM_THREADS=1, so ask the OS instead)
+    cores = (len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()) if nthreads <= 0 else nthreads
 
     def run(B, T):
         ww = Workload("cpu_sample", H=w.H, B=B, T=T, lower_bound=w.lower_bound, state_in=w.state_in,

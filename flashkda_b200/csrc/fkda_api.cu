@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "../../include/fkda.h"
 #include "fkda_common.cuh"
@@ -89,7 +90,7 @@ int validate(const fkda_fwd_params* p, Layout* L) {
   if (p->H > 65535) return fail(FKDA_ERR_INVALID_ARGUMENT, "H must be at most 65535");
   if (p->N * p->H > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "N*H exceeds 2^31-1 chains");
   if (!make_layout(T_total, p->H, p->N, p->cu_seqlens ? 1 : 0, p->T, L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
-  if (L->chunks_per_head > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "too many chunks for one call");
+  if (L->chunks_per_head * p->H > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "too many (chunk, head) pairs for one call");
   if (!p->workspace) return fail(FKDA_ERR_INVALID_ARGUMENT, "workspace is NULL");
   if (reinterpret_cast<uintptr_t>(p->workspace) & 255u) return fail(FKDA_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
   if (p->workspace_bytes < L->total_bytes)
@@ -126,6 +127,10 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   q.total_chunks = static_cast<int>(L.chunks_per_head);
   q.scale = p->scale;
   q.gate_scale = static_cast<float>(static_cast<double>(p->lower_bound) * 1.4426950408889634);
+  {
+    static const char* dbg_env = getenv("FKDA_PREPARE_SKIP");   // tuning aid, unset in production
+    q.dbg = dbg_env ? atoi(dbg_env) : 0;
+  }
   e = fkda::launch_prepare(q, stream);
   if (e != cudaSuccess) return cuda_fail(e, "prepare launch");
   return FKDA_OK;

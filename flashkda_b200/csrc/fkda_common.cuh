@@ -145,6 +145,15 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, uint32_t smem_src, uint32_t
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
                : "memory");
 }
+// 16-byte asynchronous global->shared copy; `src_bytes` = 0 writes zeros instead (the address must still be valid).
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Fire-and-forget prefetch of a contiguous global range into L2 (16-byte aligned address, size multiple of 16).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
@@ -284,6 +293,7 @@ struct PrepParams {
   int total_chunks;            // records per head (upper bound for varlen)
   float scale;
   float gate_scale;            // lower_bound * log2(e)
+  int dbg;                     // tuning aid: bit mask of phases to skip (0 in production)
 };
 
 struct ScanParams {

@@ -71,21 +71,28 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
 // ---- shared-memory plan of the prepare kernel (byte offsets) --------------------------------------
 // The record under construction occupies [0, kRecBytes).  Its WP and UP regions are written last,
 // so until the intra-chunk products are done they hold three temporaries.
+// Raw q, k, g tiles are staged at the start of the record image ([3][32 tok][256 B], 16-byte chunks XOR-swizzled by
+// the token index) before anything of the record is written; v is staged the same way in its own buffer and stays.
+constexpr int kSmStageQKG = 0;               // 24 KB, dead after P1
 constexpr int kSmKM = kRecWP;                // [32][128] k-, relative to own sub-block start   (dead after P4)
 constexpr int kSmKP1 = kRecUP;               // [16][128] k+ of sub-block 1 rel. to its own start (dead after P4)
 constexpr int kSmQP1 = kRecUP + 4096;        // [16][128] q+ of sub-block 1 rel. to its own start (dead after P4)
 constexpr int kSmKPP = kRecBytes;            // [32][128] k+ from chunk start (rows 0-15 double as sub-block operand)
 constexpr int kSmKR0 = kSmKPP + 8192;        // [16][128] k of sub-block 0 decayed to the sub-block end
-constexpr int kSmV = kSmKR0 + 4096;          // [32][128] v
+constexpr int kSmV = kSmKR0 + 4096;          // [32 tok][256 B] v, chunks XOR-swizzled by the token index
 constexpr int kSmTB = kSmV + 8192;           // [32][32] bf16 T diag(beta)
-constexpr int kSmA = kSmTB + 2048;           // [32][33] fp32 A
-constexpr int kSmT = kSmA + 4224;            // [32][33] fp32 T
-constexpr int kSmX = kSmT + 4224;            // [16][17] fp32
-constexpr int kSmTot = kSmX + 1088;          // [2][128] fp32 sub-block log2 decays
+constexpr int kLd = 36;                      // row stride (floats) of the small fp32 matrices: 16-byte aligned rows
+constexpr int kSmA = kSmTB + 2048;           // [32][36] fp32 A
+constexpr int kSmT = kSmA + 32 * kLd * 4;    // [32][36] fp32 T
+constexpr int kSmX = kSmT + 32 * kLd * 4;    // [16][36] fp32
+constexpr int kSmTot = kSmX + 16 * kLd * 4;          // [2][128] fp32 sub-block log2 decays
 constexpr int kSmSsq = kSmTot + 1024;        // [2][32][4] fp32 partial sums of squares
 constexpr int kSmBeta = kSmSsq + 1024;       // [32] fp32 sigmoid(beta)
 constexpr int kPrepSmemBytes = kSmBeta + 128;
 static_assert(kPrepSmemBytes * 3 + 3 * 1024 <= 228 * 1024, "three CTAs per SM");
+
+// byte offset of 16-byte chunk `chunk` of token row `row` in a swizzled [32][256 B] staging tile
+__device__ __forceinline__ int stage_off(int row, int chunk) { return row * 256 + ((chunk ^ (row & 7)) << 4); }
 
 __device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
   f[0] = bf_lo(w.x); f[1] = bf_hi(w.x); f[2] = bf_lo(w.y); f[3] = bf_hi(w.y);
@@ -118,8 +125,10 @@ __device__ __forceinline__ void block16_product(uint32_t a_base, uint32_t b_base
 __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int h = blockIdx.y;
-  const int gc = blockIdx.x;
+  // consecutive CTAs take consecutive heads of the same chunk: together they read whole [H x 256 B] token rows,
+  // which keeps concurrent DRAM accesses inside the same pages
+  const int h = static_cast<int>(blockIdx.x % static_cast<unsigned>(p.H));
+  const int gc = static_cast<int>(blockIdx.x / static_cast<unsigned>(p.H));
 
   // ---- chunk -> (sequence, first token, valid length) -------------------------------------------
   int64_t t0;
@@ -158,23 +167,27 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   float* s_A = reinterpret_cast<float*>(smem + kSmA);
   float* s_T = reinterpret_cast<float*>(smem + kSmT);
   float* s_X = reinterpret_cast<float*>(smem + kSmX);
+  const uint32_t sbase = smem_u32(smem);
 
   // ---- P1: loads, partial sums of squares, v tile, beta, gate and its in-sub-block running sum ------
   uint4 qw[2], kw[2];
   float G[2][8];      // log2 cumulative decay relative to the sub-block start
   {
-    uint4 gw[2];
-    const uint4 z = make_uint4(0, 0, 0, 0);
+    // coalesced asynchronous loads: 16 consecutive lanes fetch one 256-byte token row of one tensor
+    {
+      const int lrow = tid >> 4, lchunk = tid & 15;
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const int row = hf ? row1 : row0;
-      const bool valid = row < len;
-      const size_t off = (static_cast<size_t>(t0 + row) * p.H + h) * kD + 8 * j;
-      qw[hf] = valid ? __ldg(reinterpret_cast<const uint4*>(p.q + off)) : z;
-      kw[hf] = valid ? __ldg(reinterpret_cast<const uint4*>(p.k + off)) : z;
-      gw[hf] = valid ? __ldg(reinterpret_cast<const uint4*>(p.g + off)) : z;
-      const uint4 vw = valid ? __ldg(reinterpret_cast<const uint4*>(p.v + off)) : z;
-      *reinterpret_cast<uint4*>(smem + kSmV + core_off(row, 8 * j, kD)) = vw;
+      for (int hf = 0; hf < 2; ++hf) {
+        const int row = lrow + 16 * hf;
+        const bool valid = (row < len) && !(p.dbg & 64);
+        const size_t off = (static_cast<size_t>(t0 + (valid ? row : 0)) * p.H + h) * kD + 8 * lchunk;
+        const uint32_t nbytes = valid ? 16u : 0u;
+        const uint32_t dst = sbase + stage_off(row, lchunk);
+        cp_async16(dst + kSmStageQKG, p.q + off, nbytes);
+        cp_async16(dst + kSmStageQKG + 8192, p.k + off, nbytes);
+        cp_async16(dst + kSmStageQKG + 16384, p.g + off, nbytes);
+        cp_async16(dst + kSmV, p.v + off, nbytes);
+      }
     }
     if (tid < kChunk) {
       float b = 0.f;
@@ -190,6 +203,16 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
       hab[0] = ha * b0.x; hab[1] = ha * b0.y; hab[2] = ha * b0.z; hab[3] = ha * b0.w;
       hab[4] = ha * b1.x; hab[5] = ha * b1.y; hab[6] = ha * b1.z; hab[7] = ha * b1.w;
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    uint4 gw[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;
+      qw[hf] = *reinterpret_cast<const uint4*>(smem + kSmStageQKG + stage_off(row, j));
+      kw[hf] = *reinterpret_cast<const uint4*>(smem + kSmStageQKG + 8192 + stage_off(row, j));
+      gw[hf] = *reinterpret_cast<const uint4*>(smem + kSmStageQKG + 16384 + stage_off(row, j));
     }
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
@@ -212,6 +235,11 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       }
       unpack8(gw[hf], f);
       const bool valid = row < len;
+      if (p.dbg & 32) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) G[hf][i] = f[i];
+        continue;
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float x = valid ? fmaf(tanh_approx(fmaf(f[i], ha, hab[i])), hgs, hgs) : 0.f;
@@ -238,6 +266,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   }
   __syncthreads();
 
+  if (p.dbg & 16) goto store_record;
   // ---- P2: norms and every decayed operand ------------------------------------------------------------
   {
     // per-channel factors: fa = 2^(own sub-block total), fb = 2^(other sub-block total)
@@ -304,8 +333,8 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   }
   __syncthreads();
 
+  if (p.dbg & 1) goto store_record;
   // ---- P4: the six 16x16x128 intra-chunk products (one warp each) --------------------------------------
-  const uint32_t sbase = smem_u32(smem);
   if (warp < 6) {
     const int which = warp % 3;            // 0: (0,0) block, 1: (1,1) block, 2: (1,0) block
     const bool is_m = warp >= 3;           // q-side (M) instead of k-side (A)
@@ -336,8 +365,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
             x0 *= br;
             x1 *= br;
           }
-          s_A[r * 33 + c] = x0;
-          s_A[r * 33 + c + 1] = x1;
+          *reinterpret_cast<float2*>(s_A + r * kLd + c) = make_float2(x0, x1);
         } else {
           if (which != 2) {               // lower triangle including the diagonal
             x0 = (lc <= lr) ? x0 : 0.f;
@@ -358,51 +386,73 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   }
   __syncthreads();
 
-  // ---- P5: T = (I + A)^-1 -------------------------------------------------------------------------------
+  if (p.dbg & 2) goto after_p5;
+  // ---- P5: T = (I + A)^-1 and TB = T diag(beta), all inside warp 0 (no block-wide barriers) -------------------
   if (warp == 0) {
-    // forward substitution, one column of one diagonal block per lane: x_i = [i==c] - sum_{j<i} A_ij x_j
-    const int b = lane >> 4, c = lane & 15;
-    float x[16];
+    {
+      // forward substitution, one column of one diagonal block per lane: x_i = [i==c] - sum_{j<i} A_ij x_j
+      const int b = lane >> 4, c = lane & 15;
+      float x[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float acc = (i == c) ? 1.f : 0.f;
+      for (int i = 0; i < 16; ++i) {
+        float acc = (i == c) ? 1.f : 0.f;
 #pragma unroll
-      for (int jj = 0; jj < i; ++jj) acc = fmaf(-s_A[(b * 16 + i) * 33 + b * 16 + jj], x[jj], acc);
-      x[i] = acc;
-      s_T[(b * 16 + i) * 33 + b * 16 + c] = acc;
+        for (int jj = 0; jj < i; ++jj) acc = fmaf(-s_A[(b * 16 + i) * kLd + b * 16 + jj], x[jj], acc);
+        x[i] = acc;
+        s_T[(b * 16 + i) * kLd + b * 16 + c] = acc;
+      }
     }
-  }
-  __syncthreads();
-  {
-    const int i = tid >> 4, c = tid & 15;   // X = A_10 T_00
-    float acc = 0.f;
+    __syncwarp();
+    const int i = lane >> 1, c8 = (lane & 1) * 8;     // each lane: 8 consecutive entries of one row of a 16x16 product
+    {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // X = A_10 T_00
 #pragma unroll
-    for (int jj = 0; jj < 16; ++jj) acc = fmaf(s_A[(16 + i) * 33 + jj], s_T[jj * 33 + c], acc);
-    s_X[i * 17 + c] = acc;
-  }
-  __syncthreads();
-  {
-    const int i = tid >> 4, c = tid & 15;   // T_10 = -T_11 X
-    float acc = 0.f;
-#pragma unroll
-    for (int jj = 0; jj < 16; ++jj) acc = fmaf(-s_T[(16 + i) * 33 + 16 + jj], s_X[jj * 17 + c], acc);
-    s_T[(16 + i) * 33 + c] = acc;
-  }
-  __syncthreads();
-  {
-    // TB = T diag(beta) as a bf16 core-layout operand; 4 consecutive columns per thread
-    const int i = tid >> 3, c4 = (tid & 7) * 4;
-    float t[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int c = c4 + e;
-      const bool nz = (c <= i) && !(i < 16 && c >= 16);
-      t[e] = nz ? s_T[i * 33 + c] * s_beta[c] : 0.f;
+      for (int jj = 0; jj < 16; ++jj) {
+        const float a = s_A[(16 + i) * kLd + jj];
+        const float4 t0 = *reinterpret_cast<const float4*>(s_T + jj * kLd + c8);
+        const float4 t1 = *reinterpret_cast<const float4*>(s_T + jj * kLd + c8 + 4);
+        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]); acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
+        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]); acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
+      }
+      *reinterpret_cast<float4*>(s_X + i * kLd + c8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(s_X + i * kLd + c8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
-    *reinterpret_cast<uint2*>(smem + kSmTB + core_off(i, c4, kChunk)) = make_uint2(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]));
+    __syncwarp();
+    {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // T_10 = -T_11 X
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        const float a = -s_T[(16 + i) * kLd + 16 + jj];
+        const float4 t0 = *reinterpret_cast<const float4*>(s_X + jj * kLd + c8);
+        const float4 t1 = *reinterpret_cast<const float4*>(s_X + jj * kLd + c8 + 4);
+        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]); acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
+        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]); acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
+      }
+      *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    __syncwarp();
+    {
+      // TB = T diag(beta) as a bf16 core-layout operand; lane = row
+      const int r = lane;
+      uint8_t* row = smem + kSmTB + (r >> 3) * 512 + (r & 7) * 16;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {          // 8 columns per 16-byte store
+        float t[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int c = q4 * 8 + e;
+          const bool nz = (c <= r) && !(r < 16 && c >= 16);
+          t[e] = nz ? s_T[r * kLd + c] * s_beta[c] : 0.f;
+        }
+        *reinterpret_cast<uint4*>(row + q4 * 128) = pack8(t);
+      }
+    }
   }
   __syncthreads();
 
+after_p5:
+  if (p.dbg & 4) goto store_record;
   // ---- P6: w' = TB k+ (warps 0-3, 32 k-columns each) ; u'^T = v^T TB^T (warps 4-7, 32 v-rows each) -----
   {
     const int mi = lane >> 3, r = lane & 7;
@@ -449,7 +499,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
         uint32_t a[2][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)     // A = v^T: transposed loads of (token group 2ks + (mi>>1), v tile vc0 + 2mt + (mi&1))
-          ldsm_x4_trans(sbase + kSmV + (2 * ks + (mi >> 1)) * 2048 + (vc0 + 2 * mt + (mi & 1)) * 128 + r * 16, a[mt][0], a[mt][1],
+          ldsm_x4_trans(sbase + kSmV + stage_off((2 * ks + (mi >> 1)) * 8 + r, vc0 + 2 * mt + (mi & 1)), a[mt][0], a[mt][1],
                         a[mt][2], a[mt][3]);
 #pragma unroll
         for (int np = 0; np < 2; ++np) {   // B = TB^T: plain loads of (token group 2np + (mi>>1), k tile 2ks + (mi&1))
@@ -472,9 +522,10 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
                   pack_bf16(acc[mt][2 * np + 1][0], acc[mt][2 * np + 1][1]), pack_bf16(acc[mt][2 * np + 1][2], acc[mt][2 * np + 1][3]));
     }
   }
+store_record:
   fence_proxy_async_smem();
   __syncthreads();
-  if (tid == 0) {
+  if (tid == 0 && !(p.dbg & 8)) {
     uint8_t* dst = p.records + (static_cast<size_t>(h) * p.total_chunks + gc) * kRecBytes;
     bulk_s2g(dst, sbase, kRecBytes);
     bulk_commit();
@@ -491,7 +542,7 @@ cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes);
   if (e != cudaSuccess) return e;
   if (p.total_chunks == 0 || p.H == 0) return cudaSuccess;
-  dim3 grid(p.total_chunks, p.H);
+  const unsigned grid = static_cast<unsigned>(p.total_chunks) * static_cast<unsigned>(p.H);
   prepare_kernel<<<grid, 256, kPrepSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
