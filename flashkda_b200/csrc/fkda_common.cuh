@@ -115,11 +115,14 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // up (`*abort_flag != 0`); the caller then leaves its loop, so a lost arrival can never hang
 // the GPU.  Returns true when the barrier phase completed.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// `backoff_ns` > 0 makes a waiter that is not on the critical path sleep between probes, so that it does not take
+// issue slots from the warps that are.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if (backoff_ns) __nanosleep(backoff_ns);
     if (((++spins) & 63u) == 0u) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {

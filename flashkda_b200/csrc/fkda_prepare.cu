@@ -168,6 +168,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   float* s_T = reinterpret_cast<float*>(smem + kSmT);
   float* s_X = reinterpret_cast<float*>(smem + kSmX);
   const uint32_t sbase = smem_u32(smem);
+  uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + gc) * kRecBytes;
 
   // ---- P1: loads, partial sums of squares, v tile, beta, gate and its in-sub-block running sum ------
   uint4 qw[2], kw[2];
@@ -331,7 +332,15 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       }
     }
   }
+  fence_proxy_async_smem();
   __syncthreads();
+  if (tid == 0 && !(p.dbg & 8)) {
+    // the parts of the record that are final after P2 leave now and overlap with the remaining phases
+    bulk_s2g(rec_dst + kRecKR, sbase + kRecKR, 8192);
+    bulk_s2g(rec_dst + kRecE, sbase + kRecE, 512);
+    bulk_s2g(rec_dst + kRecQP, sbase + kRecQP, 8192);
+    bulk_commit();
+  }
 
   if (p.dbg & 1) goto store_record;
   // ---- P4: the six 16x16x128 intra-chunk products (one warp each) --------------------------------------
@@ -389,7 +398,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   if (p.dbg & 2) goto after_p5;
   // ---- P5: T = (I + A)^-1 and TB = T diag(beta), all inside warp 0 (no block-wide barriers) -------------------
   if (warp == 0) {
-    {
+    if (!(p.dbg & 512)) {
       // forward substitution, one column of one diagonal block per lane: x_i = [i==c] - sum_{j<i} A_ij x_j
       const int b = lane >> 4, c = lane & 15;
       float x[16];
@@ -404,7 +413,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
     }
     __syncwarp();
     const int i = lane >> 1, c8 = (lane & 1) * 8;     // each lane: 8 consecutive entries of one row of a 16x16 product
-    {
+    if (!(p.dbg & 256)) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // X = A_10 T_00
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
@@ -418,7 +427,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       *reinterpret_cast<float4*>(s_X + i * kLd + c8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     __syncwarp();
-    {
+    if (!(p.dbg & 256)) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // T_10 = -T_11 X
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
@@ -526,8 +535,9 @@ store_record:
   fence_proxy_async_smem();
   __syncthreads();
   if (tid == 0 && !(p.dbg & 8)) {
-    uint8_t* dst = p.records + (static_cast<size_t>(h) * p.total_chunks + gc) * kRecBytes;
-    bulk_s2g(dst, sbase, kRecBytes);
+    bulk_s2g(rec_dst + kRecMQK, sbase + kRecMQK, 2048);
+    bulk_s2g(rec_dst + kRecWP, sbase + kRecWP, 8192);
+    bulk_s2g(rec_dst + kRecUP, sbase + kRecUP, 8192);
     bulk_commit();
     bulk_wait_read0();
   }

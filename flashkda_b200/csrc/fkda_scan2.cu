@@ -69,8 +69,8 @@ enum {
 };
 static_assert(BAR_COUNT * 8 <= 256, "barrier area");
 
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  const bool ok = mbar_wait(bar, parity, abort_flag);
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t backoff_ns = 0) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, backoff_ns);
   return __all_sync(0xffffffffu, ok);
 }
 // use count of the X/Y buffers: chunk c >= 1 uses buffer c & 1
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       int issued = 0;
       for (int c = 0; c < nchunks; ++c) {
         const int s = c % kStages, k = c / kStages;
-        if (k > 0 && !mbar_wait(bar(BAR_EMPTY + s), (k - 1) & 1, abort_flag)) { failed = true; break; }
+        if (k > 0 && !mbar_wait(bar(BAR_EMPTY + s), (k - 1) & 1, abort_flag, 64)) { failed = true; break; }
         FKDA_TRACE(4, c, 0);
         mbar_arrive_expect_tx(bar(BAR_FULL + s), kRecBytes);
         bulk_g2s(sbase + kSmStage + s * kRecBytes, rec0 + static_cast<size_t>(c) * kRecBytes, kRecBytes, bar(BAR_FULL + s));
@@ -180,7 +180,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         const uint32_t rec = sbase + kSmStage + (c % kStages) * kRecBytes;
         const uint32_t ut = tmem + kColUt + 16 * (c & 1);
         const bool more = c + 1 < nchunks;
+        FKDA_TRACE(0, c, 6);
         if (!mbar_wait(bar(BAR_SBDREADY), c & 1, abort_flag)) { failed = true; break; }
+        FKDA_TRACE(0, c, 7);
         if (!mbar_wait(bar(BAR_UREADY), c & 1, abort_flag)) { failed = true; break; }
         tc_fence_after();
         FKDA_TRACE(0, c, 0);
@@ -244,11 +246,11 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     if (lane == 0) {
       constexpr uint32_t idesc_n32 = umma_idesc_bf16(128, 32, 0, 0);
       for (int c = 1; c < nchunks; ++c) {
-        if (!mbar_wait(full_bar(c - 1), full_par(c - 1), abort_flag)) { failed = true; break; }
-        if (!mbar_wait(full_bar(c), full_par(c), abort_flag)) { failed = true; break; }
+        if (!mbar_wait(full_bar(c - 1), full_par(c - 1), abort_flag, 64)) { failed = true; break; }
+        if (!mbar_wait(full_bar(c), full_par(c), abort_flag, 64)) { failed = true; break; }
         if (c >= 3) {   // accumulator read by the X/Y epilogue of chunk c-2, its operands consumed by the U products
-          if (!mbar_wait(bar(BAR_XREADY + (c & 1)), xy_use(c - 2) & 1u, abort_flag)) { failed = true; break; }
-          if (!mbar_wait(bar(BAR_XYFREE + (c & 1)), xy_use(c - 2) & 1u, abort_flag)) { failed = true; break; }
+          if (!mbar_wait(bar(BAR_XREADY + (c & 1)), xy_use(c - 2) & 1u, abort_flag, 64)) { failed = true; break; }
+          if (!mbar_wait(bar(BAR_XYFREE + (c & 1)), xy_use(c - 2) & 1u, abort_flag, 64)) { failed = true; break; }
         }
         tc_fence_after();
         FKDA_TRACE(0, c, 4);
@@ -360,39 +362,31 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     // ---- per chunk: decay the updated state for the next chunk and refresh its bf16 copy ------------------
     for (int c = 0; c + 1 < nchunks && !failed; ++c) {
       if (!warp_wait(full_bar(c + 1), full_par(c + 1), abort_flag)) { failed = true; break; }
+      // The decay factors of the next chunk are the same for every lane.  Each lane fetches two of this group's
+      // 64 factors now (before the state update lands) and they are handed round by shuffles below: no
+      // shared-memory latency between the TMEM load and store, and no 64 extra registers.
+      const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 64 * grp;
+      const float e_lo = e[lane], e_hi = e[32 + lane];
       if (!warp_wait(bar(BAR_SFULL), c & 1, abort_flag)) { failed = true; break; }
-      const int trole = (warp == 8) ? 2 : 5;
-      const bool tr_on = (warp == 8 || warp == 12) && lane == 0;
+      const int trole = 2;
+      const bool tr_on = (warp == 8) && lane == 0;
       if (tr_on) FKDA_TRACE(trole, c, 0);
       tc_fence_after();
       if (tr_on) FKDA_TRACE(trole, c, 1);
-      const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 64 * grp;
       uint32_t x0[32], x1[32], y[16];
       tmem_ld32(tq + kColS + 64 * grp, x0);
       tmem_ld32(tq + kColS + 64 * grp + 32, x1);
       tmem_wait_ld();
       if (tr_on) FKDA_TRACE(trole, c, 2);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 f = *reinterpret_cast<const float4*>(e + 4 * i);
-        x0[4 * i] = __float_as_uint(__uint_as_float(x0[4 * i]) * f.x);
-        x0[4 * i + 1] = __float_as_uint(__uint_as_float(x0[4 * i + 1]) * f.y);
-        x0[4 * i + 2] = __float_as_uint(__uint_as_float(x0[4 * i + 2]) * f.z);
-        x0[4 * i + 3] = __float_as_uint(__uint_as_float(x0[4 * i + 3]) * f.w);
-      }
+      for (int i = 0; i < 32; ++i) x0[i] = __float_as_uint(__uint_as_float(x0[i]) * __shfl_sync(0xffffffffu, e_lo, i));
       if (tr_on) FKDA_TRACE(trole, c, 6);
       tmem_st32(tq + kColS + 64 * grp, x0);
       pack32(x0, y);
       tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp, y);
       if (tr_on) FKDA_TRACE(trole, c, 7);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 f = *reinterpret_cast<const float4*>(e + 32 + 4 * i);
-        x1[4 * i] = __float_as_uint(__uint_as_float(x1[4 * i]) * f.x);
-        x1[4 * i + 1] = __float_as_uint(__uint_as_float(x1[4 * i + 1]) * f.y);
-        x1[4 * i + 2] = __float_as_uint(__uint_as_float(x1[4 * i + 2]) * f.z);
-        x1[4 * i + 3] = __float_as_uint(__uint_as_float(x1[4 * i + 3]) * f.w);
-      }
+      for (int i = 0; i < 32; ++i) x1[i] = __float_as_uint(__uint_as_float(x1[i]) * __shfl_sync(0xffffffffu, e_hi, i));
       tmem_st32(tq + kColS + 64 * grp + 32, x1);
       pack32(x1, y);
       tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp + 16, y);
@@ -403,6 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       __syncwarp();
       if (lane == 0) {
         if (tr_on) FKDA_TRACE(trole, c, 3);
+        FKDA_TRACE(5, c, warp - 8);          // arrival time of each of the eight state warps
         mbar_arrive(bar(BAR_SBDREADY));
         mbar_arrive(bar(BAR_EMPTY + (c + 1) % kStages));    // done with e of record c+1
       }
@@ -445,7 +440,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + kSmOutStg + qd * 2048);   // [32 tok][32 v]
     auto xy_epilogue = [&](int c) -> bool {     // accumulator lanes 0-31 = X rows, 32-63 = Y rows (warps on quadrants 0, 1)
       if (qd >= 2) return true;
-      if (!warp_wait(bar(BAR_XFULL + (c & 1)), xy_use(c) & 1u, abort_flag)) return false;
+      if (!warp_wait(bar(BAR_XFULL + (c & 1)), xy_use(c) & 1u, abort_flag, 32)) return false;
       tc_fence_after();
       if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 0);
       uint32_t x[32], y[16];
@@ -468,7 +463,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     for (int c = 0; c < nchunks; ++c) {
       if (c == 0 && nchunks > 1 && !xy_epilogue(1)) { failed = true; break; }
       if (c + 2 < nchunks && !xy_epilogue(c + 2)) { failed = true; break; }
-      if (!warp_wait(bar(BAR_OFULL + (c & 1)), (c >> 1) & 1, abort_flag)) { failed = true; break; }
+      if (!warp_wait(bar(BAR_OFULL + (c & 1)), (c >> 1) & 1, abort_flag, 32)) { failed = true; break; }
       tc_fence_after();
       if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 2);
       uint32_t o[32];
