@@ -16,6 +16,7 @@ _lib = None
 
 FLAG_SCAN_SIMT = 0x1
 FLAG_SCAN_PLAIN = 0x2
+FLAG_SCAN_LOOKAHEAD = 0x4
 _STATE_NONE, _STATE_BF16, _STATE_FP32 = 0, 1, 2
 
 

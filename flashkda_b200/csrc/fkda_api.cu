@@ -15,6 +15,7 @@ cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
+cudaError_t launch_scan_short(const ScanParams& p, int sm_count, cudaStream_t stream);
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
 cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* g, const __nv_bfloat16* beta,
@@ -155,7 +156,13 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   cudaError_t e;
   if (p->flags & FKDA_FLAG_SCAN_SIMT) e = fkda::launch_scan_simt(s, stream);
   else if (p->flags & FKDA_FLAG_SCAN_PLAIN) e = fkda::launch_scan(s, stream);
-  else e = fkda::launch_scan2(s, stream);
+  else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->cu_seqlens == nullptr && p->T > 0 && p->T <= 2 * fkda::kChunk) {
+    // many short chains: the state-I/O-oriented persistent kernel
+    int dev = 0, sms = 0;
+    e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess) e = fkda::launch_scan_short(s, sms, stream);
+  } else e = fkda::launch_scan2(s, stream);
   if (e != cudaSuccess) return cuda_fail(e, "scan launch");
   return FKDA_OK;
 }

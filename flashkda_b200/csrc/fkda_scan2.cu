@@ -65,6 +65,7 @@ enum {
   BAR_SFULL = BAR_XYFREE + 2,      // state update of a chunk complete
   BAR_UREADY,                      // U^T of a chunk in tensor memory
   BAR_SBDREADY,                    // decayed state + its bf16 copy ready
+  BAR_APASS,                       // issuer 2 has consumed the SBDREADY phase it needs for its next chunk
   BAR_COUNT
 };
 static_assert(BAR_COUNT * 8 <= 256, "barrier area");
@@ -83,6 +84,7 @@ __device__ __forceinline__ void pack32(const uint32_t (&x)[32], uint32_t (&y)[16
 
 __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, unsigned long long* trace_buf) {
   unsigned long long* trace = (blockIdx.x == 0) ? trace_buf : nullptr;
+  if (threadIdx.x == 0) FKDA_TRACE(4, 31, 1);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -136,6 +138,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     mbar_init(bar(BAR_SFULL), 1);
     mbar_init(bar(BAR_UREADY), 4);
     mbar_init(bar(BAR_SBDREADY), 8);
+    mbar_init(bar(BAR_APASS), 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -146,6 +149,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (tid == 0) FKDA_TRACE(4, 31, 0);
 
   bool failed = false;
 
@@ -184,6 +188,10 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         if (!mbar_wait(bar(BAR_SBDREADY), c & 1, abort_flag)) { failed = true; break; }
         FKDA_TRACE(0, c, 7);
         if (!mbar_wait(bar(BAR_UREADY), c & 1, abort_flag)) { failed = true; break; }
+        // The state update below lets the state warps complete the next SBDREADY phase.  Issuer 2 watches that barrier
+        // by parity too, one phase behind: it must have seen its phase (for chunk c+1) before the next one can
+        // complete, or the parity would alias.
+        if (more && !mbar_wait(bar(BAR_APASS), (c + 1) & 1, abort_flag)) { failed = true; break; }
         tc_fence_after();
         FKDA_TRACE(0, c, 0);
         {  // S^T += U^T kr : kr [32 tok][128 k] read MN-major (k-adjacent core matrices 128 B apart, token groups 2048 B)
@@ -230,6 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
           if (!mbar_wait(bar(BAR_OFREE + (c & 1)), ((c - 2) >> 1) & 1, abort_flag)) { failed = true; break; }
         }
         if (!mbar_wait(bar(BAR_SBDREADY), (c < 2 ? 0 : c - 1) & 1, abort_flag)) { failed = true; break; }
+        mbar_arrive(bar(BAR_APASS));
         tc_fence_after();
         FKDA_TRACE(0, c, 2);
         const uint32_t sbd = tmem + kColSbd + 64 * (c & 1);
@@ -308,50 +317,67 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     const size_t row_off = ((static_cast<size_t>(n) * p.H + h) * kD + v) * kD;   // row v of this chain's state
 
     // ---- initial state: S <- e_0 S_init; bf16 copies of S_init (buffer 0) and e_0 S_init (buffer 1) --------
-    bool ok = true;
-    if (nchunks > 0) ok = warp_wait(full_bar(0), 0, abort_flag);
-    if (ok) {
-      const float* e0 = reinterpret_cast<const float*>(smem + kSmStage + kRecE);
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        const int cb = 2 * grp + half;     // 32-column block
-        uint32_t x[32], y[16];
-        if (p.initial_state != nullptr) {
-          if (p.state_fp32) {
-            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.initial_state) + row_off + cb * 32);
+    // All global loads of this thread's 64 state values are issued before anything is waited for.
+    uint32_t xi[2][32];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 f = __ldg(src + i);
-              x[4 * i] = __float_as_uint(f.x); x[4 * i + 1] = __float_as_uint(f.y);
-              x[4 * i + 2] = __float_as_uint(f.z); x[4 * i + 3] = __float_as_uint(f.w);
-            }
-          } else {
-            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + row_off + cb * 32);
+    for (int half = 0; half < 2; ++half) {
+      const int cb = 2 * grp + half;     // 32-column block
+      if (p.initial_state != nullptr) {
+        if (p.state_fp32) {
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.initial_state) + row_off + cb * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint4 w = __ldg(src + i);
-              x[8 * i] = w.x << 16; x[8 * i + 1] = w.x & 0xffff0000u; x[8 * i + 2] = w.y << 16; x[8 * i + 3] = w.y & 0xffff0000u;
-              x[8 * i + 4] = w.z << 16; x[8 * i + 5] = w.z & 0xffff0000u; x[8 * i + 6] = w.w << 16; x[8 * i + 7] = w.w & 0xffff0000u;
-            }
+          for (int i = 0; i < 8; ++i) {
+            const float4 f = __ldg(src + i);
+            xi[half][4 * i] = __float_as_uint(f.x); xi[half][4 * i + 1] = __float_as_uint(f.y);
+            xi[half][4 * i + 2] = __float_as_uint(f.z); xi[half][4 * i + 3] = __float_as_uint(f.w);
           }
         } else {
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + row_off + cb * 32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] = 0u;
+          for (int i = 0; i < 4; ++i) {
+            const uint4 w = __ldg(src + i);
+            xi[half][8 * i] = w.x << 16; xi[half][8 * i + 1] = w.x & 0xffff0000u;
+            xi[half][8 * i + 2] = w.y << 16; xi[half][8 * i + 3] = w.y & 0xffff0000u;
+            xi[half][8 * i + 4] = w.z << 16; xi[half][8 * i + 5] = w.z & 0xffff0000u;
+            xi[half][8 * i + 6] = w.w << 16; xi[half][8 * i + 7] = w.w & 0xffff0000u;
+          }
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) xi[half][i] = 0u;
+      }
+    }
+    if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 0);
+    bool ok = true;
+    if (nchunks > 0) ok = warp_wait(full_bar(0), 0, abort_flag);
+    if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 1);
+    if (ok) {
+      float e_l = 1.f, e_h = 1.f;         // this lane's two of the group's 64 decay factors of chunk 0
+      if (nchunks > 0) {
+        const float* e0 = reinterpret_cast<const float*>(smem + kSmStage + kRecE) + 64 * grp;
+        e_l = e0[lane];
+        e_h = e0[32 + lane];
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int cb = 2 * grp + half;
+        uint32_t y[16];
         if (nchunks > 0) {
-          pack32(x, y);
+          pack32(xi[half], y);
           tmem_st16(tq + kColSbd + 0 + cb * 16, y);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e0[cb * 32 + i]);
-          pack32(x, y);
+          for (int i = 0; i < 32; ++i)
+            xi[half][i] = __float_as_uint(__uint_as_float(xi[half][i]) * __shfl_sync(0xffffffffu, half ? e_h : e_l, i));
+          pack32(xi[half], y);
           tmem_st16(tq + kColSbd + 64 + cb * 16, y);
         }
-        tmem_st32(tq + kColS + cb * 32, x);
+        tmem_st32(tq + kColS + cb * 32, xi[half]);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
+        if (warp == 8) FKDA_TRACE(2, 30, 2);
         mbar_arrive(bar(BAR_SBDREADY));
         if (nchunks > 0) mbar_arrive(bar(BAR_EMPTY + 0));   // done with e of record 0
       }
@@ -409,6 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       if (nchunks > 0) ok2 = warp_wait(bar(BAR_SFULL), (nchunks - 1) & 1, abort_flag);
       if (ok2) {
         tc_fence_after();
+        if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 3);
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           const int cb = 2 * grp + half;
@@ -491,6 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     }
   }
 
+  if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 4);
   if (failed || *abort_flag) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
 
   // ---- common exit: every thread arrives here, TMEM goes back ------------------------------------------------

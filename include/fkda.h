@@ -35,6 +35,7 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 /* flags */
 #define FKDA_FLAG_SCAN_SIMT 0x1u /* evaluate the recurrence on CUDA cores (verification aid, slow) */
 #define FKDA_FLAG_SCAN_PLAIN 0x2u /* tcgen05 recurrence without look-ahead (kept for cross-checking) */
+#define FKDA_FLAG_SCAN_LOOKAHEAD 0x4u /* always use the look-ahead recurrence kernel, also for short chains */
 
 typedef struct fkda_fwd_params {
   /* bf16 [B*T][H][128], contiguous (reference: q,k,v,g of csrc/flash_kda.cpp:28-33) */
