@@ -59,7 +59,7 @@ bool make_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_pe
     chunks = fixed_ub > chunks ? fixed_ub : chunks;
   }
   L->prefix_off = fkda::kWsHeaderBytes;
-  int64_t prefix_bytes = ((N + 1) * 4 + 255) / 256 * 256;
+  int64_t prefix_bytes = ((2 * N + 1) * 4 + 255) / 256 * 256;   // chunk prefix [N+1] followed by the chain order [N]
   L->records_off = L->prefix_off + prefix_bytes;
   L->chunks_per_head = chunks;
   L->total_bytes = L->records_off + chunks * H * static_cast<int64_t>(fkda::kRecBytes);
@@ -143,6 +143,7 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   s.records = ws + L.records_off;
   s.cu_seqlens = p->cu_seqlens;
   s.chunk_prefix = reinterpret_cast<const int*>(ws + L.prefix_off);
+  s.seq_order = p->cu_seqlens ? s.chunk_prefix + (p->N + 1) : nullptr;
   s.initial_state = p->initial_state;
   s.final_state = p->final_state;
   s.out = static_cast<__nv_bfloat16*>(p->out);

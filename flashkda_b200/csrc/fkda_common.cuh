@@ -303,6 +303,7 @@ struct ScanParams {
   const uint8_t* records;
   const int64_t* cu_seqlens;
   const int* chunk_prefix;
+  const int* seq_order;        // device, N entries: sequences by decreasing length (varlen only), or nullptr
   const void* initial_state;   // [N][H][128 v][128 k] or nullptr
   void* final_state;           // same, or nullptr
   __nv_bfloat16* out;          // [T_total][H][128]

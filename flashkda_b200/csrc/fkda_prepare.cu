@@ -66,6 +66,22 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
     if (threadIdx.x == blockDim.x - 1) carry = incl;
     __syncthreads();
   }
+  // Chain order for the scan: longest sequences first (longest-processing-time-first packing of unequal chains
+  // onto the SMs; the reference walks sequences in the given order).  order[] follows prefix[] in memory.
+  int* order = prefix + (N + 1);
+  if (N <= 4096) {
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+      const int len_n = prefix[n + 1] - prefix[n];
+      int rank = 0;
+      for (int m = 0; m < N; ++m) {
+        const int len_m = prefix[m + 1] - prefix[m];
+        rank += (len_m > len_n) || (len_m == len_n && m < n);
+      }
+      order[rank] = n;
+    }
+  } else {
+    for (int n = threadIdx.x; n < N; n += blockDim.x) order[n] = n;
+  }
 }
 
 // ---- shared-memory plan of the prepare kernel (byte offsets) --------------------------------------

@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
 
   // ---- chain -> tokens and records ---------------------------------------------------------------------
   const int chain = blockIdx.x;
-  const int n = chain / p.H, h = chain - n * p.H;
+  const int slot = chain / p.H, h = chain - slot * p.H;
+  const int n = p.seq_order != nullptr ? p.seq_order[slot] : slot;     // varlen: longest sequences first
   int64_t bos, eos;
   int chunk_base;
   if (p.cu_seqlens != nullptr) {
