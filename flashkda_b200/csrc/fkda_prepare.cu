@@ -287,8 +287,9 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   // ---- P2: norms and every decayed operand ------------------------------------------------------------
   {
     // per-channel factors: fa = 2^(own sub-block total), fb = 2^(other sub-block total)
-    float fa[8], fb[8], fab[8];
+    __nv_bfloat162 fa2[4], fb2[4], fab2[4];
     {
+      float fa[8], fb[8], fab[8];
       const float4 t0v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j);
       const float4 t1v = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j + 4);
       const float to[8] = {t0v.x, t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w};
@@ -297,6 +298,12 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
         fa[i] = ex2f(tot[i]);
         fb[i] = ex2f(to[i]);
         fab[i] = fa[i] * fb[i];
+      }
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        fa2[m] = __floats2bfloat162_rn(fa[2 * m], fa[2 * m + 1]);
+        fb2[m] = __floats2bfloat162_rn(fb[2 * m], fb[2 * m + 1]);
+        fab2[m] = __floats2bfloat162_rn(fab[2 * m], fab[2 * m + 1]);
       }
       if (sb == 0 && r8 == 0) {
         float* e = reinterpret_cast<float*>(smem + kRecE) + 8 * j;
@@ -312,39 +319,47 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
       const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
       const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
-      float qf[8], kf[8], kp[8], qp[8], km[8], t[8];
-      unpack8(qw[hf], qf);
-      unpack8(kw[hf], kf);
+      // The row norm is folded into the decay factor in fp32 (rk 2^G etc.), rounded to bf16 once, and applied to the raw
+      // bf16 inputs with packed bf16x2 multiplies: no unpacking of q/k, half the multiply and conversion count.
+      const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
+      const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
+      __nv_bfloat162 kp[4], qp[4], km[4], t[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float pw = ex2f(G[hf][i]), ipw = ex2f(-G[hf][i]);
-        const float kh = kf[i] * rk, qh = qf[i] * rq;
-        kp[i] = kh * pw;       // decayed from the sub-block start (<= |khat|)
-        qp[i] = qh * pw;
-        km[i] = kh * ipw;      // inverse decay, up to 2^115 for lower_bound = -5
+      for (int m = 0; m < 4; ++m) {
+        const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
+        const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
+        const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
+        const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
+        kp[m] = __hmul2(k2, __floats2bfloat162_rn(rk * pw0, rk * pw1));   // decayed from the sub-block start (<= |khat|)
+        qp[m] = __hmul2(q2, __floats2bfloat162_rn(rq * pw0, rq * pw1));
+        km[m] = __hmul2(k2, __floats2bfloat162_rn(rk * ip0, rk * ip1));   // inverse decay, up to 2^115 for lower_bound = -5
       }
-      *reinterpret_cast<uint4*>(smem + kSmKM + core_off(row, 8 * j, kD)) = pack8(km);
+      auto as_u4 = [](const __nv_bfloat162 (&x)[4]) {
+        return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
+                          *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
+      };
+      *reinterpret_cast<uint4*>(smem + kSmKM + core_off(row, 8 * j, kD)) = as_u4(km);
       if (sb == 0) {
-        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(kp);
-        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(qp);
+        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = as_u4(kp);
+        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = as_u4(qp);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = km[i] * fa[i];      // decayed to the sub-block end
-        *reinterpret_cast<uint4*>(smem + kSmKR0 + core_off(lrow, 8 * j, kD)) = pack8(t);
+        for (int m = 0; m < 4; ++m) t[m] = __hmul2(km[m], fa2[m]);      // decayed to the sub-block end
+        *reinterpret_cast<uint4*>(smem + kSmKR0 + core_off(lrow, 8 * j, kD)) = as_u4(t);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = km[i] * fab[i];     // ... and on through sub-block 1
-        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(t);
+        for (int m = 0; m < 4; ++m) t[m] = __hmul2(km[m], fab2[m]);     // ... and on through sub-block 1
+        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = as_u4(t);
       } else {
-        *reinterpret_cast<uint4*>(smem + kSmKP1 + core_off(lrow, 8 * j, kD)) = pack8(kp);
-        *reinterpret_cast<uint4*>(smem + kSmQP1 + core_off(lrow, 8 * j, kD)) = pack8(qp);
+        *reinterpret_cast<uint4*>(smem + kSmKP1 + core_off(lrow, 8 * j, kD)) = as_u4(kp);
+        *reinterpret_cast<uint4*>(smem + kSmQP1 + core_off(lrow, 8 * j, kD)) = as_u4(qp);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = km[i] * fa[i];      // decayed to the chunk end
-        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = pack8(t);
+        for (int m = 0; m < 4; ++m) t[m] = __hmul2(km[m], fa2[m]);      // decayed to the chunk end
+        *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = as_u4(t);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = kp[i] * fb[i];      // decayed from the chunk start
-        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = pack8(t);
+        for (int m = 0; m < 4; ++m) t[m] = __hmul2(kp[m], fb2[m]);      // decayed from the chunk start
+        *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = as_u4(t);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = qp[i] * fb[i];
-        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = pack8(t);
+        for (int m = 0; m < 4; ++m) t[m] = __hmul2(qp[m], fb2[m]);
+        *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = as_u4(t);
       }
     }
   }
