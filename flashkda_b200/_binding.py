@@ -17,6 +17,12 @@ _lib = None
 FLAG_SCAN_SIMT = 0x1
 FLAG_SCAN_PLAIN = 0x2
 FLAG_SCAN_LOOKAHEAD = 0x4
+FLAG_SCAN_NO_SEGMENTS = 0x8
+
+
+def FLAG_SEGMENTS(n: int) -> int:
+    """Flag bits that cut every sequence of a fixed-length batch into `n` runs walked in parallel."""
+    return (int(n) & 0xff) << 8
 _STATE_NONE, _STATE_BF16, _STATE_FP32 = 0, 1, 2
 
 
@@ -48,6 +54,8 @@ def lib():
         L = ctypes.CDLL(_LIB_PATH)
         i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
         L.fkda_get_workspace_size.argtypes = [i64, i64, i64, ctypes.POINTER(i64)]
+        L.fkda_get_workspace_size_flags.argtypes = [i64, i64, i64, i64, ctypes.POINTER(i64)]
+        L.fkda_plan_segments.argtypes = [i64, i64, ctypes.POINTER(ci), ctypes.POINTER(ci)]
         L.fkda_fwd.argtypes = [ctypes.POINTER(FwdParams), vp]
         L.fkda_prepare.argtypes = [ctypes.POINTER(FwdParams), vp]
         L.fkda_scan.argtypes = [ctypes.POINTER(FwdParams), vp]
@@ -58,7 +66,7 @@ def lib():
         L.fkda_selftest_umma.argtypes = [vp, vp, vp, ci, ci, vp, vp]
         L.fkda_last_error.restype = ctypes.c_char_p
         L.fkda_version.restype = ctypes.c_char_p
-        for name in ("fkda_get_workspace_size", "fkda_fwd", "fkda_prepare", "fkda_scan", "fkda_prologue",
+        for name in ("fkda_get_workspace_size", "fkda_get_workspace_size_flags", "fkda_plan_segments", "fkda_fwd", "fkda_prepare", "fkda_scan", "fkda_prologue",
                      "fkda_workspace_layout", "fkda_read_status", "fkda_selftest_umma"):
             getattr(L, name).restype = ci
         _lib = L
@@ -74,12 +82,23 @@ def _check(rc):
         raise RuntimeError(f"flash_kda: {last_error()} (code {rc})")
 
 
-def get_workspace_size(T_total: int, H: int, N: int = 1) -> int:
+def get_workspace_size(T_total: int, H: int, N: int = 1, flags: int = 0) -> int:
     """Bytes of scratch `fwd` allocates per call (counterpart of the reference's
-    get_workspace_size, csrc/flash_kda.cpp:5-26; the figure itself differs)."""
+    get_workspace_size, csrc/flash_kda.cpp:5-26; the figure itself differs).  `flags` matters only
+    with FLAG_SEGMENTS(n), which needs room for the per-run states."""
     out = ctypes.c_int64(0)
-    _check(lib().fkda_get_workspace_size(T_total, H, N, ctypes.byref(out)))
+    if flags:
+        _check(lib().fkda_get_workspace_size_flags(T_total, H, N, int(flags), ctypes.byref(out)))
+    else:
+        _check(lib().fkda_get_workspace_size(T_total, H, N, ctypes.byref(out)))
     return out.value
+
+
+def plan_segments(chains: int, chunks_per_sequence: int):
+    """(runs per sequence, chunks per run) the recurrence uses for a fixed-length batch; (1, 0) = whole sequences."""
+    a, b = ctypes.c_int(0), ctypes.c_int(0)
+    _check(lib().fkda_plan_segments(chains, chunks_per_sequence, ctypes.byref(a), ctypes.byref(b)))
+    return a.value, b.value
 
 
 def workspace_layout(T_total, H, N, varlen, T_per_seq):
@@ -157,7 +176,7 @@ def _params(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_s
     B, T, H, N, state_dtype = _validate(q, k, v, g, beta, out, A_log, dt_bias, initial_state, final_state,
                                         cu_seqlens)
     if workspace is None:
-        workspace = torch.empty(get_workspace_size(B * T, H, N), dtype=torch.uint8, device=q.device)
+        workspace = torch.empty(get_workspace_size(B * T, H, N, flags), dtype=torch.uint8, device=q.device)
     p = FwdParams(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(out), _ptr(A_log), _ptr(dt_bias),
                   _ptr(initial_state), _ptr(final_state), _ptr(cu_seqlens), _ptr(workspace),
                   workspace.numel(), B, T, H, N, float(scale), float(lower_bound), state_dtype, int(flags))

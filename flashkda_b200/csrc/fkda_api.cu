@@ -16,6 +16,7 @@ cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_short(const ScanParams& p, int sm_count, cudaStream_t stream);
+cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, cudaStream_t stream);
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
 cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* g, const __nv_bfloat16* beta,
@@ -45,11 +46,30 @@ struct Layout {
   int64_t prefix_off;      // int32 [N+1]
   int64_t records_off;
   int64_t chunks_per_head; // records per head
+  int64_t seg_off;         // fp32 slots of the segment-parallel scan (seg_bytes may be 0)
+  int64_t seg_bytes;
+  int n_segs;              // runs per sequence (1: whole sequences), of seg_chunks chunks each
+  int seg_chunks;
   int64_t total_bytes;
 };
 
+// Runs per sequence for a fixed-length batch under `flags`: forced by FKDA_FLAG_SEGMENTS(n), switched off by the
+// kernel-selection flags, else planned from the sizes.
+int segments_for(int64_t chains, int64_t chunks_per_seq, int64_t flags, int* seg_chunks) {
+  *seg_chunks = 0;
+  if (flags & (FKDA_FLAG_SCAN_SIMT | FKDA_FLAG_SCAN_PLAIN | FKDA_FLAG_SCAN_NO_SEGMENTS)) return 1;
+  const int64_t forced = (flags >> 8) & 0xff;
+  if (forced >= 2) {
+    if (chunks_per_seq < forced) return 1;
+    *seg_chunks = static_cast<int>((chunks_per_seq + forced - 1) / forced);
+    return static_cast<int>(forced);
+  }
+  if (flags & FKDA_FLAG_SCAN_LOOKAHEAD) return 1;
+  return fkda::plan_segments(chains, chunks_per_seq, seg_chunks);
+}
+
 // `varlen` < 0: size for whichever mode needs more (the upper bound T_total/32 + N covers both).
-bool make_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq, Layout* L) {
+bool make_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq, int64_t flags, Layout* L) {
   if (T_total < 0 || H <= 0 || N <= 0) return false;
   int64_t chunks;
   if (varlen == 0) chunks = N * ((T_per_seq + fkda::kChunk - 1) / fkda::kChunk);
@@ -57,12 +77,19 @@ bool make_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_pe
   if (varlen < 0) {
     int64_t fixed_ub = (T_total + fkda::kChunk - 1) / fkda::kChunk + N;
     chunks = fixed_ub > chunks ? fixed_ub : chunks;
+    if (T_total % N == 0) T_per_seq = T_total / N; else varlen = 1;   // a fixed-length call has T_total = N T
   }
   L->prefix_off = fkda::kWsHeaderBytes;
   int64_t prefix_bytes = ((2 * N + 1) * 4 + 255) / 256 * 256;   // chunk prefix [N+1] followed by the chain order [N]
   L->records_off = L->prefix_off + prefix_bytes;
   L->chunks_per_head = chunks;
-  L->total_bytes = L->records_off + chunks * H * static_cast<int64_t>(fkda::kRecBytes);
+  L->seg_off = L->records_off + chunks * H * static_cast<int64_t>(fkda::kRecBytes);
+  L->n_segs = 1;
+  L->seg_chunks = 0;
+  if (varlen <= 0 && N * H <= 0x7fffffffLL)
+    L->n_segs = segments_for(N * H, (T_per_seq + fkda::kChunk - 1) / fkda::kChunk, flags, &L->seg_chunks);
+  L->seg_bytes = L->n_segs > 1 ? N * H * L->n_segs * 3 * fkda::kSegSlotFloats * 4 : 0;
+  L->total_bytes = L->seg_off + L->seg_bytes;
   return true;
 }
 
@@ -90,7 +117,7 @@ int validate(const fkda_fwd_params* p, Layout* L) {
   const int64_t T_total = p->B * p->T;
   if (p->H > 65535) return fail(FKDA_ERR_INVALID_ARGUMENT, "H must be at most 65535");
   if (p->N * p->H > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "N*H exceeds 2^31-1 chains");
-  if (!make_layout(T_total, p->H, p->N, p->cu_seqlens ? 1 : 0, p->T, L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
+  if (!make_layout(T_total, p->H, p->N, p->cu_seqlens ? 1 : 0, p->T, p->flags, L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
   if (L->chunks_per_head * p->H > 0x7fffffffLL) return fail(FKDA_ERR_INVALID_ARGUMENT, "too many (chunk, head) pairs for one call");
   if (!p->workspace) return fail(FKDA_ERR_INVALID_ARGUMENT, "workspace is NULL");
   if (reinterpret_cast<uintptr_t>(p->workspace) & 255u) return fail(FKDA_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
@@ -163,6 +190,9 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e == cudaSuccess) e = fkda::launch_scan_short(s, sms, stream);
+  } else if (L.n_segs > 1) {
+    // few long chains: cut them into runs that are walked in parallel
+    e = fkda::launch_scan_segmented(s, L.n_segs, L.seg_chunks, reinterpret_cast<float*>(ws + L.seg_off), stream);
   } else e = fkda::launch_scan2(s, stream);
   if (e != cudaSuccess) return cuda_fail(e, "scan launch");
   return FKDA_OK;
@@ -172,18 +202,28 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
 
 extern "C" {
 
-int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* bytes) {
+int fkda_get_workspace_size_flags(int64_t T_total, int64_t H, int64_t N, int64_t flags, int64_t* bytes) {
   Layout L;
   if (!bytes) return fail(FKDA_ERR_INVALID_ARGUMENT, "bytes is NULL");
-  if (!make_layout(T_total, H, N, -1, 0, &L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "T_total >= 0, H > 0 and N > 0 required");
+  if (!make_layout(T_total, H, N, -1, 0, flags, &L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "T_total >= 0, H > 0 and N > 0 required");
   *bytes = L.total_bytes;
+  return FKDA_OK;
+}
+
+int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* bytes) {
+  return fkda_get_workspace_size_flags(T_total, H, N, 0, bytes);
+}
+
+int fkda_plan_segments(int64_t chains, int64_t chunks_per_sequence, int* segments, int* chunks_per_segment) {
+  if (!segments || !chunks_per_segment) return fail(FKDA_ERR_INVALID_ARGUMENT, "NULL pointer");
+  *segments = fkda::plan_segments(chains, chunks_per_sequence, chunks_per_segment);
   return FKDA_OK;
 }
 
 int fkda_workspace_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq, int64_t* records_offset,
                           int64_t* record_bytes, int64_t* chunks_per_head) {
   Layout L;
-  if (!make_layout(T_total, H, N, varlen ? 1 : 0, T_per_seq, &L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
+  if (!make_layout(T_total, H, N, varlen ? 1 : 0, T_per_seq, 0, &L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
   if (records_offset) *records_offset = L.records_off;
   if (record_bytes) *record_bytes = fkda::kRecBytes;
   if (chunks_per_head) *chunks_per_head = L.chunks_per_head;

@@ -314,6 +314,41 @@ struct ScanParams {
   int N;
   int total_chunks;
   int state_fp32;              // dtype of both state tensors: 1 = fp32, 0 = bf16
+  // Segment-parallel form (fixed-length batches with few chains): every sequence is cut into n_segs runs of
+  // seg_chunks chunks and each CTA walks one run.  Pass 1 walks run 0 from the caller's state (its outputs are
+  // final) and, for the runs 1 .. n_segs-2, the two halves of the affine map  Z_end = Z_start M + N  that a run
+  // applies to the state Z = S^T: N from a zero state, M from the identity with u' taken as zero.  A small kernel
+  // chains the maps into the state at the start of every run; pass 2 walks runs 1 .. n_segs-1 from those.
+  int seg_chunks;              // 0: one CTA per whole sequence
+  int n_segs;
+  int seg_pass;                // 1 or 2
+  float* seg_buf;              // fp32 [(n*H + h)][n_segs][3][128][128]: 0 = M, 1 = N, 2 = state at the start of the run
 };
+
+constexpr int64_t kSegSlotFloats = 128 * 128;
+
+// How many runs to cut each sequence of a fixed-length batch into (1 = walk whole sequences), and their length in
+// chunks.  Costs are in chunk steps of one CTA: the launches proceed in waves of one CTA per SM, pass 1 holds
+// chains * (2 n - 3) CTAs and pass 2 chains * (n - 1), both walking ceil(chunks / n) chunks; chaining the maps
+// costs about three chunk steps per run.  The plan is a pure function of the sizes so that the workspace size and
+// the launch agree; it assumes the 148 SMs of a B200.
+inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
+  constexpr int64_t kSms = 148;
+  *seg_chunks = 0;
+  if (chains <= 0 || chains * 3 > kSms || chunks < 48) return 1;
+  const int64_t whole = (chains + kSms - 1) / kSms * chunks;
+  int64_t best = whole, best_n = 1;
+  for (int64_t n = 3; n <= 64; ++n) {
+    const int64_t len = (chunks + n - 1) / n;
+    if (len < 8) break;
+    if ((n - 1) * len >= chunks) continue;       // the last run would be empty
+    const int64_t w1 = (chains * (2 * n - 3) + kSms - 1) / kSms, w2 = (chains * (n - 1) + kSms - 1) / kSms;
+    const int64_t cost = (w1 + w2) * len + 3 * (n - 2) + 8;
+    if (cost < best) { best = cost; best_n = n; }
+  }
+  if (best_n == 1 || best * 4 > whole * 3) return 1;
+  *seg_chunks = static_cast<int>((chunks + best_n - 1) / best_n);
+  return static_cast<int>(best_n);
+}
 
 }  // namespace fkda

@@ -96,7 +96,19 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
   auto full_par = [&](int c) { return static_cast<uint32_t>((c / kStages) & 1); };
 
   // ---- chain -> tokens and records ---------------------------------------------------------------------
-  const int chain = blockIdx.x;
+  // variant: 0 = the recurrence proper; 1 = offset half of a run's affine map (zero state in, no output);
+  // 2 = transition half (identity in, u' taken as zero, no output)
+  int chain = blockIdx.x, seg = 0, variant = 0;
+  if (p.seg_chunks > 0) {
+    const int per = p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
+    chain = blockIdx.x / per;
+    const int j = blockIdx.x - chain * per;
+    if (p.seg_pass == 1) {
+      if (j > 0) { seg = 1 + ((j - 1) >> 1); variant = 1 + ((j - 1) & 1); }
+    } else {
+      seg = 1 + j;
+    }
+  }
   const int slot = chain / p.H, h = chain - slot * p.H;
   const int n = p.seq_order != nullptr ? p.seq_order[slot] : slot;     // varlen: longest sequences first
   int64_t bos, eos;
@@ -117,6 +129,52 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     const int avail = p.total_chunks > chunk_base ? p.total_chunks - chunk_base : 0;
     if (nchunks > avail) nchunks = avail;
   }
+  // where the state comes from and goes to: the caller's tensors, or the per-run slots of the segment buffer
+  const size_t chain_state = (static_cast<size_t>(n) * p.H + h) * kD * kD;
+  const void* init_base = nullptr;     // this chain's [128 v][128 k] block
+  int init_mode = 0;                   // 0 = zero, 1 = fp32, 2 = bf16, 3 = identity
+  void* fin_base = nullptr;
+  int fin_fp32 = p.state_fp32;
+  if (p.initial_state != nullptr) {
+    init_mode = p.state_fp32 ? 1 : 2;
+    init_base = static_cast<const uint8_t*>(p.initial_state) + chain_state * (p.state_fp32 ? 4 : 2);
+  }
+  if (p.final_state != nullptr) fin_base = static_cast<uint8_t*>(p.final_state) + chain_state * (p.state_fp32 ? 4 : 2);
+  if (p.seg_chunks > 0) {
+    float* slots = p.seg_buf + (static_cast<size_t>(n) * p.H + h) * p.n_segs * 3 * kSegSlotFloats;
+    const int c_begin = seg * p.seg_chunks < nchunks ? seg * p.seg_chunks : nchunks;
+    const int c_end = (seg == p.n_segs - 1 || (seg + 1) * p.seg_chunks > nchunks) ? nchunks : (seg + 1) * p.seg_chunks;
+    if (seg < p.n_segs - 1) {
+      const int64_t run_end = bos + static_cast<int64_t>(c_end) * kChunk;
+      eos = run_end < eos ? run_end : eos;
+    }
+    bos += static_cast<int64_t>(c_begin) * kChunk;
+    chunk_base += c_begin;
+    nchunks = c_end - c_begin;
+    if (p.seg_pass == 1) {
+      if (variant == 0) {
+        fin_base = slots + (1 * 3 + 2) * kSegSlotFloats;                 // state at the start of run 1
+      } else {
+        init_mode = variant == 2 ? 3 : 0;
+        init_base = nullptr;
+        fin_base = slots + (seg * 3 + (variant == 2 ? 0 : 1)) * kSegSlotFloats;
+      }
+      fin_fp32 = 1;
+    } else {
+      init_mode = 1;
+      init_base = slots + (seg * 3 + 2) * kSegSlotFloats;
+      if (seg != p.n_segs - 1) fin_base = nullptr;
+    }
+  }
+  // parked in shared memory for the state warps, which have no registers to spare
+  if (tid == 0) {
+    *reinterpret_cast<const void**>(smem + kSmMisc + 8) = init_base;
+    *reinterpret_cast<void**>(smem + kSmMisc + 16) = fin_base;
+    *reinterpret_cast<int*>(smem + kSmMisc + 24) = init_mode;
+    *reinterpret_cast<int*>(smem + kSmMisc + 28) = fin_fp32;
+  }
+  const bool write_out = variant == 0;
+  const bool zero_up = variant == 2;
   const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + chunk_base) * kRecBytes;
 
   // ---- setup -----------------------------------------------------------------------------------------------
@@ -288,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       const uint8_t* up_row = rec + kRecUP + (v >> 3) * 512 + (v & 7) * 16;   // row v of UP [128 v][32 tok]
       uint4 t[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) t[i] = *reinterpret_cast<const uint4*>(up_row + i * 128);
+      for (int i = 0; i < 4; ++i) t[i] = zero_up ? make_uint4(0u, 0u, 0u, 0u) : *reinterpret_cast<const uint4*>(up_row + i * 128);
       tmem_wait_ld();
       if (warp == 4 && lane == 0) FKDA_TRACE(1, c, 1);
 #pragma unroll
@@ -315,7 +373,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     const int qd = warp & 3;
     const int v = qd * 32 + lane;
     const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
-    const size_t row_off = ((static_cast<size_t>(n) * p.H + h) * kD + v) * kD;   // row v of this chain's state
+    const size_t row_off = static_cast<size_t>(v) * kD;                          // row v of this chain's state
+    const void* init_base = *reinterpret_cast<const void* volatile*>(smem + kSmMisc + 8);
+    const int init_mode = *reinterpret_cast<volatile int*>(smem + kSmMisc + 24);
 
     // ---- initial state: S <- e_0 S_init; bf16 copies of S_init (buffer 0) and e_0 S_init (buffer 1) --------
     // All global loads of this thread's 64 state values are issued before anything is waited for.
@@ -323,9 +383,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int cb = 2 * grp + half;     // 32-column block
-      if (p.initial_state != nullptr) {
-        if (p.state_fp32) {
-          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.initial_state) + row_off + cb * 32);
+      if (init_mode == 1 || init_mode == 2) {
+        if (init_mode == 1) {
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(init_base) + row_off + cb * 32);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const float4 f = __ldg(src + i);
@@ -333,7 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
             xi[half][4 * i + 2] = __float_as_uint(f.z); xi[half][4 * i + 3] = __float_as_uint(f.w);
           }
         } else {
-          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + row_off + cb * 32);
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(init_base) + row_off + cb * 32);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint4 w = __ldg(src + i);
@@ -345,7 +405,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) xi[half][i] = 0u;
+        for (int i = 0; i < 32; ++i) xi[half][i] = (init_mode == 3 && cb * 32 + i == v) ? 0x3f800000u : 0u;
       }
     }
     if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 0);
@@ -431,7 +491,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     }
 
     // ---- final state -> global -------------------------------------------------------------------------------
-    if (!failed && p.final_state != nullptr) {
+    void* fin_base = *reinterpret_cast<void* volatile*>(smem + kSmMisc + 16);
+    const int fin_fp32 = *reinterpret_cast<volatile int*>(smem + kSmMisc + 28);
+    if (!failed && fin_base != nullptr) {
       bool ok2 = true;
       if (nchunks > 0) ok2 = warp_wait(bar(BAR_SFULL), (nchunks - 1) & 1, abort_flag);
       if (ok2) {
@@ -443,14 +505,14 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
           uint32_t x[32];
           tmem_ld32(tq + kColS + cb * 32, x);
           tmem_wait_ld();
-          if (p.state_fp32) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.final_state) + row_off + cb * 32);
+          if (fin_fp32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(fin_base) + row_off + cb * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]), __uint_as_float(x[4 * i + 2]),
                                    __uint_as_float(x[4 * i + 3]));
           } else {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.final_state) + row_off + cb * 32);
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(fin_base) + row_off + cb * 32);
             uint32_t y[16];
             pack32(x, y);
 #pragma unroll
@@ -509,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
-        if (r < valid) {
+        if (write_out && r < valid) {
           const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 32 + c8);
           *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(tok0 + r) * p.H + h) * kD + qd * 32 + c8) = val;
         }
@@ -536,8 +598,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(scan2::scan2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan2::kSmemBytes);
   if (e != cudaSuccess) return e;
-  const int64_t chains = static_cast<int64_t>(p.N) * p.H;
-  if (chains == 0) return cudaSuccess;
+  int64_t chains = static_cast<int64_t>(p.N) * p.H;
+  if (p.seg_chunks > 0) chains *= p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
+  if (chains <= 0) return cudaSuccess;
   scan2::scan2_kernel<<<static_cast<unsigned>(chains), scan2::kThreads, scan2::kSmemBytes, stream>>>(p, scan2::g_trace);
   return cudaGetLastError();
 }

@@ -35,7 +35,11 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 /* flags */
 #define FKDA_FLAG_SCAN_SIMT 0x1u /* evaluate the recurrence on CUDA cores (verification aid, slow) */
 #define FKDA_FLAG_SCAN_PLAIN 0x2u /* tcgen05 recurrence without look-ahead (kept for cross-checking) */
-#define FKDA_FLAG_SCAN_LOOKAHEAD 0x4u /* always use the look-ahead recurrence kernel, also for short chains */
+#define FKDA_FLAG_SCAN_LOOKAHEAD 0x4u /* always use the look-ahead recurrence kernel on whole sequences */
+#define FKDA_FLAG_SCAN_NO_SEGMENTS 0x8u /* never cut sequences into runs that are walked in parallel */
+/* Cut every sequence of a fixed-length batch into n (2..255) runs walked in parallel, whatever the planner would
+ * choose; the workspace must then be sized with fkda_get_workspace_size_flags. */
+#define FKDA_FLAG_SEGMENTS(n) (((uint32_t)(n) & 0xffu) << 8)
 
 typedef struct fkda_fwd_params {
   /* bf16 [B*T][H][128], contiguous (reference: q,k,v,g of csrc/flash_kda.cpp:28-33) */
@@ -66,6 +70,15 @@ typedef struct fkda_fwd_params {
  * T_total = B*T.  The figure differs from the reference's: one 35328-byte operand record per
  * (head, 32-token chunk) plus a small header. */
 int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* bytes);
+
+/* The same for a call that will carry `flags` (needed only with FKDA_FLAG_SEGMENTS, which enlarges the scratch).
+ * No counterpart in the reference. */
+int fkda_get_workspace_size_flags(int64_t T_total, int64_t H, int64_t N, int64_t flags, int64_t* bytes);
+
+/* The planner of the segment-parallel recurrence: into how many runs (1 = none) a fixed-length batch with `chains`
+ * = N*H chains of `chunks_per_sequence` 32-token chunks is cut, and the run length in chunks.  The reference has no
+ * counterpart: its recurrence kernel always walks a whole sequence per CTA (csrc/smxx/fwd_kernel2.cuh:434-742). */
+int fkda_plan_segments(int64_t chains, int64_t chunks_per_sequence, int* segments, int* chunks_per_segment);
 
 /* The whole operator (replaces fwd(), csrc/flash_kda.cpp:28-217): prepare + scan on `stream`. */
 int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream);

@@ -28,7 +28,7 @@ def run_gpu(x, fin_dtype, flags=0, check_status=True):
     init_copy = None if init is None else init.clone()
     B, T, H = x["q"].shape[:3]
     N = x["cu_seqlens"].numel() - 1 if x["cu_seqlens"] is not None else B
-    ws = torch.empty(F.get_workspace_size(B * T, H, N), dtype=torch.uint8, device="cuda")
+    ws = torch.empty(F.get_workspace_size(B * T, H, N, flags), dtype=torch.uint8, device="cuda")
     flash_kda.fwd(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], x["scale"], out, xc["A_log"], xc["dt_bias"],
                   x["lower_bound"], initial_state=init, final_state=fin, cu_seqlens=xc["cu_seqlens"],
                   workspace=ws, flags=flags)
@@ -236,3 +236,34 @@ def test_baseline_config0_through_default_allocation():
                   dt_bias=xc["dt_bias"], lower_bound=x["lower_bound"], final_state=fin)
     torch.cuda.synchronize()
     check_against_f64(x, out.cpu(), fin.cpu(), "C0")
+
+
+@pytest.mark.parametrize("state", ["fp32", "bf16", "none"])
+@pytest.mark.parametrize("runs", [2, 3, 5])
+def test_segment_parallel_scan_forced_runs(runs, state):
+    """Sequences cut into runs walked in parallel (affine maps of the inner runs chained in fp32) give the same
+    result as the walk over whole sequences; ragged last chunk, last run shorter than the others."""
+    w = Workload("seg", H=2, B=2, T=32 * 13 + 7, state_in=None if state == "none" else state,
+                 state_out="fp32" if state == "none" else state, state_std=0.5, seed=31 + runs)
+    x = make_inputs(w)
+    fin_dtype = torch.bfloat16 if state == "bf16" else torch.float32
+    o_seg, s_seg = run_gpu(x, fin_dtype, F.FLAG_SCAN_LOOKAHEAD | F.FLAG_SEGMENTS(runs))
+    o_ref, s_ref = run_gpu(x, fin_dtype, F.FLAG_SCAN_LOOKAHEAD)
+    check_against_f64(x, o_seg, s_seg, f"runs={runs} state={state}")
+    assert max_abs(o_seg, o_ref) <= 1e-2
+    assert rel_fro(s_seg, s_ref) <= 5e-3
+
+
+def test_segment_parallel_scan_planned():
+    """A batch with few long chains takes the segment-parallel path by itself (the planner's choice), within the
+    same tolerances; a second call on the same workspace reproduces the first bit for bit."""
+    w = Workload("segplan", H=4, B=1, T=4096 + 19, state_in="fp32", state_out="fp32", state_std=0.5, seed=77)
+    runs, run_chunks = F.plan_segments(w.H * w.B, (w.T + 31) // 32)
+    assert runs >= 3 and (runs - 1) * run_chunks < (w.T + 31) // 32
+    x = make_inputs(w)
+    o1, s1 = run_gpu(x, torch.float32)
+    check_against_f64(x, o1, s1, f"planned runs={runs}x{run_chunks}")
+    o0, s0 = run_gpu(x, torch.float32, F.FLAG_SCAN_NO_SEGMENTS)
+    assert max_abs(o1, o0) <= 1e-2 and rel_fro(s1, s0) <= 5e-3
+    o2, s2 = run_gpu(x, torch.float32)
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16)) and torch.equal(s1, s2)

@@ -93,3 +93,20 @@ def test_c_abi_rejects_bad_params_without_a_gpu():
     assert L.fkda_fwd(ctypes.byref(p), None) == -2 and "workspace" in F.last_error()
     p = FwdParams(0x1001, *([0x1000] * 7), None, None, None, 0x3000, 1 << 40, 2, 16, 2, 2, 0.1, -5.0, 0, 0)
     assert L.fkda_fwd(ctypes.byref(p), None) == -1 and "aligned" in F.last_error()
+
+
+def test_segment_planner_is_consistent_with_the_workspace_size():
+    """Few long chains are cut into runs; many chains or short sequences are not.  The last run is never empty and
+    the workspace grows by three fp32 128x128 slots per (chain, run)."""
+    import flashkda_b200 as F
+    assert F.plan_segments(128, 256) == (1, 0)          # one chain per SM already
+    assert F.plan_segments(8, 16) == (1, 0)             # too short to be worth it
+    for chains, chunks in [(8, 4096), (16, 256), (1, 4096), (4, 129), (36, 1000)]:
+        runs, per = F.plan_segments(chains, chunks)
+        assert runs >= 3 and per * runs >= chunks and (runs - 1) * per < chunks, (chains, chunks, runs, per)
+        H, N, T = chains, 1, chunks * 32
+        grown = F.get_workspace_size(T, H, N) - F.get_workspace_size(T, H, N, F.FLAG_SCAN_NO_SEGMENTS)
+        assert grown == chains * runs * 3 * 128 * 128 * 4
+    # a forced run count sizes the workspace the same way
+    assert (F.get_workspace_size(32 * 20, 2, 1, F.FLAG_SEGMENTS(4)) - F.get_workspace_size(32 * 20, 2, 1, F.FLAG_SCAN_NO_SEGMENTS)
+            == 2 * 4 * 3 * 128 * 128 * 4)
