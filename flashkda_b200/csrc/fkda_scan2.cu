@@ -82,6 +82,8 @@ __device__ __forceinline__ void pack32(const uint32_t (&x)[32], uint32_t (&y)[16
   for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
 }
 
+// kSeg: CTAs walk runs of a sequence (segment-parallel form) instead of whole sequences
+template <bool kSeg>
 __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, unsigned long long* trace_buf) {
   unsigned long long* trace = (blockIdx.x == 0) ? trace_buf : nullptr;
   if (threadIdx.x == 0) FKDA_TRACE(4, 31, 1);
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
   // variant: 0 = the recurrence proper; 1 = offset half of a run's affine map (zero state in, no output);
   // 2 = transition half (identity in, u' taken as zero, no output)
   int chain = blockIdx.x, seg = 0, variant = 0;
-  if (p.seg_chunks > 0) {
+  if constexpr (kSeg) {
     const int per = p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
     chain = blockIdx.x / per;
     const int j = blockIdx.x - chain * per;
@@ -129,18 +131,18 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     const int avail = p.total_chunks > chunk_base ? p.total_chunks - chunk_base : 0;
     if (nchunks > avail) nchunks = avail;
   }
-  // where the state comes from and goes to: the caller's tensors, or the per-run slots of the segment buffer
-  const size_t chain_state = (static_cast<size_t>(n) * p.H + h) * kD * kD;
-  const void* init_base = nullptr;     // this chain's [128 v][128 k] block
-  int init_mode = 0;                   // 0 = zero, 1 = fp32, 2 = bf16, 3 = identity
-  void* fin_base = nullptr;
-  int fin_fp32 = p.state_fp32;
-  if (p.initial_state != nullptr) {
-    init_mode = p.state_fp32 ? 1 : 2;
-    init_base = static_cast<const uint8_t*>(p.initial_state) + chain_state * (p.state_fp32 ? 4 : 2);
-  }
-  if (p.final_state != nullptr) fin_base = static_cast<uint8_t*>(p.final_state) + chain_state * (p.state_fp32 ? 4 : 2);
-  if (p.seg_chunks > 0) {
+  if constexpr (kSeg) {
+    // where the state comes from and goes to: the caller's tensors, or the per-run slots of the segment buffer
+    const size_t chain_state = (static_cast<size_t>(n) * p.H + h) * kD * kD;
+    const void* init_base = nullptr;     // this chain's [128 v][128 k] block
+    int init_mode = 0;                   // 0 = zero, 1 = fp32, 2 = bf16, 3 = identity
+    void* fin_base = nullptr;
+    int fin_fp32 = p.state_fp32;
+    if (p.initial_state != nullptr) {
+      init_mode = p.state_fp32 ? 1 : 2;
+      init_base = static_cast<const uint8_t*>(p.initial_state) + chain_state * (p.state_fp32 ? 4 : 2);
+    }
+    if (p.final_state != nullptr) fin_base = static_cast<uint8_t*>(p.final_state) + chain_state * (p.state_fp32 ? 4 : 2);
     float* slots = p.seg_buf + (static_cast<size_t>(n) * p.H + h) * p.n_segs * 3 * kSegSlotFloats;
     const int c_begin = seg * p.seg_chunks < nchunks ? seg * p.seg_chunks : nchunks;
     const int c_end = (seg == p.n_segs - 1 || (seg + 1) * p.seg_chunks > nchunks) ? nchunks : (seg + 1) * p.seg_chunks;
@@ -165,16 +167,16 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       init_base = slots + (seg * 3 + 2) * kSegSlotFloats;
       if (seg != p.n_segs - 1) fin_base = nullptr;
     }
+    // parked in shared memory for the state warps, which have no registers to spare
+    if (tid == 0) {
+      *reinterpret_cast<const void**>(smem + kSmMisc + 8) = init_base;
+      *reinterpret_cast<void**>(smem + kSmMisc + 16) = fin_base;
+      *reinterpret_cast<int*>(smem + kSmMisc + 24) = init_mode;
+      *reinterpret_cast<int*>(smem + kSmMisc + 28) = fin_fp32;
+    }
   }
-  // parked in shared memory for the state warps, which have no registers to spare
-  if (tid == 0) {
-    *reinterpret_cast<const void**>(smem + kSmMisc + 8) = init_base;
-    *reinterpret_cast<void**>(smem + kSmMisc + 16) = fin_base;
-    *reinterpret_cast<int*>(smem + kSmMisc + 24) = init_mode;
-    *reinterpret_cast<int*>(smem + kSmMisc + 28) = fin_fp32;
-  }
-  const bool write_out = variant == 0;
-  const bool zero_up = variant == 2;
+  const bool write_out = !kSeg || variant == 0;
+  const bool zero_up = kSeg && variant == 2;
   const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + chunk_base) * kRecBytes;
 
   // ---- setup -----------------------------------------------------------------------------------------------
@@ -374,8 +376,16 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     const int v = qd * 32 + lane;
     const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
     const size_t row_off = static_cast<size_t>(v) * kD;                          // row v of this chain's state
-    const void* init_base = *reinterpret_cast<const void* volatile*>(smem + kSmMisc + 8);
-    const int init_mode = *reinterpret_cast<volatile int*>(smem + kSmMisc + 24);
+    const void* init_base;
+    int init_mode;                      // 0 = zero, 1 = fp32, 2 = bf16, 3 = identity
+    if constexpr (kSeg) {
+      init_base = *reinterpret_cast<const void* volatile*>(smem + kSmMisc + 8);
+      init_mode = *reinterpret_cast<volatile int*>(smem + kSmMisc + 24);
+    } else {
+      const size_t chain_state = (static_cast<size_t>(n) * p.H + h) * kD * kD;
+      init_base = static_cast<const uint8_t*>(p.initial_state) + chain_state * (p.state_fp32 ? 4 : 2);
+      init_mode = p.initial_state == nullptr ? 0 : (p.state_fp32 ? 1 : 2);
+    }
 
     // ---- initial state: S <- e_0 S_init; bf16 copies of S_init (buffer 0) and e_0 S_init (buffer 1) --------
     // All global loads of this thread's 64 state values are issued before anything is waited for.
@@ -491,8 +501,16 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     }
 
     // ---- final state -> global -------------------------------------------------------------------------------
-    void* fin_base = *reinterpret_cast<void* volatile*>(smem + kSmMisc + 16);
-    const int fin_fp32 = *reinterpret_cast<volatile int*>(smem + kSmMisc + 28);
+    void* fin_base;
+    int fin_fp32;
+    if constexpr (kSeg) {
+      fin_base = *reinterpret_cast<void* volatile*>(smem + kSmMisc + 16);
+      fin_fp32 = *reinterpret_cast<volatile int*>(smem + kSmMisc + 28);
+    } else {
+      const size_t chain_state = (static_cast<size_t>(n) * p.H + h) * kD * kD;
+      fin_base = p.final_state == nullptr ? nullptr : static_cast<uint8_t*>(p.final_state) + chain_state * (p.state_fp32 ? 4 : 2);
+      fin_fp32 = p.state_fp32;
+    }
     if (!failed && fin_base != nullptr) {
       bool ok2 = true;
       if (nchunks > 0) ok2 = warp_wait(bar(BAR_SFULL), (nchunks - 1) & 1, abort_flag);
@@ -596,12 +614,13 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
 }  // namespace scan2
 
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(scan2::scan2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan2::kSmemBytes);
-  if (e != cudaSuccess) return e;
   int64_t chains = static_cast<int64_t>(p.N) * p.H;
   if (p.seg_chunks > 0) chains *= p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
   if (chains <= 0) return cudaSuccess;
-  scan2::scan2_kernel<<<static_cast<unsigned>(chains), scan2::kThreads, scan2::kSmemBytes, stream>>>(p, scan2::g_trace);
+  auto kernel = p.seg_chunks > 0 ? scan2::scan2_kernel<true> : scan2::scan2_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan2::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  kernel<<<static_cast<unsigned>(chains), scan2::kThreads, scan2::kSmemBytes, stream>>>(p, scan2::g_trace);
   return cudaGetLastError();
 }
 
