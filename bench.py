@@ -174,6 +174,8 @@ def main():
     ap.add_argument("--config", type=int, default=1, help="BASELINE configuration index (1..4)")
     ap.add_argument("--shard", default="seq", choices=["seq", "head"])
     ap.add_argument("--shape", default=None, help="B,T,H override of the fixed-length workload (profiling on a small case)")
+    ap.add_argument("--flags", type=lambda v: int(v, 0), default=0,
+                    help="FKDA_FLAG_* bits passed to every call (kernel selection; tuning aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -212,13 +214,13 @@ def main():
     H_local = x["q"].shape[2]
     B, T = x["q"].shape[:2]
     N = w.N
-    ws = torch.empty(F.get_workspace_size(B * T, H_local, N), dtype=torch.uint8, device=dev)
+    ws = torch.empty(F.get_workspace_size(B * T, H_local, N, args.flags), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
 
     def call():
         flash_kda.fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["out"], x["A_log"], x["dt_bias"],
                       x["lower_bound"], initial_state=x["initial_state"], final_state=x["final_state"],
-                      cu_seqlens=x["cu_seqlens"], workspace=ws)
+                      cu_seqlens=x["cu_seqlens"], workspace=ws, flags=args.flags)
 
     def barrier():
         torch.cuda.synchronize()
@@ -248,7 +250,8 @@ def main():
     assert F.read_status(ws) == 0
 
     # ---- per-kernel durations (same stream, CUDA events), for the roofline of the dominant kernel ----
-    kw = dict(initial_state=x["initial_state"], final_state=x["final_state"], cu_seqlens=x["cu_seqlens"], workspace=ws)
+    kw = dict(initial_state=x["initial_state"], final_state=x["final_state"], cu_seqlens=x["cu_seqlens"], workspace=ws,
+              flags=args.flags)
     pos = (x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["out"], x["A_log"], x["dt_bias"], x["lower_bound"])
     ksteps = max(3, min(args.steps, 10))
     ms_prepare = time_cuda(lambda: F.prepare(*pos, **kw), ksteps, stream)
@@ -285,6 +288,16 @@ def main():
     # ---- reduce over ranks: max time -------------------------------------------------------------------
     ms, ms_prepare, ms_scan, ms_e2e = reduce_max_ms([ms, ms_prepare, ms_scan, e2e[0] if e2e else 0.0], world, dev)
 
+    # kernels per call: prepare, the recurrence (one launch, or pass 1 + map chaining + pass 2 when sequences are cut
+    # into runs), plus the chunk prefix for varlen
+    runs = 1
+    if x["cu_seqlens"] is None and not (args.flags & 0xB):
+        forced = (args.flags >> 8) & 0xFF
+        runs = forced if forced >= 2 else (1 if args.flags & 0x4 else F.plan_segments(N * H_local, (T + 31) // 32)[0])
+    if x["cu_seqlens"] is None and 0 < T <= 64 and not (args.flags & 0x4):
+        runs = 1
+    launches_per_call = 1 + (1 if x["cu_seqlens"] is not None else 0) + (1 if runs == 1 else 2 + (1 if runs > 2 else 0))
+
     if rank == 0:
         peak, peak_kind = measured_peaks()
         alg = algorithmic_bytes(B * T, H_local, N, w.state_in, w.state_out)      # per rank, per call
@@ -300,7 +313,7 @@ def main():
                        "sharding": f"{args.shard} x{world}, no data-path collective",
                        "l2": "inputs + outputs per call (%.2f GB) larger than the 126 MB L2; no explicit flush" % (alg / 1e9),
                        "chunk": 32},
-            "gpu_launches": (2 + (1 if x["cu_seqlens"] is not None else 0)) * args.steps,
+            "gpu_launches": launches_per_call * args.steps,
             "kernels_ms": {"prepare": ms_prepare, "scan": ms_scan},
             "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": ach, "peak": peak, "unit": "GB/s",
                          "frac": ach / peak, "peak_source": peak_kind, "algorithmic_bytes": alg,

@@ -49,7 +49,8 @@ constexpr int kSmXY = kSmStage + kStages * kRecBytes;   // 2 x [64][32] bf16 (co
 constexpr int kSmOutStg = kSmXY + 2 * 4096;             // 4 warps x [32 tok][32 v] bf16
 constexpr int kSmBars = kSmOutStg + 4 * 2048;
 constexpr int kSmMisc = kSmBars + 256;
-constexpr int kSmemBytes = kSmMisc + 64 + 1024;
+constexpr int kSmZero = kSmMisc + 64;                    // 512 zero bytes: stands in for u' where it is taken as zero
+constexpr int kSmemBytes = kSmZero + 512 + 1024;
 
 enum {
   BAR_FULL = 0,                    // [kStages] record landed
@@ -180,6 +181,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
   const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + chunk_base) * kRecBytes;
 
   // ---- setup -----------------------------------------------------------------------------------------------
+  if (kSeg && tid < 128) reinterpret_cast<uint32_t*>(smem + kSmZero)[tid] = 0u;
   if (tid == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -345,10 +347,10 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       if (warp == 4 && lane == 0) FKDA_TRACE(1, c, 0);
       uint32_t w[32], y[16];
       tmem_ld32(tq + kColW + 64 * (c & 1), w);
-      const uint8_t* up_row = rec + kRecUP + (v >> 3) * 512 + (v & 7) * 16;   // row v of UP [128 v][32 tok]
+      const uint8_t* up_row = zero_up ? smem + kSmZero : rec + kRecUP + (v >> 3) * 512 + (v & 7) * 16;   // row v of UP [128 v][32 tok]
       uint4 t[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) t[i] = zero_up ? make_uint4(0u, 0u, 0u, 0u) : *reinterpret_cast<const uint4*>(up_row + i * 128);
+      for (int i = 0; i < 4; ++i) t[i] = *reinterpret_cast<const uint4*>(up_row + i * 128);
       tmem_wait_ld();
       if (warp == 4 && lane == 0) FKDA_TRACE(1, c, 1);
 #pragma unroll

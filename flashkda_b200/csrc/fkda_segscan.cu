@@ -16,14 +16,37 @@ cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
 namespace {
 
 constexpr int kRowsPerCta = 8;
+constexpr int kMapBytes = kD * kD * 4;
+constexpr int kCmbM = 0;                                  // 2 x [128][128] fp32: transition maps, double-buffered
+constexpr int kCmbZ = kCmbM + 2 * kMapBytes;              // [kRowsPerCta][128] fp32: this CTA's rows of the state
+constexpr int kCmbBars = kCmbZ + kRowsPerCta * kD * 4;
+constexpr int kCmbSmemBytes = kCmbBars + 64 + 128;
 
 // Z_start[run + 1] = Z_start[run] M[run] + N[run] for run = 1 .. n_segs-2; rows of Z are independent, so each CTA
-// carries kRowsPerCta of them through all runs.  fp32 throughout.
-__global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_segs) {
-  __shared__ float z[kRowsPerCta][kD];
+// carries kRowsPerCta of them through all runs.  The 64 KB maps arrive by bulk copies two runs ahead, so the serial
+// chain of runs sees shared-memory latency only.  fp32 throughout.
+__global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_segs, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
+  const uint32_t sbase = smem_u32(smem);
+  float (*z)[kD] = reinterpret_cast<float (*)[kD]>(smem + kCmbZ);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kCmbBars + 16);
+  const int tid = threadIdx.x;
   float* slots = seg_buf + static_cast<size_t>(blockIdx.x) * n_segs * 3 * kSegSlotFloats;
-  const int k = threadIdx.x & (kD - 1);
-  const int rl = (threadIdx.x >> 7) * 4;                 // this thread's four rows within the CTA's block
+  auto load_map = [&](int run) {      // one thread
+    const int b = (run - 1) & 1;
+    mbar_arrive_expect_tx(sbase + kCmbBars + 8 * b, kMapBytes);
+    bulk_g2s(sbase + kCmbM + b * kMapBytes, slots + (run * 3 + 0) * kSegSlotFloats, kMapBytes, sbase + kCmbBars + 8 * b);
+  };
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(sbase + kCmbBars, 1);
+    mbar_init(sbase + kCmbBars + 8, 1);
+    fence_mbar_init();
+    for (int run = 1; run <= 2 && run + 1 < n_segs; ++run) load_map(run);
+  }
+  const int k = tid & (kD - 1);
+  const int rl = (tid >> 7) * 4;                         // this thread's four rows within the CTA's block
   const int r0 = blockIdx.y * kRowsPerCta + rl;
   float acc[4];
 #pragma unroll
@@ -33,17 +56,38 @@ __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_
   }
   __syncthreads();
   for (int run = 1; run + 1 < n_segs; ++run) {
-    const float* M = slots + (run * 3 + 0) * kSegSlotFloats;
+    const int b = (run - 1) & 1;
     const float* N = slots + (run * 3 + 1) * kSegSlotFloats;
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[i] = N[static_cast<size_t>(r0 + i) * kD + k];
-#pragma unroll 8
-    for (int j = 0; j < kD; ++j) {
-      const float m = M[j * kD + k];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[i] = fmaf(z[rl + i][j], m, acc[i]);
+    const bool ok = mbar_wait(sbase + kCmbBars + 8 * b, ((run - 1) >> 1) & 1, abort_flag, 32);
+    if (!__syncthreads_and(ok)) {
+      if (tid == 0) {
+        atomicCAS(status, kStatusOk, kStatusWaitTimeout);
+        // do not leave while a copy may still be landing in this CTA's shared memory
+        for (int bb = 0; bb < 2; ++bb) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(sbase + kCmbBars + 8 * bb, ((run - 1 + (bb != b)) >> 1) & 1))
+            if (globaltimer_ns() - t0 > 20000000ull) break;
+        }
+      }
+      break;
     }
-    __syncthreads();
+    const float* M = reinterpret_cast<const float*>(smem + kCmbM + b * kMapBytes);
+#pragma unroll 2
+    for (int j = 0; j < kD; j += 4) {
+      const float m0 = M[(j + 0) * kD + k], m1 = M[(j + 1) * kD + k], m2 = M[(j + 2) * kD + k], m3 = M[(j + 3) * kD + k];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 zr = *reinterpret_cast<const float4*>(&z[rl + i][j]);
+        acc[i] = fmaf(zr.x, m0, acc[i]);
+        acc[i] = fmaf(zr.y, m1, acc[i]);
+        acc[i] = fmaf(zr.z, m2, acc[i]);
+        acc[i] = fmaf(zr.w, m3, acc[i]);
+      }
+    }
+    __syncthreads();                  // every thread is done with z and with map buffer b
+    if (tid == 0 && run + 3 < n_segs) load_map(run + 2);
     float* zs = slots + ((run + 1) * 3 + 2) * kSegSlotFloats;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -65,8 +109,10 @@ cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_ch
   cudaError_t e = launch_scan2(p, stream);
   if (e != cudaSuccess) return e;
   if (n_segs > 2) {
+    e = cudaFuncSetAttribute(seg_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmbSmemBytes);
+    if (e != cudaSuccess) return e;
     const dim3 grid(static_cast<unsigned>(p.N) * p.H, kD / kRowsPerCta);
-    seg_combine_kernel<<<grid, 256, 0, stream>>>(seg_buf, n_segs);
+    seg_combine_kernel<<<grid, 256, kCmbSmemBytes, stream>>>(seg_buf, n_segs, p.status);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
