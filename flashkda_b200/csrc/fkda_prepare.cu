@@ -138,6 +138,9 @@ __device__ __forceinline__ void block16_product(uint32_t a_base, uint32_t b_base
   }
 }
 
+// kShortPath: compiled with the shortcuts for chunks of at most 16 valid tokens (launched when such chunks are a
+// large share of the call: short fixed-length sequences); without it the kernel has no trace of them.
+template <bool kShortPath>
 __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -176,6 +179,10 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
   const int j = cm & 15;        // 8-column group: channels 8j .. 8j+7
   const int sb = cm >> 4;       // sub-block (tokens 16sb .. 16sb+15); warps 0-3 -> 0, warps 4-7 -> 1
   const int row0 = sb * 16 + r8, row1 = row0 + 8;
+  // A chunk with at most 16 valid tokens (the last chunk of a sequence, or a whole short sequence) has an all-zero
+  // second sub-block: its warps skip the transcendental work and every product that involves it is known to be zero.
+  const bool short_chunk = kShortPath && len <= 16;
+  const bool sb_live = sb == 0 || !short_chunk;     // uniform per warp
 
   float* s_tot = reinterpret_cast<float*>(smem + kSmTot);
   float* s_ssq = reinterpret_cast<float*>(smem + kSmSsq);
@@ -252,6 +259,11 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       }
       unpack8(gw[hf], f);
       const bool valid = row < len;
+      if (!sb_live) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) G[hf][i] = 0.f;
+        continue;
+      }
       if (p.dbg & 32) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) G[hf][i] = f[i];
@@ -285,7 +297,19 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
 
   if (p.dbg & 16) goto store_record;
   // ---- P2: norms and every decayed operand ------------------------------------------------------------
-  {
+  if (!sb_live) {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0, lrow = row - 16;
+      *reinterpret_cast<uint4*>(smem + kSmKM + core_off(row, 8 * j, kD)) = z;
+      *reinterpret_cast<uint4*>(smem + kSmKP1 + core_off(lrow, 8 * j, kD)) = z;
+      *reinterpret_cast<uint4*>(smem + kSmQP1 + core_off(lrow, 8 * j, kD)) = z;
+      *reinterpret_cast<uint4*>(smem + kRecKR + core_off(row, 8 * j, kD)) = z;
+      *reinterpret_cast<uint4*>(smem + kSmKPP + core_off(row, 8 * j, kD)) = z;
+      *reinterpret_cast<uint4*>(smem + kRecQP + core_off(row, 8 * j, kD)) = z;
+    }
+  } else {
     // per-channel factors: fa = 2^(own sub-block total), fb = 2^(other sub-block total)
     __nv_bfloat162 fa2[4], fb2[4], fab2[4];
     {
@@ -386,8 +410,8 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       a_base = sbase + (is_m ? kSmQP1 : kSmKP1);
       b_base = sbase + (which == 1 ? kSmKM + 4096 : kSmKR0);
     }
-    float acc[2][4];
-    block16_product(a_base, b_base, lane, acc);
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    if (which == 0 || !short_chunk) block16_product(a_base, b_base, lane, acc);
     const int rbase = (which == 0) ? 0 : 16, cbase = (which == 1) ? 16 : 0;
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
@@ -444,7 +468,11 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
     }
     __syncwarp();
     const int i = lane >> 1, c8 = (lane & 1) * 8;     // each lane: 8 consecutive entries of one row of a 16x16 product
-    if (!(p.dbg & 256)) {
+    if (short_chunk) {                 // A_10 = 0: T_10 = 0
+      *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (!(p.dbg & 256) && !short_chunk) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // X = A_10 T_00
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
@@ -458,7 +486,7 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       *reinterpret_cast<float4*>(s_X + i * kLd + c8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     __syncwarp();
-    if (!(p.dbg & 256)) {
+    if (!(p.dbg & 256) && !short_chunk) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // T_10 = -T_11 X
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
@@ -507,6 +535,7 @@ after_p5:
       const int nb = warp * 4;             // first 8-column tile of this warp
 #pragma unroll
       for (int ks = 0; ks < 2; ++ks) {
+        if (ks == 1 && short_chunk) break;       // k+ rows 16-31 are zero
         uint32_t a[2][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
@@ -536,6 +565,7 @@ after_p5:
       const int vc0 = (warp & 3) * 4;      // first 8-wide v tile of this warp's 32 rows
 #pragma unroll
       for (int ks = 0; ks < 2; ++ks) {
+        if (ks == 1 && short_chunk) break;       // v rows 16-31 are zero
         uint32_t a[2][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)     // A = v^T: transposed loads of (token group 2ks + (mi>>1), v tile vc0 + 2mt + (mi&1))
@@ -580,11 +610,15 @@ cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int* 
 }
 
 cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes);
-  if (e != cudaSuccess) return e;
   if (p.total_chunks == 0 || p.H == 0) return cudaSuccess;
+  // fixed-length sequences whose last chunk holds at most 16 tokens, and that chunk is at least a quarter of them
+  const int64_t tail = p.T % kChunk;
+  const bool short_path = p.cu_seqlens == nullptr && tail >= 1 && tail <= 16 && p.T < 4 * kChunk;
+  auto kernel = short_path ? prepare_kernel<true> : prepare_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes);
+  if (e != cudaSuccess) return e;
   const unsigned grid = static_cast<unsigned>(p.total_chunks) * static_cast<unsigned>(p.H);
-  prepare_kernel<<<grid, 256, kPrepSmemBytes, stream>>>(p);
+  kernel<<<grid, 256, kPrepSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 
