@@ -64,6 +64,8 @@ def lib():
                                             ctypes.POINTER(i64)]
         L.fkda_read_status.argtypes = [vp, vp, ctypes.POINTER(ci)]
         L.fkda_selftest_umma.argtypes = [vp, vp, vp, ci, ci, vp, vp]
+        L.fkda_debug_tmem_layout_probe.argtypes = [vp, vp]
+        L.fkda_debug_tmem_layout_probe.restype = ci
         L.fkda_last_error.restype = ctypes.c_char_p
         L.fkda_version.restype = ctypes.c_char_p
         for name in ("fkda_get_workspace_size", "fkda_get_workspace_size_flags", "fkda_plan_segments", "fkda_fwd", "fkda_prepare", "fkda_scan", "fkda_prologue",
@@ -263,3 +265,13 @@ def selftest_umma(A, B, mode, reps=1):
     if int(status.item()) != 0:
         raise RuntimeError("tcgen05 self-test: a bounded wait gave up")
     return D
+
+
+def tmem_layout_probe(device="cuda"):
+    """Register <-> (lane, column) maps of the 16-lane tensor-memory fragment shapes (int32 [4, 2048];
+    see tmem_layout_probe_kernel in csrc/fkda_aux.cu)."""
+    out = torch.zeros(4, 2048, dtype=torch.int32, device=device)
+    with torch.cuda.device(out.device):
+        _check(lib().fkda_debug_tmem_layout_probe(_ptr(out), _stream(out)))
+    torch.cuda.synchronize(out.device)
+    return out.cpu()

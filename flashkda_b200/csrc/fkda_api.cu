@@ -19,6 +19,7 @@ cudaError_t launch_scan_short(const ScanParams& p, int sm_count, cudaStream_t st
 cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, cudaStream_t stream);
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
+cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream);
 cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* g, const __nv_bfloat16* beta,
                             const float* A_log, const float* dt_bias, float gate_scale, int64_t rows, int H, __nv_bfloat16* qn,
                             __nv_bfloat16* kn, float* gact, float* beta_act, cudaStream_t stream);
@@ -293,6 +294,13 @@ int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream) {
   if (nwarps < 1 || nwarps > 16 || reps < 1 || !out) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
   cudaError_t e = fkda::launch_tmem_bench(nwarps, reps, static_cast<long long*>(out), static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) return cuda_fail(e, "tmem bench launch");
+  return FKDA_OK;
+}
+
+int fkda_debug_tmem_layout_probe(void* out, void* cuda_stream) {
+  if (!out) return fail(FKDA_ERR_INVALID_ARGUMENT, "out is NULL");
+  cudaError_t e = fkda::launch_tmem_layout_probe(static_cast<uint32_t*>(out), static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_fail(e, "tmem layout probe launch");
   return FKDA_OK;
 }
 

@@ -327,6 +327,68 @@ __global__ void __launch_bounds__(512) tmem_bench_kernel(int reps, long long* ou
   }
 }
 
+// Records the register <-> (lane, column) maps of the 16-lane tensor-memory fragment shapes that the scan kernel's
+// state warps use.  One warp.  out[0][t][r], out[1][t][r]: what tcgen05.ld.16x256b.x8 returns for lanes 0-15 and
+// 16-31 of a 32 x 64 tile holding (lane << 8 | column); out[2][lane][c]: the tile after a 16x256b.x8 store of
+// (1 << 16 | t << 8 | r) to its lanes 0-15; out[3][lane][c] (c < 32): after a 16x128b.x8 store of (2 << 16 | t << 8 | r)
+// to lanes 16-31 of a 32-column tile.  All read back with the 32x32b shape, whose map is lane = thread, column = register.
+__global__ void __launch_bounds__(32) tmem_layout_probe_kernel(uint32_t* out) {
+  __shared__ uint32_t tmem_slot;
+  const int lane = threadIdx.x;
+  tmem_alloc(smem_u32(&tmem_slot), 256);
+  tmem_relinquish();
+  tc_fence_before();
+  __syncwarp();
+  tc_fence_after();
+  const uint32_t t0 = tmem_slot;
+  uint32_t x[32], y[16];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = (static_cast<uint32_t>(lane) << 8) | static_cast<uint32_t>(half * 32 + i);
+    tmem_st32(t0 + half * 32, x);
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) x[i] = 0xffffffffu;
+  tmem_st32(t0 + 64, x);
+  tmem_st32(t0 + 96, x);
+  tmem_st32(t0 + 128, x);
+  tmem_wait_st();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    tmem_ld_16x256b_x8(t0 + (static_cast<uint32_t>(16 * half) << 16), x);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[(half * 32 + lane) * 32 + i] = x[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) x[i] = (1u << 16) | (static_cast<uint32_t>(lane) << 8) | static_cast<uint32_t>(i);
+  tmem_st_16x256b_x8(t0 + 64, x);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) y[i] = (2u << 16) | (static_cast<uint32_t>(lane) << 8) | static_cast<uint32_t>(i);
+  tmem_st_16x128b_x8(t0 + 128 + (16u << 16), y);
+  tmem_wait_st();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    tmem_ld32(t0 + 64 + half * 32, x);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[2 * 2048 + lane * 64 + half * 32 + i] = x[i];
+  }
+  tmem_ld32(t0 + 128, x);
+  tmem_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) out[3 * 2048 + lane * 64 + i] = x[i];
+  tc_fence_before();
+  __syncwarp();
+  tmem_dealloc(t0, 256);
+}
+
+cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream) {
+  tmem_layout_probe_kernel<<<1, 32, 0, stream>>>(out);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream) {
   tmem_bench_kernel<<<1, nwarps * 32, 0, stream>>>(reps, out);
   return cudaGetLastError();

@@ -120,6 +120,11 @@ int fkda_debug_set_scan_trace(void* device_buffer);
  * out = int64[nwarps][4] cycles for {loads, stores, 16-column stores, load+store round trips}. */
 int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream);
 
+/* Self-test of the 16-lane tensor-memory fragment shapes the scan kernel relies on (tcgen05.ld/st 16x256b and
+ * 16x128b): out = uint32[4][2048], the register <-> (lane, column) maps as read back through the 32x32b shape
+ * (see tmem_layout_probe_kernel).  One warp, a few microseconds.  No counterpart in the reference. */
+int fkda_debug_tmem_layout_probe(void* out, void* cuda_stream);
+
 /* The forward pass with built-in scratch, for callers that cannot allocate device memory (a
  * server whose memory pool was fixed at start-up, a plugin living inside another component's
  * budget).  No counterpart in the reference, whose Python wrapper allocates a workspace per call.

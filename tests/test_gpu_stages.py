@@ -90,3 +90,26 @@ def test_prepare_records_match_fp64_operands(case):
     # with packed bf16 multiplies (two and three roundings of 2^-9 each).
     assert worst["qp"] < 8e-3 and worst["kr"] < 1.2e-2 and worst["ec"] < 2e-3, worst
     assert worst["mqk"] < 2e-2 and worst["wp"] < 3e-2 and worst["up"] < 3e-2, worst
+
+
+def test_tmem_16_lane_fragment_shapes():
+    """tcgen05.ld/st with the 16-lane shapes (16x256b.x8, 16x128b.x8) follow the mma accumulator fragment map that
+    the helpers in csrc/fkda_common.cuh document: thread t, register 4j+q <-> lane t/4 + 8(q/2), column 8j + 2(t%4) + q%2."""
+    import numpy as np
+    o = F.tmem_layout_probe().numpy().astype(np.int64) & 0xFFFFFFFF
+    ld = o[0].reshape(2, 32, 32)
+    t = np.arange(32)[:, None]
+    r = np.arange(32)[None, :]
+    lane = t // 4 + 8 * ((r % 4) // 2)
+    col = 8 * (r // 4) + 2 * (t % 4) + (r % 2)
+    for half in range(2):
+        assert np.array_equal(ld[half], ((lane + 16 * half) << 8) | col)
+    st = o[2].reshape(32, 64)
+    exp = np.full((32, 64), 0xFFFFFFFF, dtype=np.int64)
+    exp[lane, col] = (1 << 16) | (t << 8) | r
+    assert np.array_equal(st, exp)
+    s3 = o[3].reshape(32, 64)[:, :32]
+    r16 = np.arange(16)[None, :]
+    exp3 = np.full((32, 32), 0xFFFFFFFF, dtype=np.int64)
+    exp3[16 + t // 4 + 8 * (r16 % 2), 4 * (r16 // 2) + t % 4] = (2 << 16) | (t << 8) | r16
+    assert np.array_equal(s3, exp3)
