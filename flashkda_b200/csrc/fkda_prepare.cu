@@ -85,27 +85,30 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
 }
 
 // ---- shared-memory plan of the prepare kernel (byte offsets) --------------------------------------
-// The record under construction occupies [0, kRecBytes).  Its WP and UP regions are written last,
-// so until the intra-chunk products are done they hold three temporaries.
+// The record under construction occupies [0, kRecBytes); everything is arranged so that four CTAs fit one SM.
 // Raw q, k, g tiles are staged at the start of the record image ([3][32 tok][256 B], 16-byte chunks XOR-swizzled by
-// the token index) before anything of the record is written; v is staged the same way in its own buffer and stays.
+// the token index) before anything of the record is written.  The WP and UP regions are written last, so until the
+// intra-chunk products are done they hold three temporaries.  KR, E and QP are final after P2 and leave early; once
+// that copy has read them (checked before the barrier that ends P4) the KR region holds the fp32 inverse and the QP
+// region receives the v tile, which is fetched only then.
 constexpr int kSmStageQKG = 0;               // 24 KB, dead after P1
 constexpr int kSmKM = kRecWP;                // [32][128] k-, relative to own sub-block start   (dead after P4)
 constexpr int kSmKP1 = kRecUP;               // [16][128] k+ of sub-block 1 rel. to its own start (dead after P4)
 constexpr int kSmQP1 = kRecUP + 4096;        // [16][128] q+ of sub-block 1 rel. to its own start (dead after P4)
-constexpr int kSmKPP = kRecBytes;            // [32][128] k+ from chunk start (rows 0-15 double as sub-block operand)
-constexpr int kSmKR0 = kSmKPP + 8192;        // [16][128] k of sub-block 0 decayed to the sub-block end
-constexpr int kSmV = kSmKR0 + 4096;          // [32 tok][256 B] v, chunks XOR-swizzled by the token index
-constexpr int kSmTB = kSmV + 8192;           // [32][32] bf16 T diag(beta)
 constexpr int kLd = 36;                      // row stride (floats) of the small fp32 matrices: 16-byte aligned rows
-constexpr int kSmA = kSmTB + 2048;           // [32][36] fp32 A
-constexpr int kSmT = kSmA + 32 * kLd * 4;    // [32][36] fp32 T
-constexpr int kSmX = kSmT + 32 * kLd * 4;    // [16][36] fp32
-constexpr int kSmTot = kSmX + 16 * kLd * 4;          // [2][128] fp32 sub-block log2 decays
+constexpr int kSmT = kRecKR;                 // [32][36] fp32 T                                  (from P5 on)
+constexpr int kSmX = kSmT + 32 * kLd * 4;    // [16][36] fp32                                    (P5)
+static_assert(kSmX + 16 * kLd * 4 <= kRecKR + 8192, "T and X fit the KR region");
+constexpr int kSmV = kRecQP;                 // [32 tok][256 B] v, chunks XOR-swizzled by the token index (from P5 on)
+constexpr int kSmKPP = kRecBytes;            // [32][128] k+ from chunk start (rows 0-15 double as sub-block operand)
+constexpr int kSmKR0 = kSmKPP + 8192;        // [16][128] k of sub-block 0 decayed to the sub-block end (dead after P4)
+constexpr int kSmTB = kSmKR0;                // [32][32] bf16 T diag(beta)                       (from P5 on)
+constexpr int kSmA = kSmKR0 + 4096;          // [32][36] fp32 A
+constexpr int kSmTot = kSmA + 32 * kLd * 4;  // [2][128] fp32 sub-block log2 decays
 constexpr int kSmSsq = kSmTot + 1024;        // [2][32][4] fp32 partial sums of squares
 constexpr int kSmBeta = kSmSsq + 1024;       // [32] fp32 sigmoid(beta)
 constexpr int kPrepSmemBytes = kSmBeta + 128;
-static_assert(kPrepSmemBytes * 3 + 3 * 1024 <= 228 * 1024, "three CTAs per SM");
+static_assert(kPrepSmemBytes * 4 + 4 * 1024 <= 227 * 1024, "four CTAs per SM");
 
 // byte offset of 16-byte chunk `chunk` of token row `row` in a swizzled [32][256 B] staging tile
 __device__ __forceinline__ int stage_off(int row, int chunk) { return row * 256 + ((chunk ^ (row & 7)) << 4); }
@@ -141,7 +144,7 @@ __device__ __forceinline__ void block16_product(uint32_t a_base, uint32_t b_base
 // kShortPath: compiled with the shortcuts for chunks of at most 16 valid tokens (launched when such chunks are a
 // large share of the call: short fixed-length sequences); without it the kernel has no trace of them.
 template <bool kShortPath>
-__global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
+__global__ void __launch_bounds__(256, 4) prepare_kernel(const PrepParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // consecutive CTAs take consecutive heads of the same chunk: together they read whole [H x 256 B] token rows,
@@ -210,7 +213,6 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
         cp_async16(dst + kSmStageQKG, p.q + off, nbytes);
         cp_async16(dst + kSmStageQKG + 8192, p.k + off, nbytes);
         cp_async16(dst + kSmStageQKG + 16384, p.g + off, nbytes);
-        cp_async16(dst + kSmV, p.v + off, nbytes);
       }
     }
     if (tid < kChunk) {
@@ -448,7 +450,19 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       *reinterpret_cast<uint32_t*>(smem + kRecMQK + rg * 512 + cb * 128 + w * 4) = 0u;
     }
   }
+  if (tid == 0) bulk_wait_read0();      // the early copy has read KR, E, QP: their regions may be reused
   __syncthreads();
+  {
+    // v tile -> the QP region (same coalesced, swizzled staging as q, k, g); needed by P6 only, arrives during P5
+    const int lrow = tid >> 4, lchunk = tid & 15;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = lrow + 16 * hf;
+      const bool valid = (row < len) && !(p.dbg & 64);
+      const size_t off = (static_cast<size_t>(t0 + (valid ? row : 0)) * p.H + h) * kD + 8 * lchunk;
+      cp_async16(sbase + kSmV + stage_off(row, lchunk), p.v + off, valid ? 16u : 0u);
+    }
+  }
 
   if (p.dbg & 2) goto after_p5;
   // ---- P5: T = (I + A)^-1 and TB = T diag(beta), all inside warp 0 (no block-wide barriers) -------------------
@@ -517,9 +531,10 @@ __global__ void __launch_bounds__(256, 3) prepare_kernel(const PrepParams p) {
       }
     }
   }
+after_p5:
+  cp_async_wait_all();
   __syncthreads();
 
-after_p5:
   if (p.dbg & 4) goto store_record;
   // ---- P6: w' = TB k+ (warps 0-3, 32 k-columns each) ; u'^T = v^T TB^T (warps 4-7, 32 v-rows each) -----
   {
