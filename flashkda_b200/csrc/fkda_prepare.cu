@@ -468,64 +468,77 @@ __global__ void __launch_bounds__(256, 4) prepare_kernel(const PrepParams p) {
   // ---- P5: T = (I + A)^-1 and TB = T diag(beta), all inside warp 0 (no block-wide barriers) -------------------
   if (warp == 0) {
     if (!(p.dbg & 512)) {
-      // forward substitution, one column of one diagonal block per lane: x_i = [i==c] - sum_{j<i} A_ij x_j
+      // forward substitution, one column of one diagonal block per lane: x_i = [i==c] - sum_{j<i} A_ij x_j.
+      // Rows of A are read four entries at a time; entries on and above the diagonal are zero.
       const int b = lane >> 4, c = lane & 15;
       float x[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) x[i] = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         float acc = (i == c) ? 1.f : 0.f;
 #pragma unroll
-        for (int jj = 0; jj < i; ++jj) acc = fmaf(-s_A[(b * 16 + i) * kLd + b * 16 + jj], x[jj], acc);
+        for (int q4 = 0; 4 * q4 < i; ++q4) {
+          const float4 a4 = *reinterpret_cast<const float4*>(s_A + (b * 16 + i) * kLd + b * 16 + 4 * q4);
+          acc = fmaf(-a4.x, x[4 * q4], acc);
+          acc = fmaf(-a4.y, x[4 * q4 + 1], acc);
+          acc = fmaf(-a4.z, x[4 * q4 + 2], acc);
+          acc = fmaf(-a4.w, x[4 * q4 + 3], acc);
+        }
         x[i] = acc;
         s_T[(b * 16 + i) * kLd + b * 16 + c] = acc;
       }
     }
     __syncwarp();
-    const int i = lane >> 1, c8 = (lane & 1) * 8;     // each lane: 8 consecutive entries of one row of a 16x16 product
+    const int g = lane >> 2, t4 = lane & 3;
     if (short_chunk) {                 // A_10 = 0: T_10 = 0
+      const int i = lane >> 1, c8 = (lane & 1) * 8;
       *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8) = make_float4(0.f, 0.f, 0.f, 0.f);
       *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (!(p.dbg & 256) && !short_chunk) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // X = A_10 T_00
+    // T_10 = -T_11 (A_10 T_00): two 16x16x16 products on the tensor cores in tf32 (11-bit significands, finer than
+    // the bf16 the result is rounded to), fp32 accumulation
+    auto small_product = [&](const float* A, const float* B, float* D, float sign) {
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
-        const float a = s_A[(16 + i) * kLd + jj];
-        const float4 t0 = *reinterpret_cast<const float4*>(s_T + jj * kLd + c8);
-        const float4 t1 = *reinterpret_cast<const float4*>(s_T + jj * kLd + c8 + 4);
-        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]); acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
-        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]); acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
-      }
-      *reinterpret_cast<float4*>(s_X + i * kLd + c8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      *reinterpret_cast<float4*>(s_X + i * kLd + c8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-    }
-    __syncwarp();
-    if (!(p.dbg & 256) && !short_chunk) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // T_10 = -T_11 X
+      for (int ks = 0; ks < 2; ++ks) {
+        const int k0 = 8 * ks;
+        const uint32_t a0 = to_tf32(A[g * kLd + k0 + t4]), a1 = to_tf32(A[(g + 8) * kLd + k0 + t4]);
+        const uint32_t a2 = to_tf32(A[g * kLd + k0 + t4 + 4]), a3 = to_tf32(A[(g + 8) * kLd + k0 + t4 + 4]);
 #pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
-        const float a = -s_T[(16 + i) * kLd + 16 + jj];
-        const float4 t0 = *reinterpret_cast<const float4*>(s_X + jj * kLd + c8);
-        const float4 t1 = *reinterpret_cast<const float4*>(s_X + jj * kLd + c8 + 4);
-        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]); acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
-        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]); acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
+        for (int nt = 0; nt < 2; ++nt)
+          mma_tf32_1688(acc[nt], a0, a1, a2, a3, to_tf32(B[(k0 + t4) * kLd + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLd + 8 * nt + g]));
       }
-      *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      *reinterpret_cast<float4*>(s_T + (16 + i) * kLd + c8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        *reinterpret_cast<float2*>(D + g * kLd + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+        *reinterpret_cast<float2*>(D + (g + 8) * kLd + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+      }
+    };
+    if (!(p.dbg & 256) && !short_chunk) {
+      small_product(s_A + 16 * kLd, s_T, s_X, 1.f);                       // X = A_10 T_00
+      __syncwarp();
+      small_product(s_T + 16 * kLd + 16, s_X, s_T + 16 * kLd, -1.f);      // T_10 = -T_11 X
     }
     __syncwarp();
     {
-      // TB = T diag(beta) as a bf16 core-layout operand; lane = row
+      // TB = T diag(beta) as a bf16 core-layout operand; lane = row, four entries per shared-memory load
       const int r = lane;
       uint8_t* row = smem + kSmTB + (r >> 3) * 512 + (r & 7) * 16;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {          // 8 columns per 16-byte store
+        const float4 ta = *reinterpret_cast<const float4*>(s_T + r * kLd + q4 * 8);
+        const float4 tb = *reinterpret_cast<const float4*>(s_T + r * kLd + q4 * 8 + 4);
+        const float4 ba = *reinterpret_cast<const float4*>(s_beta + q4 * 8);
+        const float4 bb = *reinterpret_cast<const float4*>(s_beta + q4 * 8 + 4);
+        const float tv[8] = {ta.x, ta.y, ta.z, ta.w, tb.x, tb.y, tb.z, tb.w};
+        const float bv[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
         float t[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int c = q4 * 8 + e;
           const bool nz = (c <= r) && !(r < 16 && c >= 16);
-          t[e] = nz ? s_T[r * kLd + c] * s_beta[c] : 0.f;
+          t[e] = nz ? tv[e] * bv[e] : 0.f;
         }
         *reinterpret_cast<uint4*>(row + q4 * 128) = pack8(t);
       }
