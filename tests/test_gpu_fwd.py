@@ -162,14 +162,16 @@ def test_state_handoff_split_equals_unsplit():
     assert rel_fro(s2, s_all) <= 2e-3
 
 
-def test_long_chains_repeated_calls_stay_in_step():
+@pytest.mark.parametrize("flags", [F.FLAG_SCAN_NO_SEGMENTS, 0], ids=["whole_sequences", "planned_runs"])
+def test_long_chains_repeated_calls_stay_in_step(flags):
     """Long chains exercise every barrier of the look-ahead kernel thousands of times; repeated calls must never
-    trip a bounded wait (status 0) and must be bit-reproducible (no race on tensor- or shared memory)."""
+    trip a bounded wait (status 0) and must be bit-reproducible (no race on tensor- or shared memory).  With 32
+    chains the planner would cut the sequences into runs: both forms are walked."""
     w = Workload("long", H=16, B=2, T=4096, state_in="fp32", state_out="fp32", seed=99)
     x = make_inputs(w)
     ref = None
     for _ in range(6):
-        out, fin = run_gpu(x, torch.float32)          # asserts status == 0
+        out, fin = run_gpu(x, torch.float32, flags)   # asserts status == 0
         if ref is None:
             ref = (out, fin)
         else:
