@@ -336,7 +336,7 @@ def main():
 
 # DRAM bytes per token-head of each kernel, from ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum per launch / token-heads of the captured case).
-TRAFFIC_BYTES_PER_TOKEN_HEAD = {"prepare": 1789, "scan": 1333}   # profiles/prepare_kernel_scan2_kernel_B8xT1024xH16.md, scaled by token-heads
+TRAFFIC_BYTES_PER_TOKEN_HEAD = {"prepare": 1866, "scan": 1321}   # profiles/prepare_kernel_scan2_kernel_B8xT1024xH16.md, scaled by token-heads
 
 if __name__ == "__main__":
     main()
