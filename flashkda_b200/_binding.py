@@ -18,6 +18,7 @@ FLAG_SCAN_SIMT = 0x1
 FLAG_SCAN_PLAIN = 0x2
 FLAG_SCAN_LOOKAHEAD = 0x4
 FLAG_SCAN_NO_SEGMENTS = 0x8
+FLAG_NO_FUSED_SHORT = 0x10
 
 
 def FLAG_SEGMENTS(n: int) -> int:

@@ -16,6 +16,10 @@ cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_short(const ScanParams& p, int sm_count, cudaStream_t stream);
+cudaError_t launch_short16(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, const __nv_bfloat16* g,
+                           const __nv_bfloat16* beta, const float* A_log, const float* dt_bias, const void* initial_state,
+                           void* final_state, __nv_bfloat16* out, int64_t N, int T, int H, int state_fp32, float scale,
+                           float gate_scale, int* status, cudaStream_t stream);
 cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, cudaStream_t stream);
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
@@ -250,6 +254,20 @@ int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream) {
   int rc = validate(p, &L);
   if (rc != FKDA_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (p->cu_seqlens == nullptr && p->T > 0 && p->T <= 16 && (p->flags & 0xff1fu) == 0) {
+    // short fixed-length sequences (a continuation step): one fused kernel, no operand records
+    cudaError_t e = cudaMemsetAsync(p->workspace, 0, fkda::kWsHeaderBytes, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
+    e = fkda::launch_short16(static_cast<const __nv_bfloat16*>(p->q), static_cast<const __nv_bfloat16*>(p->k),
+                             static_cast<const __nv_bfloat16*>(p->v), static_cast<const __nv_bfloat16*>(p->g),
+                             static_cast<const __nv_bfloat16*>(p->beta), p->A_log, p->dt_bias, p->initial_state, p->final_state,
+                             static_cast<__nv_bfloat16*>(p->out), p->N, static_cast<int>(p->T), static_cast<int>(p->H),
+                             p->state_dtype == FKDA_STATE_FP32 ? 1 : 0, p->scale,
+                             static_cast<float>(static_cast<double>(p->lower_bound) * 1.4426950408889634),
+                             static_cast<int*>(p->workspace), stream);
+    if (e != cudaSuccess) return cuda_fail(e, "short-sequence kernel launch");
+    return FKDA_OK;
+  }
   rc = do_prepare(p, L, stream);
   if (rc != FKDA_OK) return rc;
   return do_scan(p, L, stream);

@@ -36,6 +36,7 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 #define FKDA_FLAG_SCAN_SIMT 0x1u /* evaluate the recurrence on CUDA cores (verification aid, slow) */
 #define FKDA_FLAG_SCAN_PLAIN 0x2u /* tcgen05 recurrence without look-ahead (kept for cross-checking) */
 #define FKDA_FLAG_SCAN_LOOKAHEAD 0x4u /* always use the look-ahead recurrence kernel on whole sequences */
+#define FKDA_FLAG_NO_FUSED_SHORT 0x10u /* T <= 16: use the two-kernel path instead of the fused short-sequence kernel */
 #define FKDA_FLAG_SCAN_NO_SEGMENTS 0x8u /* never cut sequences into runs that are walked in parallel */
 /* Cut every sequence of a fixed-length batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags. */

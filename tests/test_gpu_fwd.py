@@ -103,12 +103,14 @@ def test_varlen_matrix(seq_lens, state):
     check_against_f64(x, out, fin, f"varlen{seq_lens}-{state}")
 
 
-@pytest.mark.parametrize("kernel", ["short", "lookahead", "plain"])
-@pytest.mark.parametrize("B,T,state", [(300, 16, "fp32"), (37, 33, "bf16"), (5, 64, "fp32"), (200, 1, None), (3, 32, "bf16")])
+@pytest.mark.parametrize("kernel", ["default", "short", "lookahead", "plain"])
+@pytest.mark.parametrize("B,T,state", [(300, 16, "fp32"), (37, 33, "bf16"), (5, 64, "fp32"), (200, 1, None), (3, 32, "bf16"),
+                                       (70, 9, "bf16"), (33, 16, None)])
 def test_short_chains_all_scan_kernels(B, T, state, kernel):
-    """Sequences of at most two chunks go to the persistent short-chain kernel by default; the other two
-    recurrence kernels must give the same answers on the same shapes."""
-    flags = {"short": 0, "lookahead": F.FLAG_SCAN_LOOKAHEAD, "plain": F.FLAG_SCAN_PLAIN}[kernel]
+    """By default sequences of at most 16 tokens go to the fused short-sequence kernel and those of at most two
+    chunks to the persistent short-chain kernel; the other recurrence kernels must give the same answers on the
+    same shapes ("short": the two-kernel path with the persistent short-chain kernel also for T <= 16)."""
+    flags = {"default": 0, "short": F.FLAG_NO_FUSED_SHORT, "lookahead": F.FLAG_SCAN_LOOKAHEAD, "plain": F.FLAG_SCAN_PLAIN}[kernel]
     w = Workload("s", H=3, B=B, T=T, state_in=state, state_out=state or "fp32", state_std=0.5, seed=B + T)
     x = make_inputs(w)
     fin_dtype = torch.bfloat16 if state == "bf16" else torch.float32
@@ -269,3 +271,24 @@ def test_segment_parallel_scan_planned():
     assert max_abs(o1, o0) <= 1e-2 and rel_fro(s1, s0) <= 5e-3
     o2, s2 = run_gpu(x, torch.float32)
     assert torch.equal(o1.view(torch.int16), o2.view(torch.int16)) and torch.equal(s1, s2)
+
+
+@pytest.mark.parametrize("T", [1, 5, 8, 16])
+@pytest.mark.parametrize("state", ["fp32", "bf16"])
+def test_fused_short_sequences_match_two_kernel_path(T, state):
+    """The fused kernel for T <= 16 against the two-kernel path on the same inputs (gate regime with little decay,
+    so that the incoming state matters), and its state hand-off: two 8-token steps equal one 16-token step."""
+    w = Workload("f16", H=4, B=19, T=T, state_in=state, state_out=state, state_std=0.5, seed=T, lower_bound=-1.0)
+    x = make_inputs(w)
+    dt = torch.bfloat16 if state == "bf16" else torch.float32
+    o1, s1 = run_gpu(x, dt)
+    o0, s0 = run_gpu(x, dt, F.FLAG_NO_FUSED_SHORT)
+    check_against_f64(x, o1, s1, f"fused T={T} {state}")
+    assert max_abs(o1, o0) <= 1e-2 and rel_fro(s1, s0) <= (2e-2 if state == "bf16" else 5e-3)
+    if T == 16 and state == "fp32":
+        cut = lambda a, b: {k: (v[:, a:b].contiguous() if k in ("q", "k", "v", "g", "beta") else v) for k, v in x.items()}
+        xa, xb = cut(0, 8), cut(8, 16)
+        oa, sa = run_gpu(xa, dt)
+        xb["initial_state"] = sa
+        ob, sb = run_gpu(xb, dt)
+        assert max_abs(torch.cat([oa, ob], 1), o1) <= 1e-2 and rel_fro(sb, s1) <= 5e-3
