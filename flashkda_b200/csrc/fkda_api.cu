@@ -254,7 +254,9 @@ int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream) {
   int rc = validate(p, &L);
   if (rc != FKDA_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (p->cu_seqlens == nullptr && p->T > 0 && p->T <= 16 && (p->flags & 0xff1fu) == 0) {
+  static const char* fused_env = getenv("FKDA_FUSED_MAX_T");     // tuning aid, unset in production
+  const int64_t fused_max_t = fused_env ? atoll(fused_env) : fkda::kFusedMaxT;
+  if (p->cu_seqlens == nullptr && p->T > 0 && p->T <= fused_max_t && (p->flags & 0xff1fu) == 0) {
     // short fixed-length sequences (a continuation step): one fused kernel, no operand records
     cudaError_t e = cudaMemsetAsync(p->workspace, 0, fkda::kWsHeaderBytes, stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");

@@ -369,6 +369,9 @@ struct ScanParams {
 
 constexpr int64_t kSegSlotFloats = 128 * 128;
 
+// Fixed-length sequences of at most this many tokens take the fused short-sequence kernel (fkda_short16.cu).
+constexpr int64_t kFusedMaxT = 32;
+
 // How many runs to cut each sequence of a fixed-length batch into (1 = walk whole sequences), and their length in
 // chunks.  Costs are in chunk steps of one CTA: the launches proceed in waves of one CTA per SM, pass 1 holds
 // chains * (2 n - 3) CTAs and pass 2 chains * (n - 1), both walking ceil(chunks / n) chunks; chaining the maps

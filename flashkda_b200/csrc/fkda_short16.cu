@@ -1,6 +1,7 @@
-// Fused forward pass for batches of short fixed-length sequences (T <= 16): one CTA per (sequence, head) chain
+// Fused forward pass for batches of short fixed-length sequences: one CTA per (sequence, head) chain walks the
+// sequence in blocks of 16 tokens,
 // reads q, k, v, g, beta and the chain's state, and writes out and the new state - no operand record goes through
-// global memory.  This is the shape of a continuation / decode step after a prefill: per chain 16 KB of inputs
+// global memory, and between blocks the state stays in shared memory in fp32.  This is the shape of a continuation / decode step after a prefill: per chain 16 KB of inputs
 // against 128 KB of fp32 state in and out, so the kernel is a stream over the states.
 //
 // Replaces, for these shapes, both of the reference's kernels (csrc/smxx/fwd_kernel1.cuh:107-586 and
@@ -75,7 +76,7 @@ struct Params {
   const void* initial_state;
   void* final_state;
   __nv_bfloat16* out;
-  int T;                 // tokens per sequence, 1..16
+  int T;                 // tokens per sequence
   int H;
   int state_fp32;
   float scale;
@@ -83,14 +84,16 @@ struct Params {
   int* status;           // device status word (a bounded wait that gives up is recorded there)
 };
 
+// kOneBlock: T <= 16, compiled without the block loop's bookkeeping
+template <bool kOneBlock>
 __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chain = blockIdx.x;
   const int n = chain / p.H, h = chain - n * p.H;       // consecutive CTAs: consecutive heads of the same tokens
-  const int len = p.T;
-  const int64_t t0 = static_cast<int64_t>(n) * p.T;
+  const int64_t t_seq0 = static_cast<int64_t>(n) * p.T;
+  const int nblk = kOneBlock ? 1 : (p.T + kRows - 1) / kRows;
 
   float* s_A = reinterpret_cast<float*>(smem + kA);
   float* s_T = reinterpret_cast<float*>(smem + kT);
@@ -103,7 +106,7 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
   const uint32_t bar = sbase + kBar;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kBar + 8);
   const int row_bytes = p.state_fp32 ? 512 : 256;
-  const int row_stride = p.state_fp32 ? kStride32 : kStride16;
+  const int in_off = p.state_fp32 ? 0 : kStride16;     // bf16 rows arrive in the second half of their fp32 slot
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar, kD);
@@ -112,26 +115,29 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
   __syncthreads();
   if (p.initial_state != nullptr && tid < kD) {
     mbar_arrive_expect_tx(bar, row_bytes);
-    bulk_g2s(sbase + kState + tid * row_stride,
+    bulk_g2s(sbase + kState + tid * kStride32 + in_off,
              static_cast<const uint8_t*>(p.initial_state) + (static_cast<size_t>(chain) * kD + tid) * row_bytes, row_bytes, bar);
   }
-  // ---- inputs: coalesced asynchronous loads, 16 lanes per 256-byte token row -------------------------------
-  {
-    const int row = tid >> 4, chunk = tid & 15;
-    const bool valid = row < len;
-    const size_t off = (static_cast<size_t>(t0 + (valid ? row : 0)) * p.H + h) * kD + 8 * chunk;
+  // ---- inputs: coalesced asynchronous loads, 16 lanes per 256-byte token row; q, k, g and v of the next block are
+  // requested as soon as the staging of the current block has been consumed
+  auto load_qkg = [&](int blk) {
+    const int lrow = tid >> 4, chunk = tid & 15;
+    const bool valid = kRows * blk + lrow < p.T;
+    const size_t off = (static_cast<size_t>(t_seq0 + (valid ? kRows * blk + lrow : 0)) * p.H + h) * kD + 8 * chunk;
     const uint32_t nbytes = valid ? 16u : 0u;
-    const uint32_t dst = sbase + stage_off(row, chunk);
+    const uint32_t dst = sbase + stage_off(lrow, chunk);
     cp_async16(dst + kStQ, p.q + off, nbytes);
     cp_async16(dst + kStK, p.k + off, nbytes);
     cp_async16(dst + kStG, p.g + off, nbytes);
-    cp_async16(dst + kStV, p.v + off, nbytes);
-  }
-  if (tid < kRows) {
-    float b = 0.f;
-    if (tid < len) b = sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(t0 + tid) * p.H + h]));
-    s_beta[tid] = b;
-  }
+  };
+  auto load_v = [&](int blk) {
+    const int lrow = tid >> 4, chunk = tid & 15;
+    const bool valid = kRows * blk + lrow < p.T;
+    const size_t off = (static_cast<size_t>(t_seq0 + (valid ? kRows * blk + lrow : 0)) * p.H + h) * kD + 8 * chunk;
+    cp_async16(sbase + kStV + stage_off(lrow, chunk), p.v + off, valid ? 16u : 0u);
+  };
+  load_qkg(0);
+  load_v(0);
   // thread -> one (row, 8-column) item: rows 0-7 in warps 0-3, rows 8-15 in warps 4-7
   const int r8 = tid & 7;
   const int j = (tid >> 3) & 15;
@@ -146,8 +152,23 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
     hab[0] = ha * b0.x; hab[1] = ha * b0.y; hab[2] = ha * b0.z; hab[3] = ha * b0.w;
     hab[4] = ha * b1.x; hab[5] = ha * b1.y; hab[6] = ha * b1.z; hab[7] = ha * b1.w;
   }
+  const int g = lane >> 2, t4 = lane & 3;
+  const int mi = lane >> 3, r = lane & 7;
+  const int v0 = 16 * warp + g;
+  uint8_t* const srow = smem + kState + v0 * kStride32;
+  bool failed = false;
+
+  for (int blk = 0; blk < nblk; ++blk) {
+  const int64_t t0 = t_seq0 + kRows * blk;
+  const int len = p.T - kRows * blk < kRows ? p.T - kRows * blk : kRows;
+  if (tid < kRows) {
+    float b = 0.f;
+    if (tid < len) b = sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(t0 + tid) * p.H + h]));
+    s_beta[tid] = b;
+  }
   cp_async_wait_all();
   __syncthreads();
+  if (*abort_flag) { failed = true; break; }
 
   // ---- norms, gate, running decay ---------------------------------------------------------------------------------
   const uint4 qw = *reinterpret_cast<const uint4*>(smem + kStQ + stage_off(row, j));
@@ -234,11 +255,9 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
     *reinterpret_cast<uint4*>(smem + kKR + core_off(row, 8 * j, kD)) = as_u4(kr);
   }
   __syncthreads();
-
-  const int g = lane >> 2, t4 = lane & 3;
+  if (!kOneBlock && blk + 1 < nblk) load_qkg(blk + 1);
 
   // ---- A, M (one warp each), then T = (I + A)^-1 and T diag(beta) inside warp 0 --------------------------------
-  const int mi = lane >> 3, r = lane & 7;
   if (warp < 2) {
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const uint32_t a_lane = sbase + (warp == 0 ? kKP : kQP) + (mi & 1) * 2048 + (mi >> 1) * 128 + r * 16;
@@ -337,22 +356,17 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
     mma_bf16_16816(up[1], a0, a1, a2, a3, b2, b3);
   }
   __syncthreads();
+  if (!kOneBlock && blk + 1 < nblk) load_v(blk + 1);
 
   // ---- this warp's 16 rows of the state -> accumulator fragments -----------------------------------------------------
   // tile jt covers state columns k = 8jt .. 8jt+7: S[jt][0,1] = row v0, columns 8jt + 2t, +1; S[jt][2,3] = row v0 + 8
-  const int v0 = 16 * warp + g;
-  uint8_t* const srow = smem + kState + v0 * row_stride;
   float S[16][4];
-  if (p.initial_state != nullptr) {
-    const bool ok = mbar_wait(bar, 0, abort_flag);
-    if (!__all_sync(0xffffffffu, ok)) {
-      // the copy may still be landing: give it a moment before this CTA's shared memory goes away, then give up
-      const uint64_t t_begin = globaltimer_ns();
-      while (!mbar_try_wait(bar, 0) && globaltimer_ns() - t_begin < 20000000ull) {}
-      if (lane == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
-      return;
-    }
-    if (p.state_fp32) {
+  if (blk == 0 && p.initial_state == nullptr) {
+#pragma unroll
+    for (int jt = 0; jt < 16; ++jt) S[jt][0] = S[jt][1] = S[jt][2] = S[jt][3] = 0.f;
+  } else {
+    if (blk == 0) mbar_wait(bar, 0, abort_flag);     // gives up after 2 s and raises the abort flag, seen at the next block top / the exit
+    if (blk > 0 || p.state_fp32) {
 #pragma unroll
       for (int jt = 0; jt < 16; ++jt) {
         const float2 lo = *reinterpret_cast<const float2*>(srow + (8 * jt + 2 * t4) * 4);
@@ -362,14 +376,11 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
     } else {
 #pragma unroll
       for (int jt = 0; jt < 16; ++jt) {
-        const uint32_t lo = *reinterpret_cast<const uint32_t*>(srow + (8 * jt + 2 * t4) * 2);
-        const uint32_t hi = *reinterpret_cast<const uint32_t*>(srow + 8 * kStride16 + (8 * jt + 2 * t4) * 2);
+        const uint32_t lo = *reinterpret_cast<const uint32_t*>(srow + kStride16 + (8 * jt + 2 * t4) * 2);
+        const uint32_t hi = *reinterpret_cast<const uint32_t*>(srow + 8 * kStride32 + kStride16 + (8 * jt + 2 * t4) * 2);
         S[jt][0] = bf_lo(lo); S[jt][1] = bf_hi(lo); S[jt][2] = bf_lo(hi); S[jt][3] = bf_hi(hi);
       }
     }
-  } else {
-#pragma unroll
-    for (int jt = 0; jt < 16; ++jt) S[jt][0] = S[jt][1] = S[jt][2] = S[jt][3] = 0.f;
   }
 
   // ---- W = w' S and O = q+ S on this warp's 16 v (B fragments = the state registers rounded to bf16) -------------
@@ -416,7 +427,8 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
   }
 
   // ---- S' = diag(e) S + U^T kr: A = U^T (rows v, K = tokens), B = kr read transposed, accumulators = the state ----
-  if (p.final_state != nullptr) {
+  const bool last = kOneBlock || blk + 1 == nblk;
+  if (!last || p.final_state != nullptr) {
 #pragma unroll
     for (int jp = 0; jp < 8; ++jp) {   // two column tiles per transposed load
       uint32_t b0, b1, b2, b3;
@@ -429,8 +441,8 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
         mma_bf16_16816(S[jt], Ut[0][0], Ut[1][0], Ut[0][1], Ut[1][1], q ? b2 : b0, q ? b3 : b1);
       }
     }
-    // back into this warp's staging rows (nobody else touches them), then one bulk copy per row
-    if (p.state_fp32) {
+    // back into this warp's staging rows (nobody else touches them): fp32 between blocks, the caller's type at the end
+    if (!last || p.state_fp32) {
 #pragma unroll
       for (int jt = 0; jt < 16; ++jt) {
         *reinterpret_cast<float2*>(srow + (8 * jt + 2 * t4) * 4) = make_float2(S[jt][0], S[jt][1]);
@@ -440,15 +452,26 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
 #pragma unroll
       for (int jt = 0; jt < 16; ++jt) {
         *reinterpret_cast<uint32_t*>(srow + (8 * jt + 2 * t4) * 2) = pack_bf16(S[jt][0], S[jt][1]);
-        *reinterpret_cast<uint32_t*>(srow + 8 * kStride16 + (8 * jt + 2 * t4) * 2) = pack_bf16(S[jt][2], S[jt][3]);
+        *reinterpret_cast<uint32_t*>(srow + 8 * kStride32 + (8 * jt + 2 * t4) * 2) = pack_bf16(S[jt][2], S[jt][3]);
       }
     }
+  }
+  }  // blocks
+
+  if (failed || *abort_flag) {
+    // the state copy may still be landing: give it a moment before this CTA's shared memory goes away
+    const uint64_t t_begin = globaltimer_ns();
+    while (!mbar_try_wait(bar, 0) && globaltimer_ns() - t_begin < 20000000ull) {}
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+    return;
+  }
+  if (p.final_state != nullptr) {      // one bulk copy per row, per warp as soon as its rows are done
     fence_proxy_async_smem();
     __syncwarp();
     if (lane < 16) {
       const int vr = 16 * warp + lane;
       bulk_s2g(static_cast<uint8_t*>(p.final_state) + (static_cast<size_t>(chain) * kD + vr) * row_bytes,
-               sbase + kState + vr * row_stride, row_bytes);
+               sbase + kState + vr * kStride32, row_bytes);
       bulk_commit();
       bulk_wait_read0();               // shared memory must outlive the copy's reads
     }
@@ -463,9 +486,10 @@ cudaError_t launch_short16(const __nv_bfloat16* q, const __nv_bfloat16* k, const
                            float gate_scale, int* status, cudaStream_t stream) {
   if (N * H == 0) return cudaSuccess;
   short16::Params p{q, k, v, g, beta, A_log, dt_bias, initial_state, final_state, out, T, H, state_fp32, scale, gate_scale, status};
-  cudaError_t e = cudaFuncSetAttribute(short16::short16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, short16::kSmemBytes);
+  auto kernel = T <= short16::kRows ? short16::short16_kernel<true> : short16::short16_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, short16::kSmemBytes);
   if (e != cudaSuccess) return e;
-  short16::short16_kernel<<<static_cast<unsigned>(N * H), short16::kThreads, short16::kSmemBytes, stream>>>(p);
+  kernel<<<static_cast<unsigned>(N * H), short16::kThreads, short16::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -273,11 +273,12 @@ def test_segment_parallel_scan_planned():
     assert torch.equal(o1.view(torch.int16), o2.view(torch.int16)) and torch.equal(s1, s2)
 
 
-@pytest.mark.parametrize("T", [1, 5, 8, 16])
+@pytest.mark.parametrize("T", [1, 5, 8, 16, 17, 24, 32])
 @pytest.mark.parametrize("state", ["fp32", "bf16"])
 def test_fused_short_sequences_match_two_kernel_path(T, state):
-    """The fused kernel for T <= 16 against the two-kernel path on the same inputs (gate regime with little decay,
-    so that the incoming state matters), and its state hand-off: two 8-token steps equal one 16-token step."""
+    """The fused kernel (T <= 32: one or two blocks of 16 tokens) against the two-kernel path on the same inputs
+    (gate regime with little decay, so that the incoming state matters), and its state hand-off: two 8-token steps
+    equal one 16-token step."""
     w = Workload("f16", H=4, B=19, T=T, state_in=state, state_out=state, state_std=0.5, seed=T, lower_bound=-1.0)
     x = make_inputs(w)
     dt = torch.bfloat16 if state == "bf16" else torch.float32
@@ -292,3 +293,27 @@ def test_fused_short_sequences_match_two_kernel_path(T, state):
         xb["initial_state"] = sa
         ob, sb = run_gpu(xb, dt)
         assert max_abs(torch.cat([oa, ob], 1), o1) <= 1e-2 and rel_fro(sb, s1) <= 5e-3
+
+
+def test_fused_kernel_walks_many_blocks():
+    """The fused kernel is a complete forward pass; the dispatch only sends T <= 32 to it because the two-kernel path
+    is faster beyond.  With the tuning variable that lifts the limit it must reproduce a 5-block and a 63-block walk
+    (ragged last block, bf16 and fp32 state).  Runs in a child process: the variable is read once per process."""
+    import os, subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import sys, torch
+        sys.path.insert(0, "tests")
+        import test_gpu_fwd as t
+        from flashkda_b200.workloads import Workload, make_inputs
+        for T, state in ((75, "fp32"), (1001, "bf16")):
+            w = Workload("fb", H=2, B=3, T=T, state_in=state, state_out=state, state_std=0.5, seed=T, lower_bound=-1.0)
+            x = make_inputs(w)
+            dt = torch.bfloat16 if state == "bf16" else torch.float32
+            out, fin = t.run_gpu(x, dt)
+            t.check_against_f64(x, out, fin, f"fused-many-blocks T={T}")
+        print("OK")
+    """)
+    env = dict(os.environ, FKDA_FUSED_MAX_T="100000")
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600,
+                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert res.returncode == 0 and "OK" in res.stdout, res.stdout + res.stderr
