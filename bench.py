@@ -205,6 +205,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         import torch.distributed as dist
+        # stdout carries the one JSON line: whatever NCCL has to say (its version banner included) goes to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     # ---- this rank's shard ------------------------------------------------------------------------
