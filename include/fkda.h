@@ -36,7 +36,7 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 #define FKDA_FLAG_SCAN_SIMT 0x1u /* evaluate the recurrence on CUDA cores (verification aid, slow) */
 #define FKDA_FLAG_SCAN_PLAIN 0x2u /* tcgen05 recurrence without look-ahead (kept for cross-checking) */
 #define FKDA_FLAG_SCAN_LOOKAHEAD 0x4u /* always use the look-ahead recurrence kernel on whole sequences */
-#define FKDA_FLAG_NO_FUSED_SHORT 0x10u /* T <= 16: use the two-kernel path instead of the fused short-sequence kernel */
+#define FKDA_FLAG_NO_FUSED_SHORT 0x10u /* fixed-length T <= 32: use the two-kernel path instead of the fused short-sequence kernel */
 #define FKDA_FLAG_SCAN_NO_SEGMENTS 0x8u /* never cut sequences into runs that are walked in parallel */
 /* Cut every sequence of a fixed-length batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags. */
@@ -81,7 +81,8 @@ int fkda_get_workspace_size_flags(int64_t T_total, int64_t H, int64_t N, int64_t
  * counterpart: its recurrence kernel always walks a whole sequence per CTA (csrc/smxx/fwd_kernel2.cuh:434-742). */
 int fkda_plan_segments(int64_t chains, int64_t chunks_per_sequence, int* segments, int* chunks_per_segment);
 
-/* The whole operator (replaces fwd(), csrc/flash_kda.cpp:28-217): prepare + scan on `stream`. */
+/* The whole operator (replaces fwd(), csrc/flash_kda.cpp:28-217), enqueued on `stream`: prepare + scan, or, for
+ * fixed-length sequences of at most 32 tokens, one fused kernel that uses the workspace for its status word only. */
 int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream);
 
 /* The two stages on their own, for tests and profiling.  fkda_prepare fills the workspace
