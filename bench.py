@@ -205,9 +205,19 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         import torch.distributed as dist
-        # stdout carries the one JSON line: whatever NCCL has to say (its version banner included) goes to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=dev)
+        # stdout carries the one JSON line: whatever NCCL prints while the communicator is set up (its version banner
+        # goes to stdout by plain printf) is sent to stderr
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     # ---- this rank's shard ------------------------------------------------------------------------
     from flashkda_b200.sharding import plan, reduce_max_ms
