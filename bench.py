@@ -147,7 +147,10 @@ def reference_arm(args, w, rank):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sample_T / value,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": w.name, "B": w.B, "T": w.T, "H": w.H, "state": w.state_in},
+            "data": "synthetic",
+            "config": {"workload": w.name, "B_per_gpu": w.B, "T": w.T, "H_per_gpu": w.H, "K": 128, "V": 128, "N_per_gpu": w.N,
+                       "state": f"{w.state_in} in / {w.state_out} out", "lower_bound": w.lower_bound,
+                       "sharding": "host cores of rank 0", "chunk": 16},
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
