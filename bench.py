@@ -373,8 +373,10 @@ def main():
             "kernels_ms": {"short16": ms} if fused else {"prepare": ms_prepare, "scan": ms_scan},
             "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": ach, "peak": peak, "unit": "GB/s",
                          "frac": ach / peak, "peak_source": peak_kind, "algorithmic_bytes": alg,
-                         "traffic": TRAFFIC_BYTES_PER_TOKEN_HEAD.get(dom_name) and
-                         TRAFFIC_BYTES_PER_TOKEN_HEAD[dom_name] * B * T * H_local},
+                         "traffic": (SHORT16_TRAFFIC_BYTES_PER_CHAIN * N * H_local
+                                     if fused and T == 16 and w.state_in == "fp32" and w.state_out == "fp32" else
+                                     TRAFFIC_BYTES_PER_TOKEN_HEAD.get(dom_name) and
+                                     TRAFFIC_BYTES_PER_TOKEN_HEAD[dom_name] * B * T * H_local)},
             "roofline_call": {"achieved": ach_call, "peak": peak, "unit": "GB/s", "frac": ach_call / peak},
             "clocks": clocks,
         }
@@ -392,6 +394,7 @@ def main():
 
 # DRAM bytes per token-head of each kernel, from ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum per launch / token-heads of the captured case).
+SHORT16_TRAFFIC_BYTES_PER_CHAIN = 140_400   # profiles/short16_kernel_B128xT16xH32.md (T = 16, fp32 state in and out), scaled by chains
 TRAFFIC_BYTES_PER_TOKEN_HEAD = {"prepare": 1866, "scan": 1321}   # profiles/prepare_kernel_scan2_kernel_B8xT1024xH16.md, scaled by token-heads
 
 if __name__ == "__main__":
