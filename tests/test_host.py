@@ -110,3 +110,14 @@ def test_segment_planner_is_consistent_with_the_workspace_size():
     # a forced run count sizes the workspace the same way
     assert (F.get_workspace_size(32 * 20, 2, 1, F.FLAG_SEGMENTS(4)) - F.get_workspace_size(32 * 20, 2, 1, F.FLAG_SCAN_NO_SEGMENTS)
             == 2 * 4 * 3 * 128 * 128 * 4)
+
+
+def test_flag_constants_match_the_header():
+    text = open(os.path.join(ROOT, "include", "fkda.h")).read()
+    values = {m.group(1): int(m.group(2), 16) for m in re.finditer(r"#define\s+(FKDA_FLAG_\w+)\s+(0x[0-9a-fA-F]+)u", text)}
+    assert values["FKDA_FLAG_SCAN_SIMT"] == F.FLAG_SCAN_SIMT
+    assert values["FKDA_FLAG_SCAN_PLAIN"] == F.FLAG_SCAN_PLAIN
+    assert values["FKDA_FLAG_SCAN_LOOKAHEAD"] == F.FLAG_SCAN_LOOKAHEAD
+    assert values["FKDA_FLAG_SCAN_NO_SEGMENTS"] == F.FLAG_SCAN_NO_SEGMENTS
+    assert values["FKDA_FLAG_NO_FUSED_SHORT"] == F.FLAG_NO_FUSED_SHORT
+    assert F.FLAG_SEGMENTS(5) == 5 << 8 and "FKDA_FLAG_SEGMENTS(n)" in text
