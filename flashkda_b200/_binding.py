@@ -66,6 +66,8 @@ def lib():
         L.fkda_read_status.argtypes = [vp, vp, ctypes.POINTER(ci)]
         L.fkda_selftest_umma.argtypes = [vp, vp, vp, ci, ci, vp, vp]
         L.fkda_debug_tmem_layout_probe.argtypes = [vp, vp]
+        L.fkda_debug_umma_bench.argtypes = [ci, ci, ci, ci, ci, vp, vp, vp]
+        L.fkda_debug_umma_bench.restype = ci
         L.fkda_debug_tmem_layout_probe.restype = ci
         L.fkda_last_error.restype = ctypes.c_char_p
         L.fkda_version.restype = ctypes.c_char_p
@@ -276,3 +278,17 @@ def tmem_layout_probe(device="cuda"):
         _check(lib().fkda_debug_tmem_layout_probe(_ptr(out), _stream(out)))
     torch.cuda.synchronize(out.device)
     return out.cpu()
+
+
+def umma_bench(issuers=1, reps=64, ksteps=8, n=64, a_in_tmem=True, device="cuda"):
+    """Cycles per tcgen05.mma (M = 128, K = 16, N = n) when `issuers` threads of one CTA each issue `reps` chains of
+    `ksteps` accumulating instructions: returns (issue, complete) cycles per instruction for the slowest issuer."""
+    out = torch.zeros(8, dtype=torch.int64, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    with torch.cuda.device(out.device):
+        _check(lib().fkda_debug_umma_bench(issuers, reps, ksteps, n, int(bool(a_in_tmem)), _ptr(out), _ptr(status), _stream(out)))
+    torch.cuda.synchronize(out.device)
+    if int(status.item()) != 0:
+        raise RuntimeError("tcgen05 benchmark: a bounded wait gave up")
+    o = out.cpu().view(4, 2)[:issuers].double() / (reps * ksteps)
+    return o[:, 0].max().item(), o[:, 1].max().item()

@@ -24,6 +24,7 @@ cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_ch
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
 cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream);
+cudaError_t launch_umma_bench(int nissuers, int reps, int ksteps, int n, int ts, long long* out, int* status, cudaStream_t stream);
 cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* g, const __nv_bfloat16* beta,
                             const float* A_log, const float* dt_bias, float gate_scale, int64_t rows, int H, __nv_bfloat16* qn,
                             __nv_bfloat16* kn, float* gact, float* beta_act, cudaStream_t stream);
@@ -314,6 +315,15 @@ int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream) {
   if (nwarps < 1 || nwarps > 16 || reps < 1 || !out) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
   cudaError_t e = fkda::launch_tmem_bench(nwarps, reps, static_cast<long long*>(out), static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) return cuda_fail(e, "tmem bench launch");
+  return FKDA_OK;
+}
+
+int fkda_debug_umma_bench(int issuers, int reps, int ksteps, int n, int a_in_tmem, void* out, int* status, void* cuda_stream) {
+  if (issuers < 1 || issuers > 4 || reps < 1 || reps > 4096 || ksteps < 1 || ksteps > 8 || (n != 32 && n != 64 && n != 128) || !out || !status)
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
+  cudaError_t e = fkda::launch_umma_bench(issuers, reps, ksteps, n, a_in_tmem ? 1 : 0, static_cast<long long*>(out), status,
+                                          static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_fail(e, "umma bench launch");
   return FKDA_OK;
 }
 

@@ -389,6 +389,81 @@ cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// Micro-benchmark of tcgen05.mma issue and completion (tuning aid): `nissuers` (1..4) threads in different warps each
+// issue `reps` products of `ksteps` M=128 instructions (K = 16 each) with N = `n` into their own 128 TMEM columns,
+// A from shared memory (ts = 0) or tensor memory (ts = 1), then commit and wait.  out[issuer*2 + {0,1}] = cycles until
+// the last instruction was issued / until the commit arrived.  Operand contents are irrelevant (zeros).
+__global__ void __launch_bounds__(128) umma_bench_kernel(int nissuers, int reps, int ksteps, int n, int ts, long long* out, int* status) {
+  __shared__ __align__(1024) uint8_t sA[16384];
+  __shared__ __align__(1024) uint8_t sB[16384];
+  __shared__ __align__(8) uint64_t mbar[4];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < 4096; i += 128) {
+    reinterpret_cast<uint32_t*>(sA)[i] = 0u;
+    reinterpret_cast<uint32_t*>(sB)[i] = 0u;
+  }
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&mbar[i]), 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  {  // defined contents for the A operand columns read from tensor memory (columns 448..511 of every lane)
+    uint32_t z[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) z[i] = 0u;
+    tmem_st32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 448, z);
+    tmem_st32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 480, z);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  bool ok = true;
+  if (warp < nissuers && lane == 0) {
+    const uint32_t idesc = n == 128 ? umma_idesc_bf16(128, 128, 0, 0) : (n == 64 ? umma_idesc_bf16(128, 64, 0, 0) : umma_idesc_bf16(128, 32, 0, 0));
+    const uint32_t d = tmem + 96 * warp;           // up to 128 columns each (overlapping between issuers), clear of the A columns at 448
+    const uint32_t a_addr = smem_u32(sA), b_addr = smem_u32(sB);
+    const long long t0 = clock64();
+    for (int rep = 0; rep < reps; ++rep)
+      for (int ks = 0; ks < ksteps; ++ks) {
+        // 8-row groups 1024 bytes apart and four k-step offsets: every operand byte read lies inside its 16 KB array
+        // (16 groups x 1024 + 3 x 256 + 128 = 17280 - 1024 = 16256 at most)
+        const uint64_t bdesc = umma_desc(b_addr + (ks & 3) * 256, 128, 1024);
+        if (ts) umma_ts(d, tmem + 448 + (ks & 7) * 8, bdesc, idesc, (rep | ks) ? 1u : 0u);
+        else umma_ss(d, umma_desc(a_addr + (ks & 3) * 256, 128, 1024), bdesc, idesc, (rep | ks) ? 1u : 0u);
+      }
+    const long long t1 = clock64();
+    umma_commit(smem_u32(&mbar[warp]));
+    ok = mbar_wait(smem_u32(&mbar[warp]), 0, &abort_flag);
+    const long long t2 = clock64();
+    out[warp * 2 + 0] = t1 - t0;
+    out[warp * 2 + 1] = t2 - t0;
+    if (!ok) atomicExch(status, 1);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+cudaError_t launch_umma_bench(int nissuers, int reps, int ksteps, int n, int ts, long long* out, int* status, cudaStream_t stream) {
+  umma_bench_kernel<<<1, 128, 0, stream>>>(nissuers, reps, ksteps, n, ts, out, status);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream) {
   tmem_bench_kernel<<<1, nwarps * 32, 0, stream>>>(reps, out);
   return cudaGetLastError();

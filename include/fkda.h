@@ -122,6 +122,12 @@ int fkda_debug_set_scan_trace(void* device_buffer);
  * out = int64[nwarps][4] cycles for {loads, stores, 16-column stores, load+store round trips}. */
 int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream);
 
+/* Tuning aid: `issuers` (1..4) threads of one CTA each issue `reps` products of `ksteps` (1..8) tcgen05.mma
+ * instructions (M = 128, K = 16, N = n in {32, 64, 128}; A from shared or tensor memory) and wait for their commit;
+ * out = int64[issuers][2] cycles {until the last instruction was issued, until the commit arrived}; status[0] = 1 if
+ * a bounded wait gave up. */
+int fkda_debug_umma_bench(int issuers, int reps, int ksteps, int n, int a_in_tmem, void* out, int* status, void* cuda_stream);
+
 /* Self-test of the 16-lane tensor-memory fragment shapes the scan kernel relies on (tcgen05.ld/st 16x256b and
  * 16x128b): out = uint32[4][2048], the register <-> (lane, column) maps as read back through the 32x32b shape
  * (see tmem_layout_probe_kernel).  One warp, a few microseconds.  No counterpart in the reference. */

@@ -113,3 +113,12 @@ def test_tmem_16_lane_fragment_shapes():
     exp3 = np.full((32, 32), 0xFFFFFFFF, dtype=np.int64)
     exp3[16 + t // 4 + 8 * (r16 % 2), 4 * (r16 // 2) + t % 4] = (2 << 16) | (t << 8) | r16
     assert np.array_equal(s3, exp3)
+
+
+def test_umma_bench_runs_inside_its_operand_arrays():
+    """The tcgen05.mma micro-benchmark (tuning aid) completes for every shape it accepts; accumulating instructions of
+    one thread are serialised by the accumulator (over 100 cycles each), those of several threads overlap."""
+    one = F.umma_bench(issuers=1, reps=16, ksteps=8, n=128, a_in_tmem=False)
+    four = F.umma_bench(issuers=4, reps=16, ksteps=8, n=32, a_in_tmem=True)
+    assert one[1] > 60 and four[1] > 60
+    assert F.umma_bench(issuers=2, reps=8, ksteps=2, n=64, a_in_tmem=True)[1] > 0
