@@ -65,9 +65,12 @@ enum {
   BAR_XYFREE = BAR_WFREE + 2,      // [2] products that read the X/Y operands of a buffer are complete
   BAR_SFULL = BAR_XYFREE + 2,      // state update of a chunk complete
   BAR_UREADY,                      // U^T of a chunk in tensor memory
-  BAR_SBDREADY,                    // decayed state + its bf16 copy ready
-  BAR_APASS,                       // issuer 2 has consumed the SBDREADY phase it needs for its next chunk
-  BAR_COUNT
+  BAR_SREADY,                      // decayed state (fp32 accumulator) ready for the next update; phase 0 = initial state,
+                                   // phase k = after chunk k-1.  Watched by issuer 1 only, which cannot fall behind.
+  BAR_SBDREADY,                    // [2] bf16 copy of the decayed state ready, same phases: barrier ph & 1, its phase ph >> 1.
+                                   // Released before BAR_SREADY: the products that read the copy head the longest chain.
+                                   // Watched by issuer 2, which the data flow lets lag two phases: hence two barriers.
+  BAR_COUNT = BAR_SBDREADY + 2
 };
 static_assert(BAR_COUNT * 8 <= 256, "barrier area");
 
@@ -200,8 +203,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     }
     mbar_init(bar(BAR_SFULL), 1);
     mbar_init(bar(BAR_UREADY), 4);
-    mbar_init(bar(BAR_SBDREADY), 8);
-    mbar_init(bar(BAR_APASS), 1);
+    mbar_init(bar(BAR_SREADY), 8);
+    mbar_init(bar(BAR_SBDREADY + 0), 8);
+    mbar_init(bar(BAR_SBDREADY + 1), 8);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -248,13 +252,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         const uint32_t ut = tmem + kColUt + 16 * (c & 1);
         const bool more = c + 1 < nchunks;
         FKDA_TRACE(0, c, 6);
-        if (!mbar_wait(bar(BAR_SBDREADY), c & 1, abort_flag)) { failed = true; break; }
+        if (!mbar_wait(bar(BAR_SREADY), c & 1, abort_flag)) { failed = true; break; }
         FKDA_TRACE(0, c, 7);
         if (!mbar_wait(bar(BAR_UREADY), c & 1, abort_flag)) { failed = true; break; }
-        // The state update below lets the state warps complete the next SBDREADY phase.  Issuer 2 watches that barrier
-        // by parity too, one phase behind: it must have seen its phase (for chunk c+1) before the next one can
-        // complete, or the parity would alias.
-        if (more && !mbar_wait(bar(BAR_APASS), (c + 1) & 1, abort_flag)) { failed = true; break; }
         tc_fence_after();
         FKDA_TRACE(0, c, 0);
         {  // S^T += U^T kr : kr [32 tok][128 k] read MN-major (k-adjacent core matrices 128 B apart, token groups 2048 B)
@@ -300,8 +300,10 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
           if (!mbar_wait(bar(BAR_WFREE + (c & 1)), ((c - 2) >> 1) & 1, abort_flag)) { failed = true; break; }
           if (!mbar_wait(bar(BAR_OFREE + (c & 1)), ((c - 2) >> 1) & 1, abort_flag)) { failed = true; break; }
         }
-        if (!mbar_wait(bar(BAR_SBDREADY), (c < 2 ? 0 : c - 1) & 1, abort_flag)) { failed = true; break; }
-        mbar_arrive(bar(BAR_APASS));
+        {
+          const int ph = c < 2 ? 0 : c - 1;       // needs the copy of Sd_{c-2}
+          if (!mbar_wait(bar(BAR_SBDREADY + (ph & 1)), (ph >> 1) & 1, abort_flag)) { failed = true; break; }
+        }
         tc_fence_after();
         FKDA_TRACE(0, c, 2);
         const uint32_t sbd = tmem + kColSbd + 64 * (c & 1);
@@ -451,7 +453,8 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       __syncwarp();
       if (lane == 0) {
         if (warp == 8) FKDA_TRACE(2, 30, 2);
-        mbar_arrive(bar(BAR_SBDREADY));
+        mbar_arrive(bar(BAR_SBDREADY + 0));
+        mbar_arrive(bar(BAR_SREADY));
         if (nchunks > 0) mbar_arrive(bar(BAR_EMPTY + 0));   // done with e of record 0
       }
     } else {
@@ -477,18 +480,23 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       tmem_ld32(tq + kColS + 64 * grp + 32, x1);
       tmem_wait_ld();
       if (tr_on) FKDA_TRACE(trole, c, 2);
+      // the bf16 copy first: the products that read it head the longest chain of the step
 #pragma unroll
       for (int i = 0; i < 32; ++i) x0[i] = __float_as_uint(__uint_as_float(x0[i]) * __shfl_sync(0xffffffffu, e_lo, i));
       if (tr_on) FKDA_TRACE(trole, c, 6);
-      tmem_st32(tq + kColS + 64 * grp, x0);
       pack32(x0, y);
       tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp, y);
       if (tr_on) FKDA_TRACE(trole, c, 7);
 #pragma unroll
       for (int i = 0; i < 32; ++i) x1[i] = __float_as_uint(__uint_as_float(x1[i]) * __shfl_sync(0xffffffffu, e_hi, i));
-      tmem_st32(tq + kColS + 64 * grp + 32, x1);
       pack32(x1, y);
       tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp + 16, y);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_SBDREADY + ((c + 1) & 1)));
+      tmem_st32(tq + kColS + 64 * grp, x0);
+      tmem_st32(tq + kColS + 64 * grp + 32, x1);
       if (tr_on) FKDA_TRACE(trole, c, 4);
       tmem_wait_st();
       if (tr_on) FKDA_TRACE(trole, c, 5);
@@ -497,7 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       if (lane == 0) {
         if (tr_on) FKDA_TRACE(trole, c, 3);
         FKDA_TRACE(5, c, warp - 8);          // arrival time of each of the eight state warps
-        mbar_arrive(bar(BAR_SBDREADY));
+        mbar_arrive(bar(BAR_SREADY));
         mbar_arrive(bar(BAR_EMPTY + (c + 1) % kStages));    // done with e of record c+1
       }
     }
