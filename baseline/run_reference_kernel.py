@@ -2,8 +2,8 @@
 baseline/_ref by `pip install --target baseline/_ref` from a copy of the reference with the
 CUTLASS headers of the flashinfer wheel linked in as its `cutlass/` submodule) on the same
 synthetic workloads as bench.py, with the same CUDA-event method, and report its distance to
-this repository's kernels.  Informational: gives the "same box, reference kernel" row of
-BASELINE.md.  Usage: python baseline/run_reference_kernel.py [config ...]
+this repository's kernels.  Informational: the "same GPU, reference kernels" comparison.
+Usage: python baseline/run_reference_kernel.py [config ...]
 """
 import json
 import os

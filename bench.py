@@ -175,7 +175,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="fkda", choices=["fkda", "reference"])
-    ap.add_argument("--config", type=int, default=1, help="BASELINE configuration index (1..4)")
+    ap.add_argument("--config", type=int, default=1, help="index of the headline configuration (1..4)")
     ap.add_argument("--shard", default="seq", choices=["seq", "head"])
     ap.add_argument("--shape", default=None, help="B,T,H override of the fixed-length workload (profiling on a small case)")
     ap.add_argument("--flags", type=lambda v: int(v, 0), default=0,

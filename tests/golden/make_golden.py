@@ -67,7 +67,9 @@ def reference_style_inputs(T, H, seed=42):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to the reference checkout>")
+    ref_root = sys.argv[1]
     R = import_reference_oracle(ref_root)
     cases = []
 

@@ -230,7 +230,7 @@ def test_argument_errors_raise_before_launch():
 
 
 def test_baseline_config0_through_default_allocation():
-    """BASELINE config 0 (B=1, T=1024, H=4, fp32 final state) with the per-call workspace
+    """Headline configuration 0 (B=1, T=1024, H=4, fp32 final state) with the per-call workspace
     allocation of the plain `flash_kda.fwd` signature."""
     x = make_inputs(baseline_workload(0))
     xc = to_cuda(x)
