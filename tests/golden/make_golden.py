@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 tests/torch_ref.py needs a GPU for two calls only; both are substituted here, in memory,
 without touching the reference's files:
