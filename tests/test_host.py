@@ -121,3 +121,23 @@ def test_flag_constants_match_the_header():
     assert values["FKDA_FLAG_SCAN_NO_SEGMENTS"] == F.FLAG_SCAN_NO_SEGMENTS
     assert values["FKDA_FLAG_NO_FUSED_SHORT"] == F.FLAG_NO_FUSED_SHORT
     assert F.FLAG_SEGMENTS(5) == 5 << 8 and "FKDA_FLAG_SEGMENTS(n)" in text
+
+
+def test_new_entry_points_reject_bad_arguments_without_a_gpu():
+    L = ctypes.CDLL(F.lib_path())
+    i64, ci = ctypes.c_int64, ctypes.c_int
+    L.fkda_get_workspace_size_flags.argtypes = [i64, i64, i64, i64, ctypes.POINTER(i64)]
+    L.fkda_plan_segments.argtypes = [i64, i64, ctypes.POINTER(ci), ctypes.POINTER(ci)]
+    L.fkda_last_error.restype = ctypes.c_char_p
+    out = i64(0)
+    assert L.fkda_get_workspace_size_flags(1024, 4, 1, 0, None) < 0
+    assert L.fkda_get_workspace_size_flags(-1, 4, 1, 0, ctypes.byref(out)) < 0 and L.fkda_last_error()
+    assert L.fkda_get_workspace_size_flags(1024, 0, 1, 0, ctypes.byref(out)) < 0
+    assert L.fkda_plan_segments(8, 4096, None, None) < 0
+    a, b = ci(0), ci(0)
+    assert L.fkda_plan_segments(0, 4096, ctypes.byref(a), ctypes.byref(b)) == 0 and a.value == 1 and b.value == 0
+    # kernel-selection flags that exclude the segment-parallel walk must not reserve room for it
+    base = F.get_workspace_size(32 * 4096, 8, 1, F.FLAG_SCAN_NO_SEGMENTS)
+    assert F.get_workspace_size(32 * 4096, 8, 1, F.FLAG_SCAN_PLAIN) == base
+    assert F.get_workspace_size(32 * 4096, 8, 1, F.FLAG_SCAN_LOOKAHEAD) == base
+    assert F.get_workspace_size(32 * 4096, 8, 1) > base
