@@ -19,6 +19,7 @@ FLAG_SCAN_PLAIN = 0x2
 FLAG_SCAN_LOOKAHEAD = 0x4
 FLAG_SCAN_NO_SEGMENTS = 0x8
 FLAG_NO_FUSED_SHORT = 0x10
+FLAG_REFERENCE_ROUNDING = 0x20
 
 
 def FLAG_SEGMENTS(n: int) -> int:

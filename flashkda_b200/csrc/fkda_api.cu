@@ -20,6 +20,10 @@ cudaError_t launch_short16(const __nv_bfloat16* q, const __nv_bfloat16* k, const
                            const __nv_bfloat16* beta, const float* A_log, const float* dt_bias, const void* initial_state,
                            void* final_state, __nv_bfloat16* out, int64_t N, int T, int H, int state_fp32, float scale,
                            float gate_scale, int* status, cudaStream_t stream);
+cudaError_t launch_refmode(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, const __nv_bfloat16* g,
+                           const __nv_bfloat16* beta, const float* A_log, const float* dt_bias, const void* initial_state,
+                           void* final_state, __nv_bfloat16* out, const int64_t* cu_seqlens, int64_t N, int64_t T, int64_t T_total,
+                           int H, int state_fp32, float scale, float gate_scale, cudaStream_t stream);
 cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, cudaStream_t stream);
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
@@ -255,6 +259,19 @@ int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream) {
   int rc = validate(p, &L);
   if (rc != FKDA_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (p->flags & FKDA_FLAG_REFERENCE_ROUNDING) {
+    // debugging aid: the reference's tile size, state type and rounding points (one kernel, any shape)
+    cudaError_t e = cudaMemsetAsync(p->workspace, 0, fkda::kWsHeaderBytes, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
+    e = fkda::launch_refmode(static_cast<const __nv_bfloat16*>(p->q), static_cast<const __nv_bfloat16*>(p->k),
+                             static_cast<const __nv_bfloat16*>(p->v), static_cast<const __nv_bfloat16*>(p->g),
+                             static_cast<const __nv_bfloat16*>(p->beta), p->A_log, p->dt_bias, p->initial_state, p->final_state,
+                             static_cast<__nv_bfloat16*>(p->out), p->cu_seqlens, p->N, p->T, p->B * p->T, static_cast<int>(p->H),
+                             p->state_dtype == FKDA_STATE_FP32 ? 1 : 0, p->scale,
+                             static_cast<float>(static_cast<double>(p->lower_bound) * 1.4426950408889634), stream);
+    if (e != cudaSuccess) return cuda_fail(e, "reference-rounding kernel launch");
+    return FKDA_OK;
+  }
   static const char* fused_env = getenv("FKDA_FUSED_MAX_T");     // tuning aid, unset in production
   const int64_t fused_max_t = fused_env ? atoll(fused_env) : fkda::kFusedMaxT;
   if (p->cu_seqlens == nullptr && p->T > 0 && p->T <= fused_max_t && (p->flags & 0xff1fu) == 0) {

@@ -120,6 +120,7 @@ def test_flag_constants_match_the_header():
     assert values["FKDA_FLAG_SCAN_LOOKAHEAD"] == F.FLAG_SCAN_LOOKAHEAD
     assert values["FKDA_FLAG_SCAN_NO_SEGMENTS"] == F.FLAG_SCAN_NO_SEGMENTS
     assert values["FKDA_FLAG_NO_FUSED_SHORT"] == F.FLAG_NO_FUSED_SHORT
+    assert values["FKDA_FLAG_REFERENCE_ROUNDING"] == F.FLAG_REFERENCE_ROUNDING
     assert F.FLAG_SEGMENTS(5) == 5 << 8 and "FKDA_FLAG_SEGMENTS(n)" in text
 
 
