@@ -10,7 +10,7 @@
 #include "fkda_common.cuh"
 
 namespace fkda {
-cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int* prefix, int* status, cudaStream_t stream);
+cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int* prefix, int* status, cudaStream_t stream);
 cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
@@ -143,7 +143,7 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   cudaError_t e = cudaMemsetAsync(ws, 0, fkda::kWsHeaderBytes, stream);
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
   if (p->cu_seqlens) {
-    e = fkda::launch_chunk_prefix(p->cu_seqlens, static_cast<int>(p->N), p->B * p->T, prefix, status, stream);
+    e = fkda::launch_chunk_prefix(p->cu_seqlens, static_cast<int>(p->N), p->B * p->T, static_cast<int>(p->H), prefix, status, stream);
     if (e != cudaSuccess) return cuda_fail(e, "chunk_prefix launch");
   }
   fkda::PrepParams q{};
@@ -200,6 +200,21 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e == cudaSuccess) e = fkda::launch_scan_short(s, sms, stream);
+  } else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->N * p->H >= 2 * fkda::kPlanSms) {
+    // At least two chains per SM: the compact kernel, two CTAs per SM.  Equal-length chains: always.  Varlen: the
+    // chunk-prefix kernel has decided on the device (status word 1); both kernels are launched and the CTAs of the
+    // one that was not chosen leave at once.
+    if (p->cu_seqlens == nullptr || p->N * p->H > 1024) {
+      // (beyond about a thousand chains the empty launch would cost more than a wrong choice, and one long sequence
+      // among so many chains rarely sets the duration)
+      e = fkda::launch_scan(s, stream);
+    } else {
+      s.select = s.status + 1;
+      s.select_want = 1;
+      e = fkda::launch_scan(s, stream);
+      s.select_want = 0;
+      if (e == cudaSuccess) e = fkda::launch_scan2(s, stream);
+    }
   } else if (L.n_segs > 1) {
     // few long chains: cut them into runs that are walked in parallel
     e = fkda::launch_scan_segmented(s, L.n_segs, L.seg_chunks, reinterpret_cast<float*>(ws + L.seg_off), stream);

@@ -365,9 +365,12 @@ struct ScanParams {
   int n_segs;
   int seg_pass;                // 1 or 2
   float* seg_buf;              // fp32 [(n*H + h)][n_segs][3][128][128]: 0 = M, 1 = N, 2 = state at the start of the run
+  const int* select;           // device word, or nullptr: the kernel runs only if *select == select_want
+  int select_want;
 };
 
 constexpr int64_t kSegSlotFloats = 128 * 128;
+constexpr int64_t kPlanSms = 148;      // SMs of a B200: what the kernel-selection rules assume
 
 // Fixed-length sequences of at most this many tokens take the fused short-sequence kernel (fkda_short16.cu).
 constexpr int64_t kFusedMaxT = 32;
@@ -378,7 +381,7 @@ constexpr int64_t kFusedMaxT = 32;
 // costs about three chunk steps per run.  The plan is a pure function of the sizes so that the workspace size and
 // the launch agree; it assumes the 148 SMs of a B200.
 inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
-  constexpr int64_t kSms = 148;
+  constexpr int64_t kSms = kPlanSms;
   *seg_chunks = 0;
   if (chains <= 0 || chains * 3 > kSms || chunks < 48) return 1;
   const int64_t whole = (chains + kSms - 1) / kSms * chunks;

@@ -20,12 +20,17 @@ namespace fkda {
 // Replaces the reference's one-thread prefix kernel (fwd_kernel1.cuh:89-104) and also checks
 // that cu_seqlens is monotone and inside [0, T_total]; violations are clamped and reported
 // through the status word instead of faulting later.
-__global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int* __restrict__ prefix,
+// It also picks the recurrence kernel for batches with at least two chains per SM (status[1] = 1: the compact
+// kernel, two CTAs per SM): the compact kernel moves more chunks per SM and second but walks one chain more slowly,
+// so it is chosen unless the longest sequence alone would then set the duration.
+__global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int H, int* __restrict__ prefix,
                                     int* __restrict__ status) {
   __shared__ int warp_sums[32];
   __shared__ int carry;
+  __shared__ int longest;
   if (threadIdx.x == 0) {
     carry = 0;
+    longest = 0;
     prefix[0] = 0;
   }
   __syncthreads();
@@ -41,6 +46,7 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
         b = b < a ? a : (b > T_total ? T_total : b);
       }
       cnt = static_cast<int>((b - a + kChunk - 1) / kChunk);
+      atomicMax(&longest, cnt);
     }
     int x = cnt;
 #pragma unroll
@@ -65,6 +71,13 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) carry = incl;
     __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    // chunk steps per SM at the compact kernel's rate (1.25 us) against the longest chain walked alone (1.95 us), with
+    // a margin of 15 % in favour of the look-ahead kernel
+    const long long total_steps = static_cast<long long>(prefix[N]) * H;
+    const bool many = static_cast<long long>(N) * H >= 2 * kPlanSms;
+    status[1] = (many && static_cast<long long>(longest) * 195 * kPlanSms * 100 <= total_steps * 125 * 85) ? 1 : 0;
   }
   // Chain order for the scan: longest sequences first (longest-processing-time-first packing of unequal chains
   // onto the SMs; the reference walks sequences in the given order).  order[] follows prefix[] in memory.
@@ -632,8 +645,8 @@ store_record:
   }
 }
 
-cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int* prefix, int* status, cudaStream_t stream) {
-  chunk_prefix_kernel<<<1, 256, 0, stream>>>(cu, N, T_total, prefix, status);
+cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int* prefix, int* status, cudaStream_t stream) {
+  chunk_prefix_kernel<<<1, 256, 0, stream>>>(cu, N, T_total, H, prefix, status);
   return cudaGetLastError();
 }
 

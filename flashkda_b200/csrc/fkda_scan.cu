@@ -1,15 +1,18 @@
-// Inter-chunk recurrence of the KDA prefill: one CTA walks the chunks of one (sequence, head)
-// chain, with the 128x128 fp32 state resident in tensor memory for the whole chain.
+// Inter-chunk recurrence of the KDA prefill, compact form: one CTA walks the chunks of one (sequence, head)
+// chain with the 128x128 fp32 state resident in tensor memory, and two such CTAs share an SM.
 //
-// Replaces the reference's K2 (csrc/smxx/fwd_kernel2.cuh:115-839).  Per 32-token chunk, with S
-// the state at the chunk start held as S^T [v lanes][k columns]:
-//     W^T  = S^T wp^T                  tcgen05.mma  M=128 (v), N=32 (tokens), K=128
-//     O^T  = S^T qp^T                  tcgen05.mma  M=128, N=32, K=128
+// Replaces the reference's K2 (csrc/smxx/fwd_kernel2.cuh:115-839) for batches with many chains (at least two per
+// SM): every chain is a serial loop that leaves the SM idle most of the time, so two independent chains per SM
+// nearly double the throughput, where the look-ahead kernel (fkda_scan2.cu), which shortens the loop of one chain
+// per SM, would run the chains in more waves.  It is also the cross-check of the other recurrence kernels (flag
+// FKDA_FLAG_SCAN_PLAIN).  Per 32-token chunk, with S the state at the chunk start held as S^T [v lanes][k columns]:
+//     [W^T | O^T] = Sb [wp; qp]^T      tcgen05.mma  M=128 (v), N=64 (tokens of w' and of q+), K=128, A = bf16 copy of S in TMEM
 //     U^T  = up^T - W^T                warps: TMEM -> registers -> bf16 operand in shared memory
 //     S^T  = S^T diag(e) + U^T kr      tcgen05.mma  M=128, N=128 (k), K=32, accumulating in TMEM
 //     O^T += U^T mqk^T                 tcgen05.mma  M=128, N=32, K=32
-// The decay diag(e) and the bf16 operand copy of S are produced by one TMEM round trip per
-// chunk.  Operand records arrive by bulk async copies through a 3-stage mbarrier ring.
+// The decay diag(e) and the bf16 operand copy of S are produced by one TMEM round trip per chunk.  Operand records
+// arrive by bulk async copies through a 2-stage mbarrier ring.  Half of an SM: 256 TMEM columns, 88 KB of shared
+// memory, 320 threads of at most 102 registers.
 //
 // Warp roles (320 threads): warp 0 = copy producer, warp 1 = MMA issuer (+ TMEM owner),
 // warps 2-5 = state warps (U and S epilogues), warps 6-9 = output warps.  Each group of four
@@ -20,30 +23,31 @@
 
 namespace fkda {
 
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kScanThreads = 320;
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColW = 128, kColO = 160;
+constexpr uint32_t kColS = 0, kColW = 128, kColO = 160, kColSbd = 192;   // [W | O] adjacent: one N = 64 product; Sbd: two k per column
 
 // shared-memory plan (byte offsets from a 1024-byte aligned base)
 constexpr int kSmStage = 0;                                  // kStages records
-constexpr int kSmSb = kSmStage + kStages * kRecBytes;        // [128 v][128 k] bf16 operand copy of S (core layout)
-constexpr int kSmUt = kSmSb + 32768;                         // [128 v][32 tok] bf16 U^T (core layout)
-constexpr int kSmStateStg = kSmUt + 8192;                    // 4 warps x [32][33] fp32 staging for state I/O
-constexpr int kSmOutStg = kSmStateStg + 4 * 4224;            // 4 warps x [32 tok][32 v] bf16 staging for out
+constexpr int kSmUt = kSmStage + kStages * kRecBytes;        // [128 v][32 tok] bf16 U^T (core layout)
+constexpr int kSmOutStg = kSmUt + 8192;                      // 4 warps x [32 tok][32 v] bf16 staging for out
 constexpr int kSmBars = kSmOutStg + 4 * 2048;                // mbarriers
 constexpr int kSmMisc = kSmBars + 128;                       // tmem base, abort flag
 constexpr int kScanSmemBytes = kSmMisc + 64 + 1024;          // + slack for manual 1024-byte alignment
+static_assert(2 * (kScanSmemBytes + 1024) <= 227 * 1024, "two CTAs per SM");
 
 // mbarrier slots
-enum { BAR_FULL = 0, BAR_EMPTY = 3, BAR_WFULL = 6, BAR_OFULL, BAR_SFULL, BAR_UREADY, BAR_SBREADY, BAR_OFREE, BAR_COUNT };
+enum { BAR_FULL = 0, BAR_EMPTY = BAR_FULL + kStages, BAR_WFULL = BAR_EMPTY + kStages, BAR_OFULL, BAR_SFULL, BAR_UREADY, BAR_SBREADY,
+       BAR_OFREE, BAR_COUNT };
+static_assert(BAR_COUNT * 8 <= 128, "barrier area");
 
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   const bool ok = mbar_wait(bar, parity, abort_flag);
   return __all_sync(0xffffffffu, ok);
 }
 
-__global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -52,9 +56,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
   auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
 
+  if (p.select != nullptr && *p.select != p.select_want) return;     // the other recurrence kernel was chosen
   // ---- chain -> tokens and records ---------------------------------------------------------------------
   const int chain = blockIdx.x;
-  const int n = chain / p.H, h = chain - n * p.H;
+  const int slot = chain / p.H, h = chain - slot * p.H;
+  const int n = p.seq_order != nullptr ? p.seq_order[slot] : slot;     // varlen: longest sequences first
   int64_t bos, eos;
   int chunk_base;
   if (p.cu_seqlens != nullptr) {
@@ -125,26 +131,24 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams 
     // ===== MMA issuer ==========================================================================================
     if (lane == 0) {
       constexpr uint32_t idesc_n32 = umma_idesc_bf16(128, 32, 0, 0);
+      constexpr uint32_t idesc_n64 = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_n128_bmn = umma_idesc_bf16(128, 128, 0, 1);
-      const uint32_t sb_addr = sbase + kSmSb, ut_addr = sbase + kSmUt;
+      const uint32_t ut_addr = sbase + kSmUt;
       for (int c = 0; c < nchunks; ++c) {
         const int s = c % kStages, k = c / kStages;
         const uint32_t rec = sbase + kSmStage + s * kRecBytes;
         if (!mbar_wait(bar(BAR_FULL + s), k & 1, abort_flag)) { failed = true; break; }
         if (!mbar_wait(bar(BAR_SBREADY), c & 1, abort_flag)) { failed = true; break; }
-        tc_fence_after();
-        // W^T = Sb wp^T : A = Sb [128][128] K-major, B = WP [32][128] K-major; 8 k-steps of 16
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tmem + kColW, umma_desc(sb_addr + ks * 256, 128, 2048), umma_desc(rec + kRecWP + ks * 256, 128, 2048),
-                  idesc_n32, ks > 0);
-        umma_commit(bar(BAR_WFULL));
         if (c > 0 && !mbar_wait(bar(BAR_OFREE), (c - 1) & 1, abort_flag)) { failed = true; break; }
         tc_fence_after();
+        // [W^T | O^T] = Sb [wp; qp]^T : A = bf16 copy of S in tensor memory (two k per column), B = the [64][128] tile
+        // that WP and QP form in the record, K-major; 8 k-steps of 16
+        {
+          const uint64_t b = umma_desc(rec + kRecWP, 128, 2048);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tmem + kColO, umma_desc(sb_addr + ks * 256, 128, 2048), umma_desc(rec + kRecQP + ks * 256, 128, 2048),
-                  idesc_n32, ks > 0);
+          for (int ks = 0; ks < 8; ++ks) umma_ts(tmem + kColW, tmem + kColSbd + ks * 8, b + ks * 16, idesc_n64, ks > 0);
+        }
+        umma_commit(bar(BAR_WFULL));
         if (!mbar_wait(bar(BAR_UREADY), c & 1, abort_flag)) { failed = true; break; }
         tc_fence_after();
         // S^T += U^T kr : A = Ut [128][32] K-major (8-row groups 512 B apart), B = KR [32 tok][128 k] read
@@ -173,12 +177,10 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams 
     const int qd = warp & 3;
     const int v = qd * 32 + lane;
     const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
-    float* stg = reinterpret_cast<float*>(smem + kSmStateStg + qd * 4224);
-    const size_t state_off = (static_cast<size_t>(n) * p.H + h) * kD * kD + static_cast<size_t>(qd) * 32 * kD;
-    uint8_t* sb_row = smem + kSmSb + (v >> 3) * 2048 + (v & 7) * 16;   // + 128 * (k / 8)
+    const size_t row_off = ((static_cast<size_t>(n) * p.H + h) * kD + v) * kD;   // row v of this chain's state
     uint8_t* ut_row = smem + kSmUt + (v >> 3) * 512 + (v & 7) * 16;    // + 128 * (tok / 8)
 
-    // ---- initial state -> TMEM (pre-decayed by the first chunk's e) and bf16 operand copy ----------------
+    // ---- initial state -> TMEM (pre-decayed by the first chunk's e) and its bf16 operand copy --------------
     bool ok = true;
     if (nchunks > 0) ok = warp_wait(bar(BAR_FULL + 0), 0, abort_flag);
     if (ok) {
@@ -187,49 +189,40 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams 
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t x[32];
         if (p.initial_state != nullptr) {
-          // coalesced: 8 lanes cover one 128-byte row segment (fp32) / 4 lanes one 64-byte segment (bf16)
           if (p.state_fp32) {
-            const float* src = reinterpret_cast<const float*>(p.initial_state) + state_off + cb * 32;
+            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.initial_state) + row_off + cb * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const int r = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
-              const float4 f = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(r) * kD + c4));
-              stg[r * 33 + c4] = f.x; stg[r * 33 + c4 + 1] = f.y; stg[r * 33 + c4 + 2] = f.z; stg[r * 33 + c4 + 3] = f.w;
+              const float4 f = __ldg(src + i);
+              x[4 * i] = __float_as_uint(f.x); x[4 * i + 1] = __float_as_uint(f.y);
+              x[4 * i + 2] = __float_as_uint(f.z); x[4 * i + 3] = __float_as_uint(f.w);
             }
           } else {
-            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + state_off + cb * 32;
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + row_off + cb * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
-              const uint4 w = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * kD + c8));
-              float* d = stg + r * 33 + c8;
-              d[0] = bf_lo(w.x); d[1] = bf_hi(w.x); d[2] = bf_lo(w.y); d[3] = bf_hi(w.y);
-              d[4] = bf_lo(w.z); d[5] = bf_hi(w.z); d[6] = bf_lo(w.w); d[7] = bf_hi(w.w);
+              const uint4 w = __ldg(src + i);
+              x[8 * i] = w.x << 16; x[8 * i + 1] = w.x & 0xffff0000u;
+              x[8 * i + 2] = w.y << 16; x[8 * i + 3] = w.y & 0xffff0000u;
+              x[8 * i + 4] = w.z << 16; x[8 * i + 5] = w.z & 0xffff0000u;
+              x[8 * i + 6] = w.w << 16; x[8 * i + 7] = w.w & 0xffff0000u;
             }
           }
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(stg[lane * 33 + i]);
-          __syncwarp();
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = 0u;
         }
         if (nchunks > 0) {
+          uint32_t y[16];
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(sb_row + (cb * 4 + i) * 128) =
-                make_uint4(pack_bf16(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
-                           pack_bf16(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
-                           pack_bf16(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
-                           pack_bf16(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
+          for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
+          tmem_st16(tq + kColSbd + cb * 16, y);
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e0[cb * 32 + i]);
         }
         tmem_st32(tq + kColS + cb * 32, x);
       }
       tmem_wait_st();
-      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_SBREADY));
@@ -283,23 +276,18 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams 
         const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE);
 #pragma unroll 1
         for (int cb = 0; cb < 4; ++cb) {
-          uint32_t x[32];
+          uint32_t x[32], y[16];
           tmem_ld32(tq + kColS + cb * 32, x);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(sb_row + (cb * 4 + i) * 128) =
-                make_uint4(pack_bf16(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
-                           pack_bf16(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
-                           pack_bf16(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
-                           pack_bf16(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
+          for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
+          tmem_st16(tq + kColSbd + cb * 16, y);
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e[cb * 32 + i]);
           tmem_st32(tq + kColS + cb * 32, x);
         }
       }
       tmem_wait_st();
-      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_SBREADY));
@@ -316,28 +304,21 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanParams 
           uint32_t x[32];
           tmem_ld32(tq + kColS + cb * 32, x);
           tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(x[i]);
-          __syncwarp();
           if (p.state_fp32) {
-            float* dst = reinterpret_cast<float*>(p.final_state) + state_off + cb * 32;
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.final_state) + row_off + cb * 32);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
-              const float* sp = stg + r * 33 + c4;
-              *reinterpret_cast<float4*>(dst + static_cast<size_t>(r) * kD + c4) = make_float4(sp[0], sp[1], sp[2], sp[3]);
-            }
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]), __uint_as_float(x[4 * i + 2]),
+                                   __uint_as_float(x[4 * i + 3]));
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.final_state) + state_off + cb * 32;
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.final_state) + row_off + cb * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
-              const float* sp = stg + r * 33 + c8;
-              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * kD + c8) =
-                  make_uint4(pack_bf16(sp[0], sp[1]), pack_bf16(sp[2], sp[3]), pack_bf16(sp[4], sp[5]), pack_bf16(sp[6], sp[7]));
-            }
+            for (int i = 0; i < 4; ++i)
+              dst[i] = make_uint4(pack_bf16(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
+                                  pack_bf16(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
+                                  pack_bf16(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
+                                  pack_bf16(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
           }
-          __syncwarp();
         }
       } else {
         failed = true;

@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
   auto full_bar = [&](int c) { return bar(BAR_FULL + c % kStages); };
   auto full_par = [&](int c) { return static_cast<uint32_t>((c / kStages) & 1); };
 
+  if (p.select != nullptr && *p.select != p.select_want) return;     // the other recurrence kernel was chosen
   // ---- chain -> tokens and records ---------------------------------------------------------------------
   // variant: 0 = the recurrence proper; 1 = offset half of a run's affine map (zero state in, no output);
   // 2 = transition half (identity in, u' taken as zero, no output)
