@@ -200,8 +200,8 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e == cudaSuccess) e = fkda::launch_scan_short(s, sms, stream);
-  } else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->N * p->H >= 2 * fkda::kPlanSms) {
-    // At least two chains per SM: the compact kernel, two CTAs per SM.  Equal-length chains: always.  Varlen: the
+  } else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->N * p->H > fkda::kPlanSms) {
+    // More chains than SMs: the compact kernel, two CTAs per SM.  Equal-length chains: always.  Varlen: the
     // chunk-prefix kernel has decided on the device (status word 1); both kernels are launched and the CTAs of the
     // one that was not chosen leave at once.
     if (p->cu_seqlens == nullptr || p->N * p->H > 1024) {

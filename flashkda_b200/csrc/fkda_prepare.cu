@@ -20,7 +20,7 @@ namespace fkda {
 // Replaces the reference's one-thread prefix kernel (fwd_kernel1.cuh:89-104) and also checks
 // that cu_seqlens is monotone and inside [0, T_total]; violations are clamped and reported
 // through the status word instead of faulting later.
-// It also picks the recurrence kernel for batches with at least two chains per SM (status[1] = 1: the compact
+// It also picks the recurrence kernel for batches with more chains than SMs (status[1] = 1: the compact
 // kernel, two CTAs per SM): the compact kernel moves more chunks per SM and second but walks one chain more slowly,
 // so it is chosen unless the longest sequence alone would then set the duration.
 __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int H, int* __restrict__ prefix,
@@ -73,11 +73,14 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    // chunk steps per SM at the compact kernel's rate (1.25 us) against the longest chain walked alone (1.95 us), with
-    // a margin of 15 % in favour of the look-ahead kernel
-    const long long total_steps = static_cast<long long>(prefix[N]) * H;
-    const bool many = static_cast<long long>(N) * H >= 2 * kPlanSms;
-    status[1] = (many && static_cast<long long>(longest) * 195 * kPlanSms * 100 <= total_steps * 125 * 85) ? 1 : 0;
+    // More chains than SMs.  Sequences of about the same length: the compact kernel holds twice as many chains at once,
+    // where the look-ahead kernel would need a second wave.  Otherwise, from two chains per SM on: chunk steps per SM at
+    // the compact kernel's rate (1.25 us) against the longest chain walked alone (1.95 us), with a margin of 15 % in
+    // favour of the look-ahead kernel.
+    const long long chains = static_cast<long long>(N) * H, total_steps = static_cast<long long>(prefix[N]) * H;
+    const bool alike = static_cast<long long>(longest) * N * 100 <= 130ll * prefix[N];
+    const bool throughput = chains >= 2 * kPlanSms && static_cast<long long>(longest) * 195 * kPlanSms * 100 <= total_steps * 125 * 85;
+    status[1] = (chains > kPlanSms && (alike || throughput)) ? 1 : 0;
   }
   // Chain order for the scan: longest sequences first (longest-processing-time-first packing of unequal chains
   // onto the SMs; the reference walks sequences in the given order).  order[] follows prefix[] in memory.

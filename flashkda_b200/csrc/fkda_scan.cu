@@ -1,8 +1,7 @@
 // Inter-chunk recurrence of the KDA prefill, compact form: one CTA walks the chunks of one (sequence, head)
 // chain with the 128x128 fp32 state resident in tensor memory, and two such CTAs share an SM.
 //
-// Replaces the reference's K2 (csrc/smxx/fwd_kernel2.cuh:115-839) for batches with many chains (at least two per
-// SM): every chain is a serial loop that leaves the SM idle most of the time, so two independent chains per SM
+// Replaces the reference's K2 (csrc/smxx/fwd_kernel2.cuh:115-839) for batches with more chains than SMs: every chain is a serial loop that leaves the SM idle most of the time, so two independent chains per SM
 // nearly double the throughput, where the look-ahead kernel (fkda_scan2.cu), which shortens the loop of one chain
 // per SM, would run the chains in more waves.  It is also the cross-check of the other recurrence kernels (flag
 // FKDA_FLAG_SCAN_PLAIN).  Per 32-token chunk, with S the state at the chunk start held as S^T [v lanes][k columns]:
