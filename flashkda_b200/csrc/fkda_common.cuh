@@ -318,6 +318,25 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
   return r;
 }
 
+// ---- small helpers shared by the token-parallel kernels ---------------------------------------------
+// byte offset of 16-byte chunk `chunk` of token row `row` in a staged [rows][256 B] tile whose chunks are XOR-swizzled by
+// the row index (conflict-free for row-wise 16-byte reads and for ldmatrix over eight consecutive rows)
+__device__ __forceinline__ int stage_off(int row, int chunk) { return row * 256 + ((chunk ^ (row & 7)) << 4); }
+
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+  f[0] = bf_lo(w.x); f[1] = bf_hi(w.x); f[2] = bf_lo(w.y); f[3] = bf_hi(w.y);
+  f[4] = bf_lo(w.z); f[5] = bf_hi(w.z); f[6] = bf_lo(w.w); f[7] = bf_hi(w.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+// transpose of an 8x8 tile of 16-bit elements held one row pair per thread (mma fragment layout)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
 // ---- kernel parameter blocks ---------------------------------------------------------------
 struct PrepParams {
   const __nv_bfloat16* q;

@@ -126,16 +126,6 @@ constexpr int kSmBeta = kSmSsq + 1024;       // [32] fp32 sigmoid(beta)
 constexpr int kPrepSmemBytes = kSmBeta + 128;
 static_assert(kPrepSmemBytes * 4 + 4 * 1024 <= 227 * 1024, "four CTAs per SM");
 
-// byte offset of 16-byte chunk `chunk` of token row `row` in a swizzled [32][256 B] staging tile
-__device__ __forceinline__ int stage_off(int row, int chunk) { return row * 256 + ((chunk ^ (row & 7)) << 4); }
-
-__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
-  f[0] = bf_lo(w.x); f[1] = bf_hi(w.x); f[2] = bf_lo(w.y); f[3] = bf_hi(w.y);
-  f[4] = bf_lo(w.z); f[5] = bf_hi(w.z); f[6] = bf_lo(w.w); f[7] = bf_hi(w.w);
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
-}
 
 // 16x16x128 product of two core-layout operands (rows of A times rows of B), fp32 accumulators
 // in the mma.sync C layout: acc[nt][0..1] -> (row lane/4, col 8nt + 2(lane%4) + {0,1}), acc[nt][2..3] -> row + 8.

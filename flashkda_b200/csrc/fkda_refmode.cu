@@ -41,13 +41,7 @@ constexpr int kState = (kBeta + 128 + 127) / 128 * 128;
 constexpr int kStride = 512 + 32;                // fp32 state rows, padded (see fkda_short16.cu)
 constexpr int kSmemBytes = kState + kD * kStride;
 
-__device__ __forceinline__ int stage_off(int row, int chunk) { return row * 256 + ((chunk ^ (row & 7)) << 4); }
 __device__ __forceinline__ float rbf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-  uint32_t y;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
 
 struct Params {
   const __nv_bfloat16* q;

@@ -48,21 +48,9 @@ constexpr int kStride16 = 256 + 16;              // bf16 rows: stride = 4 words 
 constexpr int kSmemBytes = kState + kD * kStride32;
 static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs per SM");
 
-__device__ __forceinline__ int stage_off(int row, int chunk) { return row * 256 + ((chunk ^ (row & 7)) << 4); }
-
-__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
-  f[0] = bf_lo(w.x); f[1] = bf_hi(w.x); f[2] = bf_lo(w.y); f[3] = bf_hi(w.y);
-  f[4] = bf_lo(w.z); f[5] = bf_hi(w.z); f[6] = bf_lo(w.w); f[7] = bf_hi(w.w);
-}
 __device__ __forceinline__ uint4 as_u4(const __nv_bfloat162 (&x)[4]) {
   return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
                     *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
-}
-// transpose of an 8x8 tile of 16-bit elements held one row pair per thread (mma fragment layout)
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-  uint32_t y;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
 }
 
 struct Params {
