@@ -394,28 +394,128 @@ constexpr int64_t kPlanSms = 148;      // SMs of a B200: what the kernel-selecti
 // Fixed-length sequences of at most this many tokens take the fused short-sequence kernel (fkda_short16.cu).
 constexpr int64_t kFusedMaxT = 32;
 
+// Duration of a pass of `ctas` CTAs in hundredths of one chunk step of the look-ahead kernel, per chunk of run length,
+// and the kernel that achieves it: the look-ahead kernel runs one CTA per SM, the compact kernel two at 1.58 times the
+// step (measured).
+inline int64_t pass_cost_x100(int64_t ctas, bool* compact, int64_t la_step_x100 = 100) {
+  const int64_t la = (ctas + kPlanSms - 1) / kPlanSms * la_step_x100, co = (ctas + 2 * kPlanSms - 1) / (2 * kPlanSms) * 158;
+  *compact = co < la;
+  return co < la ? co : la;
+}
+
 // How many runs to cut each sequence of a fixed-length batch into (1 = walk whole sequences), and their length in
-// chunks.  Costs are in chunk steps of one CTA: the launches proceed in waves of one CTA per SM, pass 1 holds
-// chains * (2 n - 3) CTAs and pass 2 chains * (n - 1), both walking ceil(chunks / n) chunks; chaining the maps
-// costs about three chunk steps per run.  The plan is a pure function of the sizes so that the workspace size and
-// the launch agree; it assumes the 148 SMs of a B200.
+// chunks.  Pass 1 holds chains * (2 n - 3) CTAs and pass 2 chains * (n - 1), both walking ceil(chunks / n) chunks, each
+// on whichever recurrence kernel gets that many CTAs through faster; chaining the maps costs about three chunk steps
+// per run.  The plan is a pure function of the sizes so that the workspace size and the launch agree; it assumes the
+// 148 SMs of a B200.
 inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
-  constexpr int64_t kSms = kPlanSms;
   *seg_chunks = 0;
-  if (chains <= 0 || chains * 3 > kSms || chunks < 48) return 1;
-  const int64_t whole = (chains + kSms - 1) / kSms * chunks;
+  if (chains <= 0 || chains * 3 > kPlanSms || chunks < 48) return 1;
+  bool c;
+  const int64_t whole = pass_cost_x100(chains, &c) * chunks;
   int64_t best = whole, best_n = 1;
   for (int64_t n = 3; n <= 64; ++n) {
     const int64_t len = (chunks + n - 1) / n;
     if (len < 8) break;
     if ((n - 1) * len >= chunks) continue;       // the last run would be empty
-    const int64_t w1 = (chains * (2 * n - 3) + kSms - 1) / kSms, w2 = (chains * (n - 1) + kSms - 1) / kSms;
-    const int64_t cost = (w1 + w2) * len + 3 * (n - 2) + 8;
+    // (a run walks its chunks about a tenth more slowly than a whole sequence; each pass costs about ten chunk steps of
+    // launch, set-up and state traffic; a step of the map chaining about four, per wave of its CTAs)
+    const int64_t cmb_ctas = chains * 16 > kPlanSms ? chains * 4 : chains * 16;
+    const int64_t cost = (pass_cost_x100(chains * (2 * n - 3), &c, 110) + pass_cost_x100(chains * (n - 1), &c, 110)) * len + 100 * 20 +
+                         100 * 4 * (n - 2) * ((cmb_ctas + kPlanSms - 1) / kPlanSms);
     if (cost < best) { best = cost; best_n = n; }
   }
   if (best_n == 1 || best * 4 > whole * 3) return 1;
   *seg_chunks = static_cast<int>((chunks + best_n - 1) / best_n);
   return static_cast<int>(best_n);
+}
+
+// What one CTA of a recurrence kernel walks: a whole (sequence, head) chain, or, in the segment-parallel form (kSeg), one
+// run of it in one of three variants - 0: the recurrence proper; 1: offset half of the run's affine map (zero state in, no
+// output); 2: transition half (identity in, u' taken as zero, no output).  Pass 1 holds, per chain, run 0 (variant 0)
+// followed by (variant 1, variant 2) of the runs 1 .. n_segs-2; pass 2 holds the runs 1 .. n_segs-1 (variant 0).
+struct ChainView {
+  int n, h;
+  int64_t bos, eos;            // tokens of this walk
+  int chunk_base, nchunks;     // first record of this walk (index within the head's records), number of chunks
+  const void* init_base;       // [128 v][128 k] block the walk starts from (init_mode 1: fp32, 2: bf16), or nothing
+  int init_mode;               // 0 = zero, 1 = fp32, 2 = bf16, 3 = identity
+  void* fin_base;              // where the state goes afterwards, or nullptr
+  int fin_fp32;
+  bool write_out, zero_up;
+};
+template <bool kSeg>
+__device__ __forceinline__ ChainView chain_view(const ScanParams& p, int block) {
+  ChainView cv;
+  int chain = block, seg = 0, variant = 0;
+  if constexpr (kSeg) {
+    const int per = p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
+    chain = block / per;
+    const int j = block - chain * per;
+    if (p.seg_pass == 1) {
+      if (j > 0) { seg = 1 + ((j - 1) >> 1); variant = 1 + ((j - 1) & 1); }
+    } else {
+      seg = 1 + j;
+    }
+  }
+  const int slot = chain / p.H;
+  cv.h = chain - slot * p.H;
+  cv.n = p.seq_order != nullptr ? p.seq_order[slot] : slot;     // varlen: longest sequences first
+  if (p.cu_seqlens != nullptr) {
+    cv.bos = p.cu_seqlens[cv.n];
+    cv.eos = p.cu_seqlens[cv.n + 1];
+    cv.bos = cv.bos < 0 ? 0 : (cv.bos > p.T_total ? p.T_total : cv.bos);
+    cv.eos = cv.eos < cv.bos ? cv.bos : (cv.eos > p.T_total ? p.T_total : cv.eos);
+    cv.chunk_base = p.chunk_prefix[cv.n];
+  } else {
+    cv.bos = static_cast<int64_t>(cv.n) * p.T;
+    cv.eos = cv.bos + p.T;
+    cv.chunk_base = cv.n * static_cast<int>((p.T + kChunk - 1) / kChunk);
+  }
+  cv.nchunks = static_cast<int>((cv.eos - cv.bos + kChunk - 1) / kChunk);
+  {  // never read past the records of this head, whatever cu_seqlens claims
+    const int avail = p.total_chunks > cv.chunk_base ? p.total_chunks - cv.chunk_base : 0;
+    if (cv.nchunks > avail) cv.nchunks = avail;
+  }
+  const size_t chain_state = (static_cast<size_t>(cv.n) * p.H + cv.h) * kD * kD;
+  cv.init_base = nullptr;
+  cv.init_mode = 0;
+  cv.fin_base = nullptr;
+  cv.fin_fp32 = p.state_fp32;
+  if (p.initial_state != nullptr) {
+    cv.init_mode = p.state_fp32 ? 1 : 2;
+    cv.init_base = static_cast<const uint8_t*>(p.initial_state) + chain_state * (p.state_fp32 ? 4 : 2);
+  }
+  if (p.final_state != nullptr) cv.fin_base = static_cast<uint8_t*>(p.final_state) + chain_state * (p.state_fp32 ? 4 : 2);
+  if constexpr (kSeg) {
+    float* slots = p.seg_buf + (static_cast<size_t>(cv.n) * p.H + cv.h) * p.n_segs * 3 * kSegSlotFloats;
+    const int c_begin = seg * p.seg_chunks < cv.nchunks ? seg * p.seg_chunks : cv.nchunks;
+    const int c_end = (seg == p.n_segs - 1 || (seg + 1) * p.seg_chunks > cv.nchunks) ? cv.nchunks : (seg + 1) * p.seg_chunks;
+    if (seg < p.n_segs - 1) {
+      const int64_t run_end = cv.bos + static_cast<int64_t>(c_end) * kChunk;
+      cv.eos = run_end < cv.eos ? run_end : cv.eos;
+    }
+    cv.bos += static_cast<int64_t>(c_begin) * kChunk;
+    cv.chunk_base += c_begin;
+    cv.nchunks = c_end - c_begin;
+    if (p.seg_pass == 1) {
+      if (variant == 0) {
+        cv.fin_base = slots + (1 * 3 + 2) * kSegSlotFloats;                 // state at the start of run 1
+      } else {
+        cv.init_mode = variant == 2 ? 3 : 0;
+        cv.init_base = nullptr;
+        cv.fin_base = slots + (seg * 3 + (variant == 2 ? 0 : 1)) * kSegSlotFloats;
+      }
+      cv.fin_fp32 = 1;
+    } else {
+      cv.init_mode = 1;
+      cv.init_base = slots + (seg * 3 + 2) * kSegSlotFloats;
+      if (seg != p.n_segs - 1) cv.fin_base = nullptr;
+    }
+  }
+  cv.write_out = !kSeg || variant == 0;
+  cv.zero_up = kSeg && variant == 2;
+  return cv;
 }
 
 }  // namespace fkda

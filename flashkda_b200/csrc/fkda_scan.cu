@@ -46,6 +46,8 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
   return __all_sync(0xffffffffu, ok);
 }
 
+// kSeg: CTAs walk runs of a sequence (segment-parallel form, see fkda_segscan.cu) instead of whole sequences
+template <bool kSeg>
 __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -57,28 +59,11 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
 
   if (p.select != nullptr && *p.select != p.select_want) return;     // the other recurrence kernel was chosen
   // ---- chain -> tokens and records ---------------------------------------------------------------------
-  const int chain = blockIdx.x;
-  const int slot = chain / p.H, h = chain - slot * p.H;
-  const int n = p.seq_order != nullptr ? p.seq_order[slot] : slot;     // varlen: longest sequences first
-  int64_t bos, eos;
-  int chunk_base;
-  if (p.cu_seqlens != nullptr) {
-    bos = p.cu_seqlens[n];
-    eos = p.cu_seqlens[n + 1];
-    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
-    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
-    chunk_base = p.chunk_prefix[n];
-  } else {
-    bos = static_cast<int64_t>(n) * p.T;
-    eos = bos + p.T;
-    chunk_base = n * static_cast<int>((p.T + kChunk - 1) / kChunk);
-  }
-  int nchunks = static_cast<int>((eos - bos + kChunk - 1) / kChunk);
-  {  // never read past the records of this head, whatever cu_seqlens claims
-    const int avail = p.total_chunks > chunk_base ? p.total_chunks - chunk_base : 0;
-    if (nchunks > avail) nchunks = avail;
-  }
-  const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + chunk_base) * kRecBytes;
+  const ChainView cv = chain_view<kSeg>(p, blockIdx.x);
+  const int h = cv.h;
+  const int64_t bos = cv.bos, eos = cv.eos;
+  const int nchunks = cv.nchunks;
+  const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + cv.chunk_base) * kRecBytes;
 
   // ---- setup -----------------------------------------------------------------------------------------------
   if (tid == 0) {
@@ -176,7 +161,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
     const int qd = warp & 3;
     const int v = qd * 32 + lane;
     const uint32_t tq = tmem + (static_cast<uint32_t>(qd * 32) << 16);
-    const size_t row_off = ((static_cast<size_t>(n) * p.H + h) * kD + v) * kD;   // row v of this chain's state
+    const size_t row_off = static_cast<size_t>(v) * kD;                          // row v of this walk's state block
     uint8_t* ut_row = smem + kSmUt + (v >> 3) * 512 + (v & 7) * 16;    // + 128 * (tok / 8)
 
     // ---- initial state -> TMEM (pre-decayed by the first chunk's e) and its bf16 operand copy --------------
@@ -187,9 +172,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t x[32];
-        if (p.initial_state != nullptr) {
-          if (p.state_fp32) {
-            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.initial_state) + row_off + cb * 32);
+        if (cv.init_mode == 1 || cv.init_mode == 2) {
+          if (cv.init_mode == 1) {
+            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(cv.init_base) + row_off + cb * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float4 f = __ldg(src + i);
@@ -197,7 +182,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
               x[4 * i + 2] = __float_as_uint(f.z); x[4 * i + 3] = __float_as_uint(f.w);
             }
           } else {
-            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.initial_state) + row_off + cb * 32);
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(cv.init_base) + row_off + cb * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const uint4 w = __ldg(src + i);
@@ -209,7 +194,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] = 0u;
+          for (int i = 0; i < 32; ++i) x[i] = (cv.init_mode == 3 && cb * 32 + i == v) ? 0x3f800000u : 0u;
         }
         if (nchunks > 0) {
           uint32_t y[16];
@@ -243,7 +228,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
         float u[32];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const uint4 t = *reinterpret_cast<const uint4*>(up_row + i * 128);
+          const uint4 t = cv.zero_up ? make_uint4(0u, 0u, 0u, 0u) : *reinterpret_cast<const uint4*>(up_row + i * 128);
           u[8 * i + 0] = bf_lo(t.x) - __uint_as_float(w[8 * i + 0]);
           u[8 * i + 1] = bf_hi(t.x) - __uint_as_float(w[8 * i + 1]);
           u[8 * i + 2] = bf_lo(t.y) - __uint_as_float(w[8 * i + 2]);
@@ -293,7 +278,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
     }
 
     // ---- final state -> global -------------------------------------------------------------------------------
-    if (!failed && p.final_state != nullptr) {
+    if (!failed && cv.fin_base != nullptr) {
       bool ok2 = true;
       if (nchunks > 0) ok2 = warp_wait(bar(BAR_SFULL), (nchunks - 1) & 1, abort_flag);
       if (ok2) {
@@ -303,14 +288,14 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
           uint32_t x[32];
           tmem_ld32(tq + kColS + cb * 32, x);
           tmem_wait_ld();
-          if (p.state_fp32) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.final_state) + row_off + cb * 32);
+          if (cv.fin_fp32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(cv.fin_base) + row_off + cb * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]), __uint_as_float(x[4 * i + 2]),
                                    __uint_as_float(x[4 * i + 3]));
           } else {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.final_state) + row_off + cb * 32);
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cv.fin_base) + row_off + cb * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
               dst[i] = make_uint4(pack_bf16(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
@@ -346,7 +331,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = i * 8 + (lane >> 2), c8 = (lane & 3) * 8;
-        if (r < valid) {
+        if (cv.write_out && r < valid) {
           const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 32 + c8);
           *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(tok0 + r) * p.H + h) * kD + qd * 32 + c8) = val;
         }
@@ -367,11 +352,13 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
 }
 
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+  int64_t chains = static_cast<int64_t>(p.N) * p.H;
+  if (p.seg_chunks > 0) chains *= p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
+  if (chains <= 0) return cudaSuccess;
+  auto kernel = p.seg_chunks > 0 ? scan_kernel<true> : scan_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
   if (e != cudaSuccess) return e;
-  const int64_t chains = static_cast<int64_t>(p.N) * p.H;
-  if (chains == 0) return cudaSuccess;
-  scan_kernel<<<static_cast<unsigned>(chains), kScanThreads, kScanSmemBytes, stream>>>(p);
+  kernel<<<static_cast<unsigned>(chains), kScanThreads, kScanSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 

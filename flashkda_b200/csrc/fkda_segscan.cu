@@ -12,20 +12,22 @@
 namespace fkda {
 
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
+cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 
 namespace {
 
-constexpr int kRowsPerCta = 8;
 constexpr int kMapBytes = kD * kD * 4;
 constexpr int kCmbM = 0;                                  // 2 x [128][128] fp32: transition maps, double-buffered
-constexpr int kCmbZ = kCmbM + 2 * kMapBytes;              // [kRowsPerCta][128] fp32: this CTA's rows of the state
-constexpr int kCmbBars = kCmbZ + kRowsPerCta * kD * 4;
+constexpr int kCmbZ = kCmbM + 2 * kMapBytes;              // [rows per CTA <= 32][128] fp32: this CTA's rows of the state
+constexpr int kCmbBars = kCmbZ + 32 * kD * 4;
 constexpr int kCmbSmemBytes = kCmbBars + 64 + 128;
 
 // Z_start[run + 1] = Z_start[run] M[run] + N[run] for run = 1 .. n_segs-2; rows of Z are independent, so each CTA
-// carries kRowsPerCta of them through all runs.  The 64 KB maps arrive by bulk copies two runs ahead, so the serial
+// carries kRows of them (8, or 32 when there are many chains) through all runs.  The 64 KB maps arrive by bulk copies two runs ahead, so the serial
 // chain of runs sees shared-memory latency only.  fp32 throughout.
+template <int kRows>
 __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_segs, int* status) {
+  constexpr int kPer = kRows / 2;                        // rows per thread
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
   const uint32_t sbase = smem_u32(smem);
@@ -46,11 +48,11 @@ __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_
     for (int run = 1; run <= 2 && run + 1 < n_segs; ++run) load_map(run);
   }
   const int k = tid & (kD - 1);
-  const int rl = (tid >> 7) * 4;                         // this thread's four rows within the CTA's block
-  const int r0 = blockIdx.y * kRowsPerCta + rl;
-  float acc[4];
+  const int rl = (tid >> 7) * kPer;                      // this thread's rows within the CTA's block
+  const int r0 = blockIdx.y * kRows + rl;
+  float acc[kPer];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < kPer; ++i) {
     acc[i] = slots[(1 * 3 + 2) * kSegSlotFloats + static_cast<size_t>(r0 + i) * kD + k];
     z[rl + i][k] = acc[i];
   }
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_
     const int b = (run - 1) & 1;
     const float* N = slots + (run * 3 + 1) * kSegSlotFloats;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] = N[static_cast<size_t>(r0 + i) * kD + k];
+    for (int i = 0; i < kPer; ++i) acc[i] = N[static_cast<size_t>(r0 + i) * kD + k];
     const bool ok = mbar_wait(sbase + kCmbBars + 8 * b, ((run - 1) >> 1) & 1, abort_flag, 32);
     if (!__syncthreads_and(ok)) {
       if (tid == 0) {
@@ -78,7 +80,7 @@ __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_
     for (int j = 0; j < kD; j += 4) {
       const float m0 = M[(j + 0) * kD + k], m1 = M[(j + 1) * kD + k], m2 = M[(j + 2) * kD + k], m3 = M[(j + 3) * kD + k];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < kPer; ++i) {
         const float4 zr = *reinterpret_cast<const float4*>(&z[rl + i][j]);
         acc[i] = fmaf(zr.x, m0, acc[i]);
         acc[i] = fmaf(zr.y, m1, acc[i]);
@@ -90,7 +92,7 @@ __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_
     if (tid == 0 && run + 3 < n_segs) load_map(run + 2);
     float* zs = slots + ((run + 1) * 3 + 2) * kSegSlotFloats;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < kPer; ++i) {
       z[rl + i][k] = acc[i];
       zs[static_cast<size_t>(r0 + i) * kD + k] = acc[i];
     }
@@ -105,19 +107,27 @@ cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_ch
   p.seg_chunks = seg_chunks;
   p.n_segs = n_segs;
   p.seg_buf = seg_buf;
+  // either recurrence kernel can walk the runs: whichever gets the pass's CTAs through in less time
+  const int64_t chains = static_cast<int64_t>(p.N) * p.H;
+  bool compact1, compact2;
+  pass_cost_x100(chains * (2 * n_segs - 3), &compact1);
+  pass_cost_x100(chains * (n_segs - 1), &compact2);
   p.seg_pass = 1;
-  cudaError_t e = launch_scan2(p, stream);
+  cudaError_t e = compact1 ? launch_scan(p, stream) : launch_scan2(p, stream);
   if (e != cudaSuccess) return e;
   if (n_segs > 2) {
-    e = cudaFuncSetAttribute(seg_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmbSmemBytes);
+    // one CTA per SM (two 64 KB map buffers): 8 rows per CTA while that fills at most one wave, else 32
+    const bool wide = chains * (kD / 8) > kPlanSms;
+    auto kernel = wide ? seg_combine_kernel<32> : seg_combine_kernel<8>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmbSmemBytes);
     if (e != cudaSuccess) return e;
-    const dim3 grid(static_cast<unsigned>(p.N) * p.H, kD / kRowsPerCta);
-    seg_combine_kernel<<<grid, 256, kCmbSmemBytes, stream>>>(seg_buf, n_segs, p.status);
+    const dim3 grid(static_cast<unsigned>(chains), kD / (wide ? 32 : 8));
+    kernel<<<grid, 256, kCmbSmemBytes, stream>>>(seg_buf, n_segs, p.status);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   p.seg_pass = 2;
-  return launch_scan2(p, stream);
+  return compact2 ? launch_scan(p, stream) : launch_scan2(p, stream);
 }
 
 }  // namespace fkda
