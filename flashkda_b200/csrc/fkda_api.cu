@@ -24,7 +24,8 @@ cudaError_t launch_refmode(const __nv_bfloat16* q, const __nv_bfloat16* k, const
                            const __nv_bfloat16* beta, const float* A_log, const float* dt_bias, const void* initial_state,
                            void* final_state, __nv_bfloat16* out, const int64_t* cu_seqlens, int64_t N, int64_t T, int64_t T_total,
                            int H, int state_fp32, float scale, float gate_scale, cudaStream_t stream);
-cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, cudaStream_t stream);
+cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, int kernel_choice,
+                                  cudaStream_t stream);
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
 cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream);
@@ -67,8 +68,9 @@ struct Layout {
 // kernel-selection flags, else planned from the sizes.
 int segments_for(int64_t chains, int64_t chunks_per_seq, int64_t flags, int* seg_chunks) {
   *seg_chunks = 0;
-  if (flags & (FKDA_FLAG_SCAN_SIMT | FKDA_FLAG_SCAN_PLAIN | FKDA_FLAG_SCAN_NO_SEGMENTS)) return 1;
+  if (flags & (FKDA_FLAG_SCAN_SIMT | FKDA_FLAG_SCAN_NO_SEGMENTS)) return 1;
   const int64_t forced = (flags >> 8) & 0xff;
+  if ((flags & FKDA_FLAG_SCAN_PLAIN) && forced < 2) return 1;
   if (forced >= 2) {
     if (chunks_per_seq < forced) return 1;
     *seg_chunks = static_cast<int>((chunks_per_seq + forced - 1) / forced);
@@ -193,7 +195,11 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   s.state_fp32 = p->state_dtype == FKDA_STATE_FP32 ? 1 : 0;
   cudaError_t e;
   if (p->flags & FKDA_FLAG_SCAN_SIMT) e = fkda::launch_scan_simt(s, stream);
-  else if (p->flags & FKDA_FLAG_SCAN_PLAIN) e = fkda::launch_scan(s, stream);
+  else if ((p->flags & (FKDA_FLAG_SCAN_PLAIN | FKDA_FLAG_SCAN_LOOKAHEAD)) && L.n_segs > 1) {
+    // a forced run count together with a forced kernel: both passes on that kernel
+    e = fkda::launch_scan_segmented(s, L.n_segs, L.seg_chunks, reinterpret_cast<float*>(ws + L.seg_off),
+                                    (p->flags & FKDA_FLAG_SCAN_PLAIN) ? 1 : 2, stream);
+  } else if (p->flags & FKDA_FLAG_SCAN_PLAIN) e = fkda::launch_scan(s, stream);
   else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->cu_seqlens == nullptr && p->T > 0 && p->T <= 2 * fkda::kChunk) {
     // many short chains: the state-I/O-oriented persistent kernel
     int dev = 0, sms = 0;
@@ -217,7 +223,7 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     }
   } else if (L.n_segs > 1) {
     // few long chains: cut them into runs that are walked in parallel
-    e = fkda::launch_scan_segmented(s, L.n_segs, L.seg_chunks, reinterpret_cast<float*>(ws + L.seg_off), stream);
+    e = fkda::launch_scan_segmented(s, L.n_segs, L.seg_chunks, reinterpret_cast<float*>(ws + L.seg_off), 0, stream);
   } else e = fkda::launch_scan2(s, stream);
   if (e != cudaSuccess) return cuda_fail(e, "scan launch");
   return FKDA_OK;

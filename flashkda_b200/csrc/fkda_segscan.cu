@@ -102,7 +102,8 @@ __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_
 
 }  // namespace
 
-cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, cudaStream_t stream) {
+cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, int kernel_choice,
+                                  cudaStream_t stream) {
   ScanParams p = base;
   p.seg_chunks = seg_chunks;
   p.n_segs = n_segs;
@@ -112,6 +113,7 @@ cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_ch
   bool compact1, compact2;
   pass_cost_x100(chains * (2 * n_segs - 3), &compact1);
   pass_cost_x100(chains * (n_segs - 1), &compact2);
+  if (kernel_choice) compact1 = compact2 = kernel_choice == 1;   // forced: 1 compact, 2 look-ahead
   p.seg_pass = 1;
   cudaError_t e = compact1 ? launch_scan(p, stream) : launch_scan2(p, stream);
   if (e != cudaSuccess) return e;

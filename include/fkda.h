@@ -44,7 +44,9 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 #define FKDA_FLAG_REFERENCE_ROUNDING 0x20u
 #define FKDA_FLAG_SCAN_NO_SEGMENTS 0x8u /* never cut sequences into runs that are walked in parallel */
 /* Cut every sequence of a fixed-length batch into n (2..255) runs walked in parallel, whatever the planner would
- * choose; the workspace must then be sized with fkda_get_workspace_size_flags. */
+ * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
+ * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster
+ * one for its number of CTAs). */
 #define FKDA_FLAG_SEGMENTS(n) (((uint32_t)(n) & 0xffu) << 8)
 
 typedef struct fkda_fwd_params {

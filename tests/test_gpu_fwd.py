@@ -258,6 +258,32 @@ def test_segment_parallel_scan_forced_runs(runs, state):
     assert rel_fro(s_seg, s_ref) <= 5e-3
 
 
+@pytest.mark.parametrize("kernel", ["compact", "lookahead"])
+def test_segment_parallel_scan_on_either_recurrence_kernel(kernel):
+    """Both recurrence kernels can walk the runs; with a forced kernel both passes use it.  Twelve chains, so the
+    chaining of the maps runs in its many-chain shape (32 state rows per CTA); an incoming state that matters."""
+    flag = F.FLAG_SCAN_PLAIN if kernel == "compact" else F.FLAG_SCAN_LOOKAHEAD
+    w = Workload("segk", H=6, B=2, T=32 * 21 + 11, state_in="fp32", state_out="fp32", state_std=0.5, seed=5, lower_bound=-1.0)
+    x = make_inputs(w)
+    o_seg, s_seg = run_gpu(x, torch.float32, flag | F.FLAG_SEGMENTS(4))
+    o_ref, s_ref = run_gpu(x, torch.float32, F.FLAG_SCAN_LOOKAHEAD)
+    check_against_f64(x, o_seg, s_seg, f"segments on the {kernel} kernel")
+    assert max_abs(o_seg, o_ref) <= 1e-2 and rel_fro(s_seg, s_ref) <= 5e-3
+
+
+def test_segment_parallel_scan_planned_many_chains():
+    """Twenty chains of 128 chunks: the planner cuts them, the first pass has more CTAs than SMs and runs on the
+    compact kernel, the second on the look-ahead kernel."""
+    w = Workload("segmany", H=10, B=2, T=4096 - 13, state_in="bf16", state_out="bf16", state_std=0.5, seed=9)
+    runs, run_chunks = F.plan_segments(w.H * w.B, (w.T + 31) // 32)
+    assert runs >= 3 and w.H * w.B * (2 * runs - 3) > 148 >= w.H * w.B * (runs - 1), (runs, run_chunks)
+    x = make_inputs(w)
+    o1, s1 = run_gpu(x, torch.bfloat16)
+    check_against_f64(x, o1, s1, f"planned runs={runs}x{run_chunks}, 20 chains")
+    o0, s0 = run_gpu(x, torch.bfloat16, F.FLAG_SCAN_NO_SEGMENTS)
+    assert max_abs(o1, o0) <= 1e-2 and rel_fro(s1, s0) <= 2e-2
+
+
 def test_segment_parallel_scan_planned():
     """A batch with few long chains takes the segment-parallel path by itself (the planner's choice), within the
     same tolerances; a second call on the same workspace reproduces the first bit for bit."""
