@@ -86,6 +86,66 @@ __device__ __forceinline__ void pack32(const uint32_t (&x)[32], uint32_t (&y)[16
   for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
 }
 
+// The state warps' per-chunk loop: decay the updated state for the next chunk and refresh its bf16 copy.  A function
+// of its own (not inlined) so that its registers are allotted independently of the other warp roles.
+__device__ __noinline__ bool state_warp_loop(uint8_t* smem, uint32_t tq, int grp, int nchunks, int warp, int lane,
+                                             unsigned long long* trace) {
+  const uint32_t sbase = smem_u32(smem);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
+  auto full_bar = [&](int c) { return bar(BAR_FULL + c % kStages); };
+  auto full_par = [&](int c) { return static_cast<uint32_t>((c / kStages) & 1); };
+  bool failed = false;
+  for (int c = 0; c + 1 < nchunks && !failed; ++c) {
+    if (!warp_wait(full_bar(c + 1), full_par(c + 1), abort_flag)) { failed = true; break; }
+    // The decay factors of the next chunk are the same for every lane.  Each lane fetches two of this group's
+    // 64 factors now (before the state update lands) and they are handed round by shuffles below: no
+    // shared-memory latency between the TMEM load and store, and no 64 extra registers.
+    const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 64 * grp;
+    const float e_lo = e[lane], e_hi = e[32 + lane];
+    if (!warp_wait(bar(BAR_SFULL), c & 1, abort_flag)) { failed = true; break; }
+    const int trole = 2;
+    const bool tr_on = (warp == 8) && lane == 0;
+    if (tr_on) FKDA_TRACE(trole, c, 0);
+    tc_fence_after();
+    if (tr_on) FKDA_TRACE(trole, c, 1);
+    uint32_t x0[32], x1[32], y[16];
+    tmem_ld32(tq + kColS + 64 * grp, x0);
+    tmem_ld32(tq + kColS + 64 * grp + 32, x1);
+    tmem_wait_ld();
+    if (tr_on) FKDA_TRACE(trole, c, 2);
+    // the bf16 copy first: the products that read it head the longest chain of the step
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x0[i] = __float_as_uint(__uint_as_float(x0[i]) * __shfl_sync(0xffffffffu, e_lo, i));
+    if (tr_on) FKDA_TRACE(trole, c, 6);
+    pack32(x0, y);
+    tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp, y);
+    if (tr_on) FKDA_TRACE(trole, c, 7);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x1[i] = __float_as_uint(__uint_as_float(x1[i]) * __shfl_sync(0xffffffffu, e_hi, i));
+    pack32(x1, y);
+    tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp + 16, y);
+    tmem_wait_st();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(BAR_SBDREADY + ((c + 1) & 1)));
+    tmem_st32(tq + kColS + 64 * grp, x0);
+    tmem_st32(tq + kColS + 64 * grp + 32, x1);
+    if (tr_on) FKDA_TRACE(trole, c, 4);
+    tmem_wait_st();
+    if (tr_on) FKDA_TRACE(trole, c, 5);
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      if (tr_on) FKDA_TRACE(trole, c, 3);
+      FKDA_TRACE(5, c, warp - 8);          // arrival time of each of the eight state warps
+      mbar_arrive(bar(BAR_SREADY));
+      mbar_arrive(bar(BAR_EMPTY + (c + 1) % kStages));    // done with e of record c+1
+    }
+  }
+  return failed;
+}
+
 // kSeg: CTAs walk runs of a sequence (segment-parallel form) instead of whole sequences
 template <bool kSeg>
 __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, unsigned long long* trace_buf) {
@@ -463,53 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     }
 
     // ---- per chunk: decay the updated state for the next chunk and refresh its bf16 copy ------------------
-    for (int c = 0; c + 1 < nchunks && !failed; ++c) {
-      if (!warp_wait(full_bar(c + 1), full_par(c + 1), abort_flag)) { failed = true; break; }
-      // The decay factors of the next chunk are the same for every lane.  Each lane fetches two of this group's
-      // 64 factors now (before the state update lands) and they are handed round by shuffles below: no
-      // shared-memory latency between the TMEM load and store, and no 64 extra registers.
-      const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 64 * grp;
-      const float e_lo = e[lane], e_hi = e[32 + lane];
-      if (!warp_wait(bar(BAR_SFULL), c & 1, abort_flag)) { failed = true; break; }
-      const int trole = 2;
-      const bool tr_on = (warp == 8) && lane == 0;
-      if (tr_on) FKDA_TRACE(trole, c, 0);
-      tc_fence_after();
-      if (tr_on) FKDA_TRACE(trole, c, 1);
-      uint32_t x0[32], x1[32], y[16];
-      tmem_ld32(tq + kColS + 64 * grp, x0);
-      tmem_ld32(tq + kColS + 64 * grp + 32, x1);
-      tmem_wait_ld();
-      if (tr_on) FKDA_TRACE(trole, c, 2);
-      // the bf16 copy first: the products that read it head the longest chain of the step
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x0[i] = __float_as_uint(__uint_as_float(x0[i]) * __shfl_sync(0xffffffffu, e_lo, i));
-      if (tr_on) FKDA_TRACE(trole, c, 6);
-      pack32(x0, y);
-      tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp, y);
-      if (tr_on) FKDA_TRACE(trole, c, 7);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x1[i] = __float_as_uint(__uint_as_float(x1[i]) * __shfl_sync(0xffffffffu, e_hi, i));
-      pack32(x1, y);
-      tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp + 16, y);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_SBDREADY + ((c + 1) & 1)));
-      tmem_st32(tq + kColS + 64 * grp, x0);
-      tmem_st32(tq + kColS + 64 * grp + 32, x1);
-      if (tr_on) FKDA_TRACE(trole, c, 4);
-      tmem_wait_st();
-      if (tr_on) FKDA_TRACE(trole, c, 5);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (tr_on) FKDA_TRACE(trole, c, 3);
-        FKDA_TRACE(5, c, warp - 8);          // arrival time of each of the eight state warps
-        mbar_arrive(bar(BAR_SREADY));
-        mbar_arrive(bar(BAR_EMPTY + (c + 1) % kStages));    // done with e of record c+1
-      }
-    }
+    if (!failed) failed = state_warp_loop(smem, tq, grp, nchunks, warp, lane, trace);
 
     // ---- final state -> global -------------------------------------------------------------------------------
     void* fin_base;
