@@ -420,7 +420,7 @@ inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
     if ((n - 1) * len >= chunks) continue;       // the last run would be empty
     // (a run walks its chunks about a tenth more slowly than a whole sequence; each pass costs about ten chunk steps of
     // launch, set-up and state traffic; a step of the map chaining about four, per wave of its CTAs)
-    const int64_t cmb_ctas = chains * 16 > kPlanSms ? chains * 4 : chains * 16;
+    const int64_t cmb_ctas = chains * 16 <= kPlanSms ? chains * 16 : (chains * 8 <= kPlanSms ? chains * 8 : chains * 4);
     const int64_t cost = (pass_cost_x100(chains * (2 * n - 3), &c, 110) + pass_cost_x100(chains * (n - 1), &c, 110)) * len + 100 * 20 +
                          100 * 4 * (n - 2) * ((cmb_ctas + kPlanSms - 1) / kPlanSms);
     if (cost < best) { best = cost; best_n = n; }

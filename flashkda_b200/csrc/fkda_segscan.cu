@@ -23,7 +23,7 @@ constexpr int kCmbBars = kCmbZ + 32 * kD * 4;
 constexpr int kCmbSmemBytes = kCmbBars + 64 + 128;
 
 // Z_start[run + 1] = Z_start[run] M[run] + N[run] for run = 1 .. n_segs-2; rows of Z are independent, so each CTA
-// carries kRows of them (8, or 32 when there are many chains) through all runs.  The 64 KB maps arrive by bulk copies two runs ahead, so the serial
+// carries kRows of them (8, 16 or 32, by the number of chains) through all runs.  The 64 KB maps arrive by bulk copies two runs ahead, so the serial
 // chain of runs sees shared-memory latency only.  fp32 throughout.
 template <int kRows>
 __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_segs, int* status) {
@@ -118,12 +118,13 @@ cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_ch
   cudaError_t e = compact1 ? launch_scan(p, stream) : launch_scan2(p, stream);
   if (e != cudaSuccess) return e;
   if (n_segs > 2) {
-    // one CTA per SM (two 64 KB map buffers): 8 rows per CTA while that fills at most one wave, else 32
-    const bool wide = chains * (kD / 8) > kPlanSms;
-    auto kernel = wide ? seg_combine_kernel<32> : seg_combine_kernel<8>;
+    // one CTA per SM (two 64 KB map buffers); a step costs about 1.4 us + 0.3 us per row, so: the fewest rows per CTA
+    // (8, 16, 32) that still keep the CTAs within one wave
+    const int rows = chains * (kD / 8) <= kPlanSms ? 8 : (chains * (kD / 16) <= kPlanSms ? 16 : 32);
+    auto kernel = rows == 32 ? seg_combine_kernel<32> : (rows == 16 ? seg_combine_kernel<16> : seg_combine_kernel<8>);
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmbSmemBytes);
     if (e != cudaSuccess) return e;
-    const dim3 grid(static_cast<unsigned>(chains), kD / (wide ? 32 : 8));
+    const dim3 grid(static_cast<unsigned>(chains), kD / rows);
     kernel<<<grid, 256, kCmbSmemBytes, stream>>>(seg_buf, n_segs, p.status);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
