@@ -90,6 +90,13 @@ int fkda_fwd_static_ws(const fkda_fwd_params* p, void* cuda_stream) {
   fkda_fwd_params q = *p;
   q.workspace = ws;
   q.workspace_bytes = kStaticWsBytes;
+  if (p->cu_seqlens == nullptr) {
+    // few long chains would be cut into runs, which needs room beyond the records: where that room is missing the
+    // sequences are walked whole instead (slower, same result) rather than refused
+    int64_t with_runs = 0;
+    if (fkda_get_workspace_size_flags(p->B * p->T, p->H, p->N, p->flags, &with_runs) == FKDA_OK && with_runs > kStaticWsBytes)
+      q.flags |= FKDA_FLAG_SCAN_NO_SEGMENTS;
+  }
   const int rc = fkda_fwd(&q, cuda_stream);
   if (rc != FKDA_OK) snprintf(g_msg, sizeof(g_msg), "%s", fkda_last_error());
   return rc;

@@ -79,3 +79,12 @@ def test_static_scratch_entry_point_matches_fkda_fwd_twice_in_a_row():
     assert b"built-in scratch" in L.fkda_static_ws_last_error()
     torch.cuda.synchronize()
     assert float(out.float().abs().max()) == 0.0
+
+
+def test_static_scratch_walks_whole_sequences_when_the_runs_do_not_fit():
+    """One long chain: the planner would cut it into runs, whose scratch does not fit the built-in array beside the
+    records; the call is then served by the walk over whole sequences instead of being refused."""
+    w = Workload("long", H=1, B=1, T=57600, state_in="fp32", state_out="fp32", seed=34)
+    runs, _ = F.plan_segments(1, w.T // 32)
+    assert runs > 1 and F.get_workspace_size(w.T, 1, 1) > (64 << 20) >= F.get_workspace_size(w.T, 1, 1, F.FLAG_SCAN_NO_SEGMENTS)
+    _run_both(w)
