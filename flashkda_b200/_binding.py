@@ -23,7 +23,7 @@ FLAG_REFERENCE_ROUNDING = 0x20
 
 
 def FLAG_SEGMENTS(n: int) -> int:
-    """Flag bits that cut every sequence of a fixed-length batch into `n` runs walked in parallel."""
+    """Flag bits that cut every sequence of the batch into `n` runs walked in parallel."""
     return (int(n) & 0xff) << 8
 _STATE_NONE, _STATE_BF16, _STATE_FP32 = 0, 1, 2
 
@@ -101,7 +101,8 @@ def get_workspace_size(T_total: int, H: int, N: int = 1, flags: int = 0) -> int:
 
 
 def plan_segments(chains: int, chunks_per_sequence: int):
-    """(runs per sequence, chunks per run) the recurrence uses for a fixed-length batch; (1, 0) = whole sequences."""
+    """(runs per sequence, chunks per run) the recurrence uses for a batch of `chains` chains of that many chunks (varlen: the
+    average sequence length; the run length then follows the longest sequence); (1, 0) = whole sequences."""
     a, b = ctypes.c_int(0), ctypes.c_int(0)
     _check(lib().fkda_plan_segments(chains, chunks_per_sequence, ctypes.byref(a), ctypes.byref(b)))
     return a.value, b.value

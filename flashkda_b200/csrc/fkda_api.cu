@@ -10,7 +10,8 @@
 #include "fkda_common.cuh"
 
 namespace fkda {
-cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int* prefix, int* status, cudaStream_t stream);
+cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int n_segs, int* prefix, int* status,
+                                cudaStream_t stream);
 cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
@@ -64,7 +65,7 @@ struct Layout {
   int64_t total_bytes;
 };
 
-// Runs per sequence for a fixed-length batch under `flags`: forced by FKDA_FLAG_SEGMENTS(n), switched off by the
+// Runs per sequence under `flags`: forced by FKDA_FLAG_SEGMENTS(n), switched off by the
 // kernel-selection flags, else planned from the sizes.
 int segments_for(int64_t chains, int64_t chunks_per_seq, int64_t flags, int* seg_chunks) {
   *seg_chunks = 0;
@@ -98,8 +99,13 @@ bool make_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_pe
   L->seg_off = L->records_off + chunks * H * static_cast<int64_t>(fkda::kRecBytes);
   L->n_segs = 1;
   L->seg_chunks = 0;
-  if (varlen <= 0 && N * H <= 0x7fffffffLL)
-    L->n_segs = segments_for(N * H, (T_per_seq + fkda::kChunk - 1) / fkda::kChunk, flags, &L->seg_chunks);
+  if (N * H <= 0x7fffffffLL) {
+    // Fixed-length: planned from the sequence length.  Varlen: the lengths are on the device, so the number of runs is
+    // planned for sequences of the average length and the run length follows the longest sequence, on the device.
+    // (A size query, varlen < 0, gets the same plan either way: both use T_total / N.)
+    const int64_t per_seq = varlen > 0 ? (T_total / N + fkda::kChunk - 1) / fkda::kChunk : (T_per_seq + fkda::kChunk - 1) / fkda::kChunk;
+    L->n_segs = segments_for(N * H, per_seq, flags, &L->seg_chunks);
+  }
   L->seg_bytes = L->n_segs > 1 ? N * H * L->n_segs * 3 * fkda::kSegSlotFloats * 4 : 0;
   L->total_bytes = L->seg_off + L->seg_bytes;
   return true;
@@ -145,7 +151,7 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   cudaError_t e = cudaMemsetAsync(ws, 0, fkda::kWsHeaderBytes, stream);
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
   if (p->cu_seqlens) {
-    e = fkda::launch_chunk_prefix(p->cu_seqlens, static_cast<int>(p->N), p->B * p->T, static_cast<int>(p->H), prefix, status, stream);
+    e = fkda::launch_chunk_prefix(p->cu_seqlens, static_cast<int>(p->N), p->B * p->T, static_cast<int>(p->H), L.n_segs, prefix, status, stream);
     if (e != cudaSuccess) return cuda_fail(e, "chunk_prefix launch");
   }
   fkda::PrepParams q{};
@@ -193,6 +199,7 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   s.N = static_cast<int>(p->N);
   s.total_chunks = static_cast<int>(L.chunks_per_head);
   s.state_fp32 = p->state_dtype == FKDA_STATE_FP32 ? 1 : 0;
+  if (p->cu_seqlens && L.n_segs > 1) s.seg_chunks_dev = s.status + 2;     // set by the chunk-prefix kernel
   cudaError_t e;
   if (p->flags & FKDA_FLAG_SCAN_SIMT) e = fkda::launch_scan_simt(s, stream);
   else if ((p->flags & (FKDA_FLAG_SCAN_PLAIN | FKDA_FLAG_SCAN_LOOKAHEAD)) && L.n_segs > 1) {

@@ -375,8 +375,8 @@ struct ScanParams {
   int N;
   int total_chunks;
   int state_fp32;              // dtype of both state tensors: 1 = fp32, 0 = bf16
-  // Segment-parallel form (fixed-length batches with few chains): every sequence is cut into n_segs runs of
-  // seg_chunks chunks and each CTA walks one run.  Pass 1 walks run 0 from the caller's state (its outputs are
+  // Segment-parallel form (batches with few chains): every sequence is cut into n_segs runs of
+  // seg_chunks chunks (varlen: of *seg_chunks_dev chunks, runs beyond a sequence's end being empty) and each CTA walks one run.  Pass 1 walks run 0 from the caller's state (its outputs are
   // final) and, for the runs 1 .. n_segs-2, the two halves of the affine map  Z_end = Z_start M + N  that a run
   // applies to the state Z = S^T: N from a zero state, M from the identity with u' taken as zero.  A small kernel
   // chains the maps into the state at the start of every run; pass 2 walks runs 1 .. n_segs-1 from those.
@@ -386,6 +386,7 @@ struct ScanParams {
   float* seg_buf;              // fp32 [(n*H + h)][n_segs][3][128][128]: 0 = M, 1 = N, 2 = state at the start of the run
   const int* select;           // device word, or nullptr: the kernel runs only if *select == select_want
   int select_want;
+  const int* seg_chunks_dev;   // varlen batches: run length decided on the device from the longest sequence (else nullptr)
 };
 
 constexpr int64_t kSegSlotFloats = 128 * 128;
@@ -489,8 +490,9 @@ __device__ __forceinline__ ChainView chain_view(const ScanParams& p, int block) 
   if (p.final_state != nullptr) cv.fin_base = static_cast<uint8_t*>(p.final_state) + chain_state * (p.state_fp32 ? 4 : 2);
   if constexpr (kSeg) {
     float* slots = p.seg_buf + (static_cast<size_t>(cv.n) * p.H + cv.h) * p.n_segs * 3 * kSegSlotFloats;
-    const int c_begin = seg * p.seg_chunks < cv.nchunks ? seg * p.seg_chunks : cv.nchunks;
-    const int c_end = (seg == p.n_segs - 1 || (seg + 1) * p.seg_chunks > cv.nchunks) ? cv.nchunks : (seg + 1) * p.seg_chunks;
+    const int run_len = p.seg_chunks_dev != nullptr ? *p.seg_chunks_dev : p.seg_chunks;
+    const int c_begin = seg * run_len < cv.nchunks ? seg * run_len : cv.nchunks;
+    const int c_end = (seg == p.n_segs - 1 || (seg + 1) * run_len > cv.nchunks) ? cv.nchunks : (seg + 1) * run_len;
     if (seg < p.n_segs - 1) {
       const int64_t run_end = cv.bos + static_cast<int64_t>(c_end) * kChunk;
       cv.eos = run_end < cv.eos ? run_end : cv.eos;

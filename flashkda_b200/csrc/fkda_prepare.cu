@@ -23,7 +23,9 @@ namespace fkda {
 // It also picks the recurrence kernel for batches with more chains than SMs (status[1] = 1: the compact
 // kernel, two CTAs per SM): the compact kernel moves more chunks per SM and second but walks one chain more slowly,
 // so it is chosen unless the longest sequence alone would then set the duration.
-__global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int H, int* __restrict__ prefix,
+// For batches with few chains that are walked in runs (n_segs > 1) it sets the run length, status[2]: the longest
+// sequence's chunks spread over the runs, at least 8 chunks.
+__global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int H, int n_segs, int* __restrict__ prefix,
                                     int* __restrict__ status) {
   __shared__ int warp_sums[32];
   __shared__ int carry;
@@ -81,6 +83,8 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
     const bool alike = static_cast<long long>(longest) * N * 100 <= 130ll * prefix[N];
     const bool throughput = chains >= 2 * kPlanSms && static_cast<long long>(longest) * 195 * kPlanSms * 100 <= total_steps * 125 * 85;
     status[1] = (chains > kPlanSms && (alike || throughput)) ? 1 : 0;
+    const int run_len = n_segs > 1 ? (longest + n_segs - 1) / n_segs : 0;
+    status[2] = run_len < 8 ? 8 : run_len;
   }
   // Chain order for the scan: longest sequences first (longest-processing-time-first packing of unequal chains
   // onto the SMs; the reference walks sequences in the given order).  order[] follows prefix[] in memory.
@@ -638,8 +642,9 @@ store_record:
   }
 }
 
-cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int* prefix, int* status, cudaStream_t stream) {
-  chunk_prefix_kernel<<<1, 256, 0, stream>>>(cu, N, T_total, H, prefix, status);
+cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int n_segs, int* prefix, int* status,
+                                cudaStream_t stream) {
+  chunk_prefix_kernel<<<1, 256, 0, stream>>>(cu, N, T_total, H, n_segs, prefix, status);
   return cudaGetLastError();
 }
 

@@ -209,8 +209,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     }
     if (p.final_state != nullptr) fin_base = static_cast<uint8_t*>(p.final_state) + chain_state * (p.state_fp32 ? 4 : 2);
     float* slots = p.seg_buf + (static_cast<size_t>(n) * p.H + h) * p.n_segs * 3 * kSegSlotFloats;
-    const int c_begin = seg * p.seg_chunks < nchunks ? seg * p.seg_chunks : nchunks;
-    const int c_end = (seg == p.n_segs - 1 || (seg + 1) * p.seg_chunks > nchunks) ? nchunks : (seg + 1) * p.seg_chunks;
+    const int run_len = p.seg_chunks_dev != nullptr ? *p.seg_chunks_dev : p.seg_chunks;
+    const int c_begin = seg * run_len < nchunks ? seg * run_len : nchunks;
+    const int c_end = (seg == p.n_segs - 1 || (seg + 1) * run_len > nchunks) ? nchunks : (seg + 1) * run_len;
     if (seg < p.n_segs - 1) {
       const int64_t run_end = bos + static_cast<int64_t>(c_end) * kChunk;
       eos = run_end < eos ? run_end : eos;

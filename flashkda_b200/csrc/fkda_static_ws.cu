@@ -90,7 +90,7 @@ int fkda_fwd_static_ws(const fkda_fwd_params* p, void* cuda_stream) {
   fkda_fwd_params q = *p;
   q.workspace = ws;
   q.workspace_bytes = kStaticWsBytes;
-  if (p->cu_seqlens == nullptr) {
+  {
     // few long chains would be cut into runs, which needs room beyond the records: where that room is missing the
     // sequences are walked whole instead (slower, same result) rather than refused
     int64_t with_runs = 0;

@@ -43,7 +43,7 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
  * fkda_fwd only. */
 #define FKDA_FLAG_REFERENCE_ROUNDING 0x20u
 #define FKDA_FLAG_SCAN_NO_SEGMENTS 0x8u /* never cut sequences into runs that are walked in parallel */
-/* Cut every sequence of a fixed-length batch into n (2..255) runs walked in parallel, whatever the planner would
+/* Cut every sequence of the batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
  * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster
  * one for its number of CTAs). */
@@ -83,8 +83,9 @@ int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* byte
  * No counterpart in the reference. */
 int fkda_get_workspace_size_flags(int64_t T_total, int64_t H, int64_t N, int64_t flags, int64_t* bytes);
 
-/* The planner of the segment-parallel recurrence: into how many runs (1 = none) a fixed-length batch with `chains`
- * = N*H chains of `chunks_per_sequence` 32-token chunks is cut, and the run length in chunks.  The reference has no
+/* The planner of the segment-parallel recurrence: into how many runs (1 = none) a batch with `chains`
+ * = N*H chains of `chunks_per_sequence` 32-token chunks is cut, and the run length in chunks.  (For a varlen batch the call plans with the average sequence length and
+ * sets the run length on the device from the longest sequence.)  The reference has no
  * counterpart: its recurrence kernel always walks a whole sequence per CTA (csrc/smxx/fwd_kernel2.cuh:434-742). */
 int fkda_plan_segments(int64_t chains, int64_t chunks_per_sequence, int* segments, int* chunks_per_segment);
 

@@ -284,6 +284,37 @@ def test_segment_parallel_scan_planned_many_chains():
     assert max_abs(o1, o0) <= 1e-2 and rel_fro(s1, s0) <= 2e-2
 
 
+@pytest.mark.parametrize("kernel", ["compact", "lookahead"])
+@pytest.mark.parametrize("state", ["fp32", "bf16"])
+def test_segment_parallel_scan_of_variable_length_sequences(kernel, state):
+    """Varlen batches are cut into runs too: the run length is set on the device from the longest sequence, shorter
+    sequences end in empty runs (which pass the state through), an empty sequence has only empty runs."""
+    flag = F.FLAG_SCAN_PLAIN if kernel == "compact" else F.FLAG_SCAN_LOOKAHEAD
+    w = Workload("segvar", H=2, seq_lens=[32 * 13 + 7, 0, 40, 32 * 30, 1], state_in=state, state_out=state, state_std=0.5,
+                 seed=17, lower_bound=-1.0)
+    x = make_inputs(w)
+    dt = torch.bfloat16 if state == "bf16" else torch.float32
+    o_seg, s_seg = run_gpu(x, dt, flag | F.FLAG_SEGMENTS(4))
+    o_ref, s_ref = run_gpu(x, dt, F.FLAG_SCAN_LOOKAHEAD)
+    check_against_f64(x, o_seg, s_seg, f"varlen segments on the {kernel} kernel, {state} state")
+    assert max_abs(o_seg, o_ref) <= 1e-2 and rel_fro(s_seg, s_ref) <= (2e-2 if state == "bf16" else 5e-3)
+
+
+def test_segment_parallel_scan_planned_for_variable_length_sequences():
+    """Two long sequences of unequal length, three heads: the planner cuts them (number of runs from the average
+    length, run length from the longest on the device)."""
+    w = Workload("segvarplan", H=3, seq_lens=[2900, 5100], state_in="fp32", state_out="fp32", state_std=0.5, seed=18)
+    runs, _ = F.plan_segments(6, (8000 // 2 + 31) // 32)
+    assert runs >= 3
+    x = make_inputs(w)
+    assert F.get_workspace_size(8000, 3, 2) - F.get_workspace_size(8000, 3, 2, F.FLAG_SCAN_NO_SEGMENTS) == 6 * runs * 3 * 128 * 128 * 4
+    o1, s1 = run_gpu(x, torch.float32)
+    check_against_f64(x, o1, s1, f"varlen planned runs={runs}")
+    o0, s0 = run_gpu(x, torch.float32, F.FLAG_SCAN_NO_SEGMENTS)
+    assert max_abs(o1, o0) <= 1e-2 and rel_fro(s1, s0) <= 5e-3
+    assert not torch.equal(o1.view(torch.int16), o0.view(torch.int16)), "the two paths round differently: equal outputs mean the runs were not used"
+
+
 def test_segment_parallel_scan_planned():
     """A batch with few long chains takes the segment-parallel path by itself (the planner's choice), within the
     same tolerances; a second call on the same workspace reproduces the first bit for bit."""
