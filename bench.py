@@ -354,12 +354,20 @@ def main():
     # kernels per call: prepare, the recurrence (one launch, or pass 1 + map chaining + pass 2 when sequences are cut
     # into runs), plus the chunk prefix for varlen
     runs = 1
-    if x["cu_seqlens"] is None and not (args.flags & 0xB):
-        forced = (args.flags >> 8) & 0xFF
-        runs = forced if forced >= 2 else (1 if args.flags & 0x4 else F.plan_segments(N * H_local, (T + 31) // 32)[0])
-    if x["cu_seqlens"] is None and 0 < T <= 64 and not (args.flags & 0x4):
+    varlen = x["cu_seqlens"] is not None
+    chains = N * H_local
+    per_seq_chunks = ((B * T) // N + 31) // 32 if varlen else (T + 31) // 32     # varlen: planned for the average length
+    forced = (args.flags >> 8) & 0xFF
+    if not (args.flags & 0x9) and not ((args.flags & 0x2) and forced < 2):
+        runs = forced if forced >= 2 else (1 if args.flags & 0x4 else F.plan_segments(chains, per_seq_chunks)[0])
+    if not varlen and 0 < T <= 64 and not (args.flags & 0x4):
         runs = 1
-    launches_per_call = 1 + (1 if x["cu_seqlens"] is not None else 0) + (1 if runs == 1 else 2 + (1 if runs > 2 else 0))
+    if chains > 148 and not (args.flags & 0x7):
+        runs = 1                      # more chains than SMs: the compact kernel on whole sequences
+    recurrence = 1 if runs == 1 else 2 + (1 if runs > 2 else 0)
+    if varlen and 148 < chains <= 1024 and not (args.flags & 0x7):
+        recurrence = 2                # both recurrence kernels are launched; the one not chosen on the device leaves at once
+    launches_per_call = 1 + (1 if varlen else 0) + recurrence
     if fused:
         launches_per_call = 1
 

@@ -25,6 +25,7 @@ namespace fkda {
 // so it is chosen unless the longest sequence alone would then set the duration.
 // For batches with few chains that are walked in runs (n_segs > 1) it sets the run length, status[2]: the longest
 // sequence's chunks spread over the runs, at least 8 chunks.
+constexpr int kOrderMax = 4096;      // batches of more sequences keep the given order
 __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int H, int n_segs, int* __restrict__ prefix,
                                     int* __restrict__ status) {
   __shared__ int warp_sums[32];
@@ -89,16 +90,32 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
   // Chain order for the scan: longest sequences first (longest-processing-time-first packing of unequal chains
   // onto the SMs; the reference walks sequences in the given order).  order[] follows prefix[] in memory.
   int* order = prefix + (N + 1);
-  if (N <= 4096) {
-    for (int n = threadIdx.x; n < N; n += blockDim.x) {
-      const int len_n = prefix[n + 1] - prefix[n];
-      int rank = 0;
-      for (int m = 0; m < N; ++m) {
-        const int len_m = prefix[m + 1] - prefix[m];
-        rank += (len_m > len_n) || (len_m == len_n && m < n);
+  if (N <= kOrderMax) {
+    // bitonic sort of (chunks descending, index ascending) keys in shared memory
+    __shared__ unsigned long long keys[kOrderMax];
+    __syncthreads();                                   // prefix[] of the last block of sequences is complete
+    int P = 1;
+    while (P < N) P <<= 1;
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+      unsigned long long key = ~0ull;                  // padding sorts last
+      if (i < N) {
+        const unsigned len = static_cast<unsigned>(prefix[i + 1] - prefix[i]);
+        key = (static_cast<unsigned long long>(0xffffffffu - len) << 32) | static_cast<unsigned>(i);
       }
-      order[rank] = n;
+      keys[i] = key;
     }
+    __syncthreads();
+    for (int k = 2; k <= P; k <<= 1)
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        for (int t = threadIdx.x; t < (P >> 1); t += blockDim.x) {     // one compare-exchange per pair
+          const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1)), partner = i | j;
+          const unsigned long long x = keys[i], y = keys[partner];
+          const bool ascending = (i & k) == 0;
+          if ((x > y) == ascending) { keys[i] = y; keys[partner] = x; }
+        }
+        __syncthreads();
+      }
+    for (int i = threadIdx.x; i < N; i += blockDim.x) order[i] = static_cast<int>(keys[i] & 0xffffffffu);
   } else {
     for (int n = threadIdx.x; n < N; n += blockDim.x) order[n] = n;
   }
@@ -644,7 +661,7 @@ store_record:
 
 cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int n_segs, int* prefix, int* status,
                                 cudaStream_t stream) {
-  chunk_prefix_kernel<<<1, 256, 0, stream>>>(cu, N, T_total, H, n_segs, prefix, status);
+  chunk_prefix_kernel<<<1, N > 256 ? 1024 : 256, 0, stream>>>(cu, N, T_total, H, n_segs, prefix, status);
   return cudaGetLastError();
 }
 

@@ -122,3 +122,25 @@ def test_umma_bench_runs_inside_its_operand_arrays():
     four = F.umma_bench(issuers=4, reps=16, ksteps=8, n=32, a_in_tmem=True)
     assert one[1] > 60 and four[1] > 60
     assert F.umma_bench(issuers=2, reps=8, ksteps=2, n=64, a_in_tmem=True)[1] > 0
+
+
+@pytest.mark.parametrize("N", [1, 5, 300, 4096])
+def test_chunk_prefix_and_chain_order(N):
+    """The scheduling kernel of varlen calls: chunk prefix sums and the order in which the recurrence takes the
+    sequences (longest first, ties in the given order), read back from the workspace header."""
+    import flashkda_b200 as F
+    from flashkda_b200.workloads import Workload, make_inputs
+    g = torch.Generator().manual_seed(N)
+    lens = [int(v) for v in torch.randint(0, 200 if N < 1000 else 40, (N,), generator=g)]
+    if N >= 5:
+        lens[3] = 0
+    w = Workload("order", H=1, seq_lens=lens, seed=N)
+    x = make_inputs(w, device="cuda")
+    ws = F.prepare(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["out"], x["A_log"], x["dt_bias"], x["lower_bound"],
+                   cu_seqlens=x["cu_seqlens"])
+    assert F.read_status(ws) == 0
+    head = ws[256:256 + 4 * (2 * N + 1)].view(torch.int32).cpu()
+    chunks = torch.tensor([(v + 31) // 32 for v in lens], dtype=torch.int64)
+    assert torch.equal(head[:N + 1].long(), torch.cat([torch.zeros(1, dtype=torch.int64), chunks.cumsum(0)]))
+    want = sorted(range(N), key=lambda i: (-int(chunks[i]), i))
+    assert head[N + 1:].tolist() == want
