@@ -404,8 +404,8 @@ inline int64_t pass_cost_x100(int64_t ctas, bool* compact, int64_t la_step_x100 
   return co < la ? co : la;
 }
 
-// How many runs to cut each sequence of a fixed-length batch into (1 = walk whole sequences), and their length in
-// chunks.  Pass 1 holds chains * (2 n - 3) CTAs and pass 2 chains * (n - 1), both walking ceil(chunks / n) chunks, each
+// How many runs to cut each sequence of a batch into (1 = walk whole sequences), and their length in chunks (varlen
+// batches: called with the average sequence length; the run length is then set on the device from the longest one).  Pass 1 holds chains * (2 n - 3) CTAs and pass 2 chains * (n - 1), both walking ceil(chunks / n) chunks, each
 // on whichever recurrence kernel gets that many CTAs through faster; chaining the maps costs about three chunk steps
 // per run.  The plan is a pure function of the sizes so that the workspace size and the launch agree; it assumes the
 // 148 SMs of a B200.
