@@ -65,6 +65,15 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
   const int nchunks = cv.nchunks;
   const uint8_t* rec0 = p.records + (static_cast<size_t>(h) * p.total_chunks + cv.chunk_base) * kRecBytes;
 
+  // The incoming state is read row by row in four dependent round trips further down: ask for its lines now, so that
+  // those reads find them in the L2 (state warps: lane = row, 512 B or 256 B per row).
+  if (warp >= 2 && warp < 6 && (cv.init_mode == 1 || cv.init_mode == 2)) {
+    const int v = (warp & 3) * 32 + lane;
+    const uint8_t* row = static_cast<const uint8_t*>(cv.init_base) + static_cast<size_t>(v) * kD * (cv.init_mode == 1 ? 4 : 2);
+    const int lines = cv.init_mode == 1 ? 4 : 2;
+    for (int i = 0; i < lines; ++i) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + 128 * i));
+  }
+
   // ---- setup -----------------------------------------------------------------------------------------------
   if (tid == 0) {
     *abort_flag = 0;
