@@ -118,6 +118,19 @@ def test_short_chains_all_scan_kernels(B, T, state, kernel):
     check_against_f64(x, out, fin, f"short-B{B}xT{T}-{state}-{kernel}")
 
 
+@pytest.mark.parametrize("T,state", [(65, "fp32"), (96, "bf16"), (129, "fp32"), (160, None)])
+def test_many_chains_of_up_to_five_chunks(T, state):
+    """More chains than SMs and at most five chunks each: the persistent short-chain kernel takes these too; same
+    answers as the look-ahead kernel and the fp64 recurrence."""
+    w = Workload("s5", H=4, B=40, T=T, state_in=state, state_out=state or "fp32", state_std=0.5, seed=T, lower_bound=-1.0)
+    x = make_inputs(w)
+    dt = torch.bfloat16 if state == "bf16" else torch.float32
+    o1, s1 = run_gpu(x, dt)
+    check_against_f64(x, o1, s1, f"160 chains of T={T}, {state} state")
+    o0, s0 = run_gpu(x, dt, F.FLAG_SCAN_LOOKAHEAD)
+    assert max_abs(o1, o0) <= 1e-2 and rel_fro(s1, s0) <= (2e-2 if state == "bf16" else 5e-3)
+
+
 @pytest.mark.parametrize("B,T", [(2, 64), (2, 1024), (4, 256), (8, 128), (64, 16)])
 def test_batched(B, T):
     w = Workload("b", H=4, B=B, T=T, state_in="fp32", state_out="fp32", seed=B)
