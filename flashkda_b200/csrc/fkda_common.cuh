@@ -415,7 +415,7 @@ inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
   bool c;
   const int64_t whole = pass_cost_x100(chains, &c) * chunks;
   int64_t best = whole, best_n = 1;
-  for (int64_t n = 3; n <= 64; ++n) {
+  for (int64_t n = 3; n <= 160; ++n) {
     const int64_t len = (chunks + n - 1) / n;
     if (len < 8) break;
     if ((n - 1) * len >= chunks) continue;       // the last run would be empty
