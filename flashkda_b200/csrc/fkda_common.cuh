@@ -389,7 +389,9 @@ struct ScanParams {
   const int* seg_chunks_dev;   // varlen batches: run length decided on the device from the longest sequence (else nullptr)
 };
 
-constexpr int64_t kSegSlotFloats = 128 * 128;
+constexpr int kSegMapStride = 136;             // floats per row of a transition map M in its slot: the map chaining reads
+                                               // whole slots into shared memory, where this stride keeps its fragment loads conflict-free
+constexpr int64_t kSegSlotFloats = 128 * kSegMapStride;   // every slot has room for the padded form
 constexpr int64_t kPlanSms = 148;      // SMs of a B200: what the kernel-selection rules assume
 
 // Fixed-length sequences of at most this many tokens take the fused short-sequence kernel (fkda_short16.cu).
@@ -420,10 +422,10 @@ inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
     if (len < 8) break;
     if ((n - 1) * len >= chunks) continue;       // the last run would be empty
     // (a run walks its chunks about a tenth more slowly than a whole sequence; each pass costs about ten chunk steps of
-    // launch, set-up and state traffic; a step of the map chaining about four, per wave of its CTAs)
-    const int64_t cmb_ctas = chains * 16 <= kPlanSms ? chains * 16 : (chains * 8 <= kPlanSms ? chains * 8 : chains * 4);
+    // launch, set-up and state traffic; a step of the map chaining about two and a half, per wave of its chains x 8 CTAs)
+    const int64_t cmb_waves = (chains * 8 + kPlanSms - 1) / kPlanSms;
     const int64_t cost = (pass_cost_x100(chains * (2 * n - 3), &c, 110) + pass_cost_x100(chains * (n - 1), &c, 110)) * len + 100 * 20 +
-                         100 * 4 * (n - 2) * ((cmb_ctas + kPlanSms - 1) / kPlanSms);
+                         250 * (n - 2) * cmb_waves;
     if (cost < best) { best = cost; best_n = n; }
   }
   if (best_n == 1 || best * 4 > whole * 3) return 1;
@@ -443,6 +445,7 @@ struct ChainView {
   int init_mode;               // 0 = zero, 1 = fp32, 2 = bf16, 3 = identity
   void* fin_base;              // where the state goes afterwards, or nullptr
   int fin_fp32;
+  int fin_stride;              // elements per row there (128; a transition map's slot: kSegMapStride)
   bool write_out, zero_up;
 };
 template <bool kSeg>
@@ -483,6 +486,7 @@ __device__ __forceinline__ ChainView chain_view(const ScanParams& p, int block) 
   cv.init_mode = 0;
   cv.fin_base = nullptr;
   cv.fin_fp32 = p.state_fp32;
+  cv.fin_stride = kD;
   if (p.initial_state != nullptr) {
     cv.init_mode = p.state_fp32 ? 1 : 2;
     cv.init_base = static_cast<const uint8_t*>(p.initial_state) + chain_state * (p.state_fp32 ? 4 : 2);
@@ -507,6 +511,7 @@ __device__ __forceinline__ ChainView chain_view(const ScanParams& p, int block) 
         cv.init_mode = variant == 2 ? 3 : 0;
         cv.init_base = nullptr;
         cv.fin_base = slots + (seg * 3 + (variant == 2 ? 0 : 1)) * kSegSlotFloats;
+        if (variant == 2) cv.fin_stride = kSegMapStride;
       }
       cv.fin_fp32 = 1;
     } else {

@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
           tmem_ld32(tq + kColS + cb * 32, x);
           tmem_wait_ld();
           if (cv.fin_fp32) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(cv.fin_base) + row_off + cb * 32);
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(cv.fin_base) + static_cast<size_t>(v) * cv.fin_stride + cb * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]), __uint_as_float(x[4 * i + 2]),

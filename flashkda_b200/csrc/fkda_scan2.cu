@@ -550,7 +550,8 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
           tmem_ld32(tq + kColS + cb * 32, x);
           tmem_wait_ld();
           if (fin_fp32) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(fin_base) + row_off + cb * 32);
+            // (a transition map goes into its slot with padded rows: the map chaining reads it in one piece)
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(fin_base) + (zero_up ? static_cast<size_t>(v) * kSegMapStride : row_off) + cb * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]), __uint_as_float(x[4 * i + 2]),

@@ -97,7 +97,7 @@ def test_c_abi_rejects_bad_params_without_a_gpu():
 
 def test_segment_planner_is_consistent_with_the_workspace_size():
     """Few long chains are cut into runs; many chains or short sequences are not.  The last run is never empty and
-    the workspace grows by three fp32 128x128 slots per (chain, run)."""
+    the workspace grows by three fp32 slots of 128 x 136 floats per (chain, run)."""
     import flashkda_b200 as F
     assert F.plan_segments(128, 256) == (1, 0)          # one chain per SM already
     assert F.plan_segments(8, 16) == (1, 0)             # too short to be worth it
@@ -106,10 +106,10 @@ def test_segment_planner_is_consistent_with_the_workspace_size():
         assert runs >= 3 and per * runs >= chunks and (runs - 1) * per < chunks, (chains, chunks, runs, per)
         H, N, T = chains, 1, chunks * 32
         grown = F.get_workspace_size(T, H, N) - F.get_workspace_size(T, H, N, F.FLAG_SCAN_NO_SEGMENTS)
-        assert grown == chains * runs * 3 * 128 * 128 * 4
+        assert grown == chains * runs * 3 * 128 * 136 * 4
     # a forced run count sizes the workspace the same way
     assert (F.get_workspace_size(32 * 20, 2, 1, F.FLAG_SEGMENTS(4)) - F.get_workspace_size(32 * 20, 2, 1, F.FLAG_SCAN_NO_SEGMENTS)
-            == 2 * 4 * 3 * 128 * 128 * 4)
+            == 2 * 4 * 3 * 128 * 136 * 4)
 
 
 def test_flag_constants_match_the_header():
