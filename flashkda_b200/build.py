@@ -18,6 +18,8 @@ SOURCES = ["fkda_api.cu", "fkda_prepare.cu", "fkda_scan.cu", "fkda_scan2.cu", "f
 HEADERS = [os.path.join(CSRC, "fkda_common.cuh"), os.path.join(os.path.dirname(HERE), "include", "fkda.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+# extra compiler flags, e.g. FKDA_NVCC_EXTRA="-DFKDA_TUNING" for a build with the phase-skip timing aid of the prepare kernel
+NVCC_FLAGS += os.environ.get("FKDA_NVCC_EXTRA", "").split()
 
 
 def _nvcc():

@@ -174,7 +174,7 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   q.scale = p->scale;
   q.gate_scale = static_cast<float>(static_cast<double>(p->lower_bound) * 1.4426950408889634);
   {
-    static const char* dbg_env = getenv("FKDA_PREPARE_SKIP");   // tuning aid, unset in production
+    static const char* dbg_env = getenv("FKDA_PREPARE_SKIP");   // tuning aid: read by the kernel only in -DFKDA_TUNING builds
     q.dbg = dbg_env ? atoi(dbg_env) : 0;
   }
   e = fkda::launch_prepare(q, stream);
