@@ -142,3 +142,16 @@ def test_new_entry_points_reject_bad_arguments_without_a_gpu():
     assert F.get_workspace_size(32 * 4096, 8, 1, F.FLAG_SCAN_PLAIN) == base
     assert F.get_workspace_size(32 * 4096, 8, 1, F.FLAG_SCAN_LOOKAHEAD) == base
     assert F.get_workspace_size(32 * 4096, 8, 1) > base
+
+
+def test_segment_planner_invariants_over_a_grid_of_sizes():
+    """Whatever the planner decides, the runs tile the sequence: none is empty, none shorter than eight chunks, at most
+    160 of them (the flag field holds 255); batches of fifty chains or more and sequences below 48 chunks are left whole."""
+    for chains in list(range(1, 50)) + [50, 64, 148, 149, 1000]:
+        for chunks in (1, 47, 48, 49, 100, 129, 256, 1000, 4096, 4097, 32768, 40000):
+            runs, per = F.plan_segments(chains, chunks)
+            if chains >= 50 or chunks < 48:
+                assert (runs, per) == (1, 0), (chains, chunks, runs, per)
+                continue
+            assert runs == 1 and per == 0 or (3 <= runs <= 160 and per >= 8 and runs * per >= chunks and (runs - 1) * per < chunks), \
+                (chains, chunks, runs, per)
