@@ -4,9 +4,10 @@
 // (csrc/smxx/fwd_kernel2.cuh:434-742), so a call with fewer chains than SMs leaves most of the GPU idle.  A run
 // of chunks acts on the state Z = S^T ([v][k]) as an affine map, Z_end = Z_start M + N, because every chunk does
 //     Z' = Z (diag(e) - w'^T kr) + u'^T kr .
-// Here each sequence is cut into runs; the look-ahead scan kernel itself produces M (walk from the identity with
-// u' = 0) and N (walk from zero) of the inner runs in parallel, this file chains them into the state at the start
-// of every run, and a second launch of the scan kernel walks all runs in parallel from those states.
+// Here each sequence is cut into runs; a recurrence kernel itself (the look-ahead or the compact one, whichever gets
+// the pass's CTAs through faster) produces M (walk from the identity with u' = 0) and N (walk from zero) of the inner
+// runs in parallel, this file chains them into the state at the start of every run, and a second launch of a
+// recurrence kernel walks all runs in parallel from those states.
 #include "fkda_common.cuh"
 
 namespace fkda {
@@ -20,16 +21,16 @@ constexpr int kCmbRows = 16;                              // state rows per CTA:
 constexpr int kMapStride = kSegMapStride;                 // floats per map row, in its slot and here (B fragments: bank 8 t + g)
 constexpr int kMapStg = kD * kMapStride * 4;
 constexpr int kZStride = 132;                             // floats per staged state row (A fragments: bank 4 g + t)
-constexpr int kMapBufs = 3;                                // maps in flight
+constexpr int kMapBufs = 3;                               // maps in flight
 constexpr int kCmbM = 0;                                  // kMapBufs x [128][136] fp32: transition maps
-constexpr int kCmbZ = kCmbM + kMapBufs * kMapStg;                // [16][132] fp32: this CTA's rows of the state
+constexpr int kCmbZ = kCmbM + kMapBufs * kMapStg;         // [16][132] fp32: this CTA's rows of the state
 constexpr int kCmbBars = kCmbZ + kCmbRows * kZStride * 4;
 constexpr int kCmbSmemBytes = kCmbBars + 64 + 128;
 static_assert(kCmbSmemBytes <= 227 * 1024, "map buffers fit one SM");
 
 // Z_start[run + 1] = Z_start[run] M[run] + N[run] for run = 1 .. n_segs-2; rows of Z are independent, so each CTA
 // carries sixteen of them through all runs.  The maps arrive by bulk copies (one per map: its slot holds it with padded
-// rows) two runs ahead, so the serial chain of runs sees shared-memory latency only.  The products run on the tensor cores in
+// rows) three runs ahead, so the serial chain of runs sees shared-memory latency only.  The products run on the tensor cores in
 // tf32 with both operands split into a leading and a trailing part (three mma per tile: the error of the split, about
 // 2^-21 relative, is that of an fp32 product), fp32 accumulation on top of N.
 __global__ void __launch_bounds__(256) seg_combine_kernel(float* seg_buf, int n_segs, int* status) {
