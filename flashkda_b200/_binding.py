@@ -20,6 +20,7 @@ FLAG_SCAN_LOOKAHEAD = 0x4
 FLAG_SCAN_NO_SEGMENTS = 0x8
 FLAG_NO_FUSED_SHORT = 0x10
 FLAG_REFERENCE_ROUNDING = 0x20
+FLAG_FUSED_ANY_T = 0x40
 
 
 def FLAG_SEGMENTS(n: int) -> int:
@@ -67,9 +68,12 @@ def lib():
         L.fkda_read_status.argtypes = [vp, vp, ctypes.POINTER(ci)]
         L.fkda_selftest_umma.argtypes = [vp, vp, vp, ci, ci, vp, vp]
         L.fkda_debug_tmem_layout_probe.argtypes = [vp, vp]
-        L.fkda_debug_umma_bench.argtypes = [ci, ci, ci, ci, ci, vp, vp, vp]
-        L.fkda_debug_umma_bench.restype = ci
         L.fkda_debug_tmem_layout_probe.restype = ci
+        L.fkda_debug_scan_giveup.argtypes = [ctypes.POINTER(FwdParams), ci, ci, vp]
+        L.fkda_debug_scan_giveup.restype = ci
+        if hasattr(L, "fkda_debug_umma_bench"):        # builds made with -DFKDA_TUNING only
+            L.fkda_debug_umma_bench.argtypes = [ci, ci, ci, ci, ci, vp, vp, vp]
+            L.fkda_debug_umma_bench.restype = ci
         L.fkda_last_error.restype = ctypes.c_char_p
         L.fkda_version.restype = ctypes.c_char_p
         for name in ("fkda_get_workspace_size", "fkda_get_workspace_size_flags", "fkda_plan_segments", "fkda_fwd", "fkda_prepare", "fkda_scan", "fkda_prologue",
@@ -120,11 +124,18 @@ def _require(cond, msg):
         raise RuntimeError(msg)
 
 
-def _validate(q, k, v, g, beta, out, A_log, dt_bias, initial_state, final_state, cu_seqlens):
+def _validate(q, k, v, g, beta, out, A_log, dt_bias, initial_state, final_state, cu_seqlens, workspace=None):
     """The reference's checks, in the reference's order and wording (csrc/flash_kda.cpp:44-174),
     plus a same-device check the reference lacks."""
     main = (q, k, v, g, beta, out)
     _require(all(isinstance(t, torch.Tensor) for t in main + (A_log, dt_bias)), "all inputs must be tensors")
+    if workspace is not None:
+        # what the reference requires of its workspace argument (csrc/flash_kda.cpp:44-47), checked before its pointer
+        # and size reach the kernels
+        _require(isinstance(workspace, torch.Tensor) and workspace.is_cuda and workspace.is_contiguous(),
+                 "workspace must be a contiguous CUDA tensor")
+        _require(workspace.dtype == torch.uint8, "workspace must be uint8")
+        _require(workspace.device == q.device, "workspace must be on the same CUDA device as q")
     _require(all(t.is_cuda for t in main), "all tensors must be on CUDA")
     _require(all(t.is_contiguous() for t in main), "all tensors must be contiguous")
     for name, t in zip(("q", "k", "v", "g", "beta", "out"), main):
@@ -181,7 +192,7 @@ def _ptr(t):
 def _params(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state, final_state,
             cu_seqlens, workspace, flags):
     B, T, H, N, state_dtype = _validate(q, k, v, g, beta, out, A_log, dt_bias, initial_state, final_state,
-                                        cu_seqlens)
+                                        cu_seqlens, workspace)
     if workspace is None:
         workspace = torch.empty(get_workspace_size(B * T, H, N, flags), dtype=torch.uint8, device=q.device)
     p = FwdParams(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(out), _ptr(A_log), _ptr(dt_bias),
@@ -282,8 +293,18 @@ def tmem_layout_probe(device="cuda"):
     return out.cpu()
 
 
+def scan_giveup(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None, final_state=None,
+                cu_seqlens=None, *, workspace, stop_copies_after=1, wait_limit_us=3000):
+    """Test aid: prepare, then the look-ahead recurrence with a copy producer that stops after `stop_copies_after`
+    records and waits that give up after `wait_limit_us` microseconds (include/fkda_testing.h)."""
+    p, ws = _params(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state, final_state,
+                    cu_seqlens, workspace, 0)
+    with torch.cuda.device(q.device):
+        _check(lib().fkda_debug_scan_giveup(ctypes.byref(p), int(stop_copies_after), int(wait_limit_us), _stream(q)))
+
+
 def umma_bench(issuers=1, reps=64, ksteps=8, n=64, a_in_tmem=True, device="cuda"):
-    """Cycles per tcgen05.mma (M = 128, K = 16, N = n) when `issuers` threads of one CTA each issue `reps` chains of
+    """(Builds made with -DFKDA_TUNING only.)  Cycles per tcgen05.mma (M = 128, K = 16, N = n) when `issuers` threads of one CTA each issue `reps` chains of
     `ksteps` accumulating instructions: returns (issue, complete) cycles per instruction for the slowest issuer."""
     out = torch.zeros(8, dtype=torch.int64, device=device)
     status = torch.zeros(1, dtype=torch.int32, device=device)

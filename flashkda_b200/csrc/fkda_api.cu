@@ -7,6 +7,7 @@
 #include <cstdlib>
 
 #include "../../include/fkda.h"
+#include "../../include/fkda_testing.h"
 #include "fkda_common.cuh"
 
 namespace fkda {
@@ -27,10 +28,12 @@ cudaError_t launch_refmode(const __nv_bfloat16* q, const __nv_bfloat16* k, const
                            int H, int state_fp32, float scale, float gate_scale, cudaStream_t stream);
 cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, int kernel_choice,
                                   cudaStream_t stream);
+#ifdef FKDA_TUNING
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
-cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream);
 cudaError_t launch_umma_bench(int nissuers, int reps, int ksteps, int n, int ts, long long* out, int* status, cudaStream_t stream);
+#endif
+cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream);
 cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* g, const __nv_bfloat16* beta,
                             const float* A_log, const float* dt_bias, float gate_scale, int64_t rows, int H, __nv_bfloat16* qn,
                             __nv_bfloat16* kn, float* gact, float* beta_act, cudaStream_t stream);
@@ -78,7 +81,7 @@ int segments_for(int64_t chains, int64_t chunks_per_seq, int64_t flags, int* seg
     return static_cast<int>(forced);
   }
   if (flags & FKDA_FLAG_SCAN_LOOKAHEAD) return 1;
-  return fkda::plan_segments(chains, chunks_per_seq, seg_chunks);
+  return fkda::plan_segments(chains, chunks_per_seq, seg_chunks, fkda::device_sm_count());
 }
 
 // `varlen` < 0: size for whichever mode needs more (the upper bound T_total/32 + N covers both).
@@ -173,16 +176,18 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   q.total_chunks = static_cast<int>(L.chunks_per_head);
   q.scale = p->scale;
   q.gate_scale = static_cast<float>(static_cast<double>(p->lower_bound) * 1.4426950408889634);
+#ifdef FKDA_TUNING
   {
-    static const char* dbg_env = getenv("FKDA_PREPARE_SKIP");   // tuning aid: read by the kernel only in -DFKDA_TUNING builds
+    static const char* dbg_env = getenv("FKDA_PREPARE_SKIP");   // phase-skip timing of the prepare kernel (results are wrong when set)
     q.dbg = dbg_env ? atoi(dbg_env) : 0;
   }
+#endif
   e = fkda::launch_prepare(q, stream);
   if (e != cudaSuccess) return cuda_fail(e, "prepare launch");
   return FKDA_OK;
 }
 
-int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
+fkda::ScanParams scan_params(const fkda_fwd_params* p, const Layout& L) {
   uint8_t* ws = static_cast<uint8_t*>(p->workspace);
   fkda::ScanParams s{};
   s.records = ws + L.records_off;
@@ -200,6 +205,13 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   s.total_chunks = static_cast<int>(L.chunks_per_head);
   s.state_fp32 = p->state_dtype == FKDA_STATE_FP32 ? 1 : 0;
   if (p->cu_seqlens && L.n_segs > 1) s.seg_chunks_dev = s.status + 2;     // set by the chunk-prefix kernel
+  return s;
+}
+
+int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
+  uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+  fkda::ScanParams s = scan_params(p, L);
+  const int sms = fkda::device_sm_count();
   cudaError_t e;
   if (p->flags & FKDA_FLAG_SCAN_SIMT) e = fkda::launch_scan_simt(s, stream);
   else if ((p->flags & (FKDA_FLAG_SCAN_PLAIN | FKDA_FLAG_SCAN_LOOKAHEAD)) && L.n_segs > 1) {
@@ -208,15 +220,12 @@ int do_scan(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
                                     (p->flags & FKDA_FLAG_SCAN_PLAIN) ? 1 : 2, stream);
   } else if (p->flags & FKDA_FLAG_SCAN_PLAIN) e = fkda::launch_scan(s, stream);
   else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->cu_seqlens == nullptr && p->T > 0 &&
-             (p->T <= 2 * fkda::kChunk || (p->T <= 5 * fkda::kChunk && p->N * p->H > fkda::kPlanSms))) {
+             (p->T <= 2 * fkda::kChunk || (p->T <= 5 * fkda::kChunk && p->N * p->H > sms))) {
     // short chains: the state-I/O-oriented persistent kernel (up to two chunks always; up to five when there are more
     // chains than SMs, where it still beats the compact kernel: 0.122 against 0.150 ms at 2048 chains of three chunks,
     // 0.190 against 0.194 at six)
-    int dev = 0, sms = 0;
-    e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e == cudaSuccess) e = fkda::launch_scan_short(s, sms, stream);
-  } else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->N * p->H > fkda::kPlanSms) {
+    e = fkda::launch_scan_short(s, sms, stream);
+  } else if (!(p->flags & FKDA_FLAG_SCAN_LOOKAHEAD) && p->N * p->H > sms) {
     // More chains than SMs: the compact kernel, two CTAs per SM.  Equal-length chains: always.  Varlen: the
     // chunk-prefix kernel has decided on the device (status word 1); both kernels are launched and the CTAs of the
     // one that was not chosen leave at once.
@@ -257,7 +266,7 @@ int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* byte
 
 int fkda_plan_segments(int64_t chains, int64_t chunks_per_sequence, int* segments, int* chunks_per_segment) {
   if (!segments || !chunks_per_segment) return fail(FKDA_ERR_INVALID_ARGUMENT, "NULL pointer");
-  *segments = fkda::plan_segments(chains, chunks_per_sequence, chunks_per_segment);
+  *segments = fkda::plan_segments(chains, chunks_per_sequence, chunks_per_segment, fkda::device_sm_count());
   return FKDA_OK;
 }
 
@@ -268,6 +277,14 @@ int fkda_workspace_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int
   if (records_offset) *records_offset = L.records_off;
   if (record_bytes) *record_bytes = fkda::kRecBytes;
   if (chunks_per_head) *chunks_per_head = L.chunks_per_head;
+  return FKDA_OK;
+}
+
+int fkda_workspace_bytes_exact(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq, int64_t flags, int64_t* bytes) {
+  Layout L;
+  if (!bytes) return fail(FKDA_ERR_INVALID_ARGUMENT, "bytes is NULL");
+  if (!make_layout(T_total, H, N, varlen ? 1 : 0, T_per_seq, flags, &L)) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad sizes");
+  *bytes = L.total_bytes;
   return FKDA_OK;
 }
 
@@ -303,9 +320,8 @@ int fkda_fwd(const fkda_fwd_params* p, void* cuda_stream) {
     if (e != cudaSuccess) return cuda_fail(e, "reference-rounding kernel launch");
     return FKDA_OK;
   }
-  static const char* fused_env = getenv("FKDA_FUSED_MAX_T");     // tuning aid, unset in production
-  const int64_t fused_max_t = fused_env ? atoll(fused_env) : fkda::kFusedMaxT;
-  if (p->cu_seqlens == nullptr && p->T > 0 && p->T <= fused_max_t && (p->flags & 0xff1fu) == 0) {
+  const bool fused_any_t = (p->flags & 0xff57u) == FKDA_FLAG_FUSED_ANY_T;
+  if (p->cu_seqlens == nullptr && p->T > 0 && (fused_any_t || (p->T <= fkda::kFusedMaxT && (p->flags & 0xff57u) == 0))) {
     // short fixed-length sequences (a continuation step): one fused kernel, no operand records
     cudaError_t e = cudaMemsetAsync(p->workspace, 0, fkda::kWsHeaderBytes, stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
@@ -359,6 +375,25 @@ int fkda_selftest_umma(const void* A, const void* B, float* D, int mode, int rep
   return FKDA_OK;
 }
 
+int fkda_debug_scan_giveup(const fkda_fwd_params* p, int stop_copies_after, int wait_limit_us, void* cuda_stream) {
+  Layout L;
+  int rc = validate(p, &L);
+  if (rc != FKDA_OK) return rc;
+  if (stop_copies_after < 1 || wait_limit_us < 1 || wait_limit_us > 1000000)
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "stop_copies_after >= 1 and 1 <= wait_limit_us <= 1000000 required");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  rc = do_prepare(p, L, stream);
+  if (rc != FKDA_OK) return rc;
+  fkda::ScanParams s = scan_params(p, L);
+  s.seg_chunks_dev = nullptr;          // whole sequences on the look-ahead kernel
+  s.wait_limit_us = wait_limit_us;
+  s.stop_copies_after = stop_copies_after;
+  cudaError_t e = fkda::launch_scan2(s, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "scan launch");
+  return FKDA_OK;
+}
+
+#ifdef FKDA_TUNING
 int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream) {
   if (nwarps < 1 || nwarps > 16 || reps < 1 || !out) return fail(FKDA_ERR_INVALID_ARGUMENT, "bad arguments");
   cudaError_t e = fkda::launch_tmem_bench(nwarps, reps, static_cast<long long*>(out), static_cast<cudaStream_t>(cuda_stream));
@@ -375,6 +410,8 @@ int fkda_debug_umma_bench(int issuers, int reps, int ksteps, int n, int a_in_tme
   return FKDA_OK;
 }
 
+#endif  // FKDA_TUNING
+
 int fkda_debug_tmem_layout_probe(void* out, void* cuda_stream) {
   if (!out) return fail(FKDA_ERR_INVALID_ARGUMENT, "out is NULL");
   cudaError_t e = fkda::launch_tmem_layout_probe(static_cast<uint32_t*>(out), static_cast<cudaStream_t>(cuda_stream));
@@ -382,10 +419,12 @@ int fkda_debug_tmem_layout_probe(void* out, void* cuda_stream) {
   return FKDA_OK;
 }
 
+#ifdef FKDA_TUNING
 int fkda_debug_set_scan_trace(void* device_buffer) {
   fkda::set_scan_trace(static_cast<unsigned long long*>(device_buffer));
   return FKDA_OK;
 }
+#endif
 
 const char* fkda_last_error(void) { return g_err; }
 

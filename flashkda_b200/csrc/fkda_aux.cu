@@ -73,7 +73,8 @@ cudaError_t launch_prologue(const __nv_bfloat16* q, const __nv_bfloat16* k, cons
                             __nv_bfloat16* kn, float* gact, float* beta_act, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   int64_t blocks = (rows / 2 + 7) / 8 + 1;    // 8 warps per block, 2 rows per warp pass
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
   prologue_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(q, k, g, beta, A_log, dt_bias, gate_scale, rows, H, qn, kn,
                                                                      gact, beta_act);
   return cudaGetLastError();
@@ -165,7 +166,8 @@ __global__ void __launch_bounds__(256) scan_simt_kernel(const ScanParams p) {
 }
 
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(scan_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSimtSmemBytes);
+  static SmemOptIn opt_in;
+  cudaError_t e = opt_in.ensure(scan_simt_kernel, kSimtSmemBytes);
   if (e != cudaSuccess) return e;
   const int64_t chains = static_cast<int64_t>(p.N) * p.H;
   if (chains == 0) return cudaSuccess;
@@ -269,6 +271,7 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
   }
 }
 
+#ifdef FKDA_TUNING
 // Micro-benchmark of tensor-memory access (tuning aid): `nwarps` warps each move `reps` x 32 columns between
 // registers and their TMEM lane quadrant; out[warp*4 + {0,1,2,3}] = cycles for {ld, st, st16-packed, ld+st} loops.
 __global__ void __launch_bounds__(512) tmem_bench_kernel(int reps, long long* out) {
@@ -326,6 +329,8 @@ __global__ void __launch_bounds__(512) tmem_bench_kernel(int reps, long long* ou
     tmem_dealloc(tmem_slot, 512);
   }
 }
+
+#endif  // FKDA_TUNING
 
 // Records the register <-> (lane, column) maps of the 16-lane tensor-memory fragment shapes that the scan kernel's
 // state warps use.  One warp.  out[0][t][r], out[1][t][r]: what tcgen05.ld.16x256b.x8 returns for lanes 0-15 and
@@ -389,6 +394,7 @@ cudaError_t launch_tmem_layout_probe(uint32_t* out, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+#ifdef FKDA_TUNING
 // Micro-benchmark of tcgen05.mma issue and completion (tuning aid): `nissuers` (1..4) threads in different warps each
 // issue `reps` products of `ksteps` M=128 instructions (K = 16 each) with N = `n` into their own 128 TMEM columns,
 // A from shared memory (ts = 0) or tensor memory (ts = 1), then commit and wait.  out[issuer*2 + {0,1}] = cycles until
@@ -468,6 +474,8 @@ cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t
   tmem_bench_kernel<<<1, nwarps * 32, 0, stream>>>(reps, out);
   return cudaGetLastError();
 }
+
+#endif  // FKDA_TUNING
 
 cudaError_t launch_umma_selftest(const __nv_bfloat16* A, const __nv_bfloat16* B, float* D, int mode, int reps, int* status,
                                  cudaStream_t stream) {

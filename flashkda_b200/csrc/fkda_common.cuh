@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace fkda {
 
 constexpr int kD = 128;            // head dimension (K = V = 128, as in csrc/flash_kda.cpp:110 of the reference)
@@ -112,8 +114,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Gives up after `kWaitLimitNs` or as soon as another thread of the CTA has given
-// up (`*abort_flag != 0`); the caller then leaves its loop, so a lost arrival can never hang
-// the GPU.  Returns true when the barrier phase completed.
+// up (`*abort_flag > 0`); the caller then leaves its loop, so a lost arrival can never hang
+// the GPU.  Returns true when the barrier phase completed.  A kernel may initialise the flag word to -L instead of 0:
+// nobody has given up, and the limit is L microseconds instead (how a test makes a wait run out quickly).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // `backoff_ns` > 0 makes a waiter that is not on the critical path sleep between probes, so that it does not take
 // issue slots from the warps that are.
@@ -124,8 +127,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   while (!mbar_try_wait(bar, parity)) {
     if (backoff_ns) __nanosleep(backoff_ns);
     if (((++spins) & 63u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const int f = *abort_flag;
+      if (f > 0) return false;
+      const uint64_t limit = f < 0 ? static_cast<uint64_t>(-f) * 1000ull : kWaitLimitNs;
+      if (globaltimer_ns() - t0 > limit) {
         *abort_flag = 1;
         return false;
       }
@@ -387,12 +392,52 @@ struct ScanParams {
   const int* select;           // device word, or nullptr: the kernel runs only if *select == select_want
   int select_want;
   const int* seg_chunks_dev;   // varlen batches: run length decided on the device from the longest sequence (else nullptr)
+  // Test aids of the look-ahead kernel's give-up path (both 0 in production): a wait limit in microseconds instead of
+  // the default, and a number of records after which the copy producer stops issuing copies, so that the consumers'
+  // next wait runs out with nothing in flight.
+  int wait_limit_us;
+  int stop_copies_after;
 };
 
 constexpr int kSegMapStride = 136;             // floats per row of a transition map M in its slot: the map chaining reads
                                                // whole slots into shared memory, where this stride keeps its fragment loads conflict-free
 constexpr int64_t kSegSlotFloats = 128 * kSegMapStride;   // every slot has room for the padded form
-constexpr int64_t kPlanSms = 148;      // SMs of a B200: what the kernel-selection rules assume
+constexpr int kDefaultSms = 148;       // SMs of a B200: assumed where no device can be asked
+
+// SM count of the current device, asked once per device and cached; the kernel-selection rules, the planner of the
+// segment-parallel form and the workspace size all use this one figure, so that a size query and the launch agree.
+inline int device_sm_count() {
+  static std::atomic<int> cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return kDefaultSms;
+  }
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    return kDefaultSms;
+  }
+  cached[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+// Opt-in of a kernel to its dynamic shared-memory size, made once per device instead of before every launch.
+struct SmemOptIn {
+  std::atomic<unsigned long long> done{0};
+  template <class Kernel>
+  cudaError_t ensure(Kernel kernel, int bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return e;
+  }
+};
 
 // Fixed-length sequences of at most this many tokens take the fused short-sequence kernel (fkda_short16.cu).
 constexpr int64_t kFusedMaxT = 32;
@@ -400,8 +445,8 @@ constexpr int64_t kFusedMaxT = 32;
 // Duration of a pass of `ctas` CTAs in hundredths of one chunk step of the look-ahead kernel, per chunk of run length,
 // and the kernel that achieves it: the look-ahead kernel runs one CTA per SM, the compact kernel two at 1.58 times the
 // step (measured).
-inline int64_t pass_cost_x100(int64_t ctas, bool* compact, int64_t la_step_x100 = 100) {
-  const int64_t la = (ctas + kPlanSms - 1) / kPlanSms * la_step_x100, co = (ctas + 2 * kPlanSms - 1) / (2 * kPlanSms) * 158;
+inline int64_t pass_cost_x100(int64_t ctas, bool* compact, int64_t sms, int64_t la_step_x100 = 100) {
+  const int64_t la = (ctas + sms - 1) / sms * la_step_x100, co = (ctas + 2 * sms - 1) / (2 * sms) * 158;
   *compact = co < la;
   return co < la ? co : la;
 }
@@ -409,13 +454,13 @@ inline int64_t pass_cost_x100(int64_t ctas, bool* compact, int64_t la_step_x100 
 // How many runs to cut each sequence of a batch into (1 = walk whole sequences), and their length in chunks (varlen
 // batches: called with the average sequence length; the run length is then set on the device from the longest one).  Pass 1 holds chains * (2 n - 3) CTAs and pass 2 chains * (n - 1), both walking ceil(chunks / n) chunks, each
 // on whichever recurrence kernel gets that many CTAs through faster; chaining the maps costs about three chunk steps
-// per run.  The plan is a pure function of the sizes so that the workspace size and the launch agree; it assumes the
-// 148 SMs of a B200.
-inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
+// per run.  The plan is a pure function of the sizes and the device's SM count, so that the workspace size and the
+// launch agree.
+inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks, int64_t sms) {
   *seg_chunks = 0;
-  if (chains <= 0 || chains * 3 > kPlanSms || chunks < 48) return 1;
+  if (chains <= 0 || chains * 3 > sms || chunks < 48) return 1;
   bool c;
-  const int64_t whole = pass_cost_x100(chains, &c) * chunks;
+  const int64_t whole = pass_cost_x100(chains, &c, sms) * chunks;
   int64_t best = whole, best_n = 1;
   for (int64_t n = 3; n <= 160; ++n) {
     const int64_t len = (chunks + n - 1) / n;
@@ -423,8 +468,8 @@ inline int plan_segments(int64_t chains, int64_t chunks, int* seg_chunks) {
     if ((n - 1) * len >= chunks) continue;       // the last run would be empty
     // (a run walks its chunks about a tenth more slowly than a whole sequence; each pass costs about ten chunk steps of
     // launch, set-up and state traffic; a step of the map chaining about two and a half, per wave of its chains x 8 CTAs)
-    const int64_t cmb_waves = (chains * 8 + kPlanSms - 1) / kPlanSms;
-    const int64_t cost = (pass_cost_x100(chains * (2 * n - 3), &c, 110) + pass_cost_x100(chains * (n - 1), &c, 110)) * len + 100 * 20 +
+    const int64_t cmb_waves = (chains * 8 + sms - 1) / sms;
+    const int64_t cost = (pass_cost_x100(chains * (2 * n - 3), &c, sms, 110) + pass_cost_x100(chains * (n - 1), &c, sms, 110)) * len + 100 * 20 +
                          250 * (n - 2) * cmb_waves;
     if (cost < best) { best = cost; best_n = n; }
   }

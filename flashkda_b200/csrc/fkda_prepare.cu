@@ -26,8 +26,8 @@ namespace fkda {
 // For batches with few chains that are walked in runs (n_segs > 1) it sets the run length, status[2]: the longest
 // sequence's chunks spread over the runs, at least 8 chunks.
 constexpr int kOrderMax = 4096;      // batches of more sequences keep the given order
-__global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int H, int n_segs, int* __restrict__ prefix,
-                                    int* __restrict__ status) {
+__global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64_t T_total, int H, int n_segs, int sms,
+                                    int* __restrict__ prefix, int* __restrict__ status) {
   __shared__ int warp_sums[32];
   __shared__ int carry;
   __shared__ int longest;
@@ -82,8 +82,8 @@ __global__ void chunk_prefix_kernel(const int64_t* __restrict__ cu, int N, int64
     // favour of the look-ahead kernel.
     const long long chains = static_cast<long long>(N) * H, total_steps = static_cast<long long>(prefix[N]) * H;
     const bool alike = static_cast<long long>(longest) * N * 100 <= 130ll * prefix[N];
-    const bool throughput = chains >= 2 * kPlanSms && static_cast<long long>(longest) * 195 * kPlanSms * 100 <= total_steps * 125 * 85;
-    status[1] = (chains > kPlanSms && (alike || throughput)) ? 1 : 0;
+    const bool throughput = chains >= 2 * sms && static_cast<long long>(longest) * 195 * sms * 100 <= total_steps * 125 * 85;
+    status[1] = (chains > sms && (alike || throughput)) ? 1 : 0;
     const int run_len = n_segs > 1 ? (longest + n_segs - 1) / n_segs : 0;
     status[2] = run_len < 8 ? 8 : run_len;
   }
@@ -666,7 +666,7 @@ store_record:
 
 cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int n_segs, int* prefix, int* status,
                                 cudaStream_t stream) {
-  chunk_prefix_kernel<<<1, N > 256 ? 1024 : 256, 0, stream>>>(cu, N, T_total, H, n_segs, prefix, status);
+  chunk_prefix_kernel<<<1, N > 256 ? 1024 : 256, 0, stream>>>(cu, N, T_total, H, n_segs, device_sm_count(), prefix, status);
   return cudaGetLastError();
 }
 
@@ -676,7 +676,8 @@ cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream) {
   const int64_t tail = p.T % kChunk;
   const bool short_path = p.cu_seqlens == nullptr && tail >= 1 && tail <= 16 && p.T < 4 * kChunk;
   auto kernel = short_path ? prepare_kernel<true> : prepare_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes);
+  static SmemOptIn opt_in[2];
+  cudaError_t e = opt_in[short_path ? 1 : 0].ensure(kernel, kPrepSmemBytes);
   if (e != cudaSuccess) return e;
   const unsigned grid = static_cast<unsigned>(p.total_chunks) * static_cast<unsigned>(p.H);
   kernel<<<grid, 256, kPrepSmemBytes, stream>>>(p);

@@ -428,7 +428,8 @@ cudaError_t launch_refmode(const __nv_bfloat16* q, const __nv_bfloat16* k, const
                            int H, int state_fp32, float scale, float gate_scale, cudaStream_t stream) {
   if (N * H == 0) return cudaSuccess;
   refmode::Params p{q, k, v, g, beta, A_log, dt_bias, initial_state, final_state, out, cu_seqlens, T, T_total, H, state_fp32, scale, gate_scale};
-  cudaError_t e = cudaFuncSetAttribute(refmode::refmode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, refmode::kSmemBytes);
+  static SmemOptIn opt_in;
+  cudaError_t e = opt_in.ensure(refmode::refmode_kernel, refmode::kSmemBytes);
   if (e != cudaSuccess) return e;
   refmode::refmode_kernel<<<static_cast<unsigned>(N * H), refmode::kThreads, refmode::kSmemBytes, stream>>>(p);
   return cudaGetLastError();

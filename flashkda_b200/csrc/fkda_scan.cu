@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
         bulk_g2s(sbase + kSmStage + s * kRecBytes, rec0 + static_cast<size_t>(c) * kRecBytes, kRecBytes, bar(BAR_FULL + s));
         issued = c + 1;
       }
-      if (failed || *abort_flag) {
+      if (failed || *abort_flag > 0) {
         // wait (bounded) for copies still in flight so that the CTA does not exit under them
         for (int c = issued > kStages ? issued - kStages : 0; c < issued; ++c) {
           const uint64_t t0 = globaltimer_ns();
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
     }
   }
 
-  if (failed || *abort_flag) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
 
   // ---- common exit: every thread arrives here, TMEM goes back ------------------------------------------------
   tc_fence_before();
@@ -365,7 +365,8 @@ cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream) {
   if (p.seg_chunks > 0) chains *= p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
   if (chains <= 0) return cudaSuccess;
   auto kernel = p.seg_chunks > 0 ? scan_kernel<true> : scan_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+  static SmemOptIn opt_in[2];
+  cudaError_t e = opt_in[p.seg_chunks > 0 ? 1 : 0].ensure(kernel, kScanSmemBytes);
   if (e != cudaSuccess) return e;
   kernel<<<static_cast<unsigned>(chains), kScanThreads, kScanSmemBytes, stream>>>(p);
   return cudaGetLastError();

@@ -25,11 +25,16 @@ namespace scan2 {
 // Optional timeline trace (bring-up / tuning aid): when a buffer has been registered with
 // fkda_debug_set_scan_trace, CTA 0 records clock64() at a few points of each role for its first
 // 32 chunks: entry [(role * 32 + chunk) * 8 + event].  No effect when no buffer is registered.
+// Compiled in only with -DFKDA_TUNING.
+#ifdef FKDA_TUNING
 static unsigned long long* g_trace = nullptr;
 #define FKDA_TRACE(role, c, ev)                                                                         \
   do {                                                                                                  \
     if (trace != nullptr && (c) < 32) trace[((role) * 32 + (c)) * 8 + (ev)] = static_cast<unsigned long long>(clock64()); \
   } while (0)
+#else
+#define FKDA_TRACE(role, c, ev) do { } while (0)
+#endif
 
 constexpr int kStages = 5;
 constexpr int kThreads = 20 * 32;
@@ -149,7 +154,12 @@ __device__ __noinline__ bool state_warp_loop(uint8_t* smem, uint32_t tq, int grp
 // kSeg: CTAs walk runs of a sequence (segment-parallel form) instead of whole sequences
 template <bool kSeg>
 __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, unsigned long long* trace_buf) {
+#ifdef FKDA_TUNING
   unsigned long long* trace = (blockIdx.x == 0) ? trace_buf : nullptr;
+#else
+  unsigned long long* trace = nullptr;
+  (void)trace_buf;
+#endif
   if (threadIdx.x == 0) FKDA_TRACE(4, 31, 1);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -248,7 +258,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
   // ---- setup -----------------------------------------------------------------------------------------------
   if (kSeg && tid < 128) reinterpret_cast<uint32_t*>(smem + kSmZero)[tid] = 0u;
   if (tid == 0) {
-    *abort_flag = 0;
+    *abort_flag = p.wait_limit_us > 0 ? -p.wait_limit_us : 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(BAR_FULL + s), 1);
       mbar_init(bar(BAR_EMPTY + s), 1 + 4 + 8);   // MMA commit + U warps + state warps
@@ -287,6 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     if (lane == 0) {
       int issued = 0;
       for (int c = 0; c < nchunks; ++c) {
+        if (p.stop_copies_after > 0 && c >= p.stop_copies_after) break;     // test aid: the consumers' next wait runs out
         const int s = c % kStages, k = c / kStages;
         if (k > 0 && !mbar_wait(bar(BAR_EMPTY + s), (k - 1) & 1, abort_flag, 64)) { failed = true; break; }
         FKDA_TRACE(4, c, 0);
@@ -294,7 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         bulk_g2s(sbase + kSmStage + s * kRecBytes, rec0 + static_cast<size_t>(c) * kRecBytes, kRecBytes, bar(BAR_FULL + s));
         issued = c + 1;
       }
-      if (failed || *abort_flag) {
+      if (failed || *abort_flag > 0) {
         // wait (bounded) for copies still in flight so that the CTA does not exit under them
         for (int c = issued > kStages ? issued - kStages : 0; c < issued; ++c) {
           const uint64_t t0 = globaltimer_ns();
@@ -627,7 +638,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
   }
 
   if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 4);
-  if (failed || *abort_flag) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
 
   // ---- common exit: every thread arrives here, TMEM goes back ------------------------------------------------
   tc_fence_before();
@@ -645,12 +656,20 @@ cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream) {
   if (p.seg_chunks > 0) chains *= p.seg_pass == 1 ? 2 * p.n_segs - 3 : p.n_segs - 1;
   if (chains <= 0) return cudaSuccess;
   auto kernel = p.seg_chunks > 0 ? scan2::scan2_kernel<true> : scan2::scan2_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan2::kSmemBytes);
+  static SmemOptIn opt_in[2];
+  cudaError_t e = opt_in[p.seg_chunks > 0 ? 1 : 0].ensure(kernel, scan2::kSmemBytes);
   if (e != cudaSuccess) return e;
-  kernel<<<static_cast<unsigned>(chains), scan2::kThreads, scan2::kSmemBytes, stream>>>(p, scan2::g_trace);
+#ifdef FKDA_TUNING
+  unsigned long long* trace = scan2::g_trace;
+#else
+  unsigned long long* trace = nullptr;
+#endif
+  kernel<<<static_cast<unsigned>(chains), scan2::kThreads, scan2::kSmemBytes, stream>>>(p, trace);
   return cudaGetLastError();
 }
 
+#ifdef FKDA_TUNING
 void set_scan_trace(unsigned long long* buf) { scan2::g_trace = buf; }
+#endif
 
 }  // namespace fkda

@@ -108,9 +108,13 @@ __global__ void __launch_bounds__(kThreads, 1) scan_short_kernel(const ScanParam
           mbar_arrive_expect_tx(bar(BAR_FULL + s), kRecBytes);
           bulk_g2s(sbase + kSmRec + s * kRecBytes, rec_ptr(chain_of(i), c), kRecBytes, bar(BAR_FULL + s));
         }
-      if (failed || *abort_flag) {
-        const uint64_t t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 20000ull) {}   // let copies in flight land before the CTA may exit
+      if (failed || *abort_flag > 0) {
+        // wait (bounded) for the copies still in flight, so that the CTA does not exit under them
+        for (int j = g > kRing ? g - kRing : 0; j < g; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(bar(BAR_FULL + j % kRing), (j / kRing) & 1))
+            if (globaltimer_ns() - t0 > 20000000ull) break;
+        }
       }
     }
   } else if (warp == 1) {
@@ -166,14 +170,17 @@ __global__ void __launch_bounds__(kThreads, 1) scan_short_kernel(const ScanParam
       if (has_in) bulk_g2s(smem_u32(stg_row(buf)), state_gptr(p.initial_state, chain_of(i)), half_bytes, bar(BAR_STFULL + buf));
     };
     int g = 0;
-    if (my_chains > 0) fetch_state(0);
+    int fetched = 0, consumed = 0;      // incoming states asked for / arrived and waited for
+    if (my_chains > 0) { fetch_state(0); fetched = 1; }
     for (int i = 0; i < my_chains && !failed; ++i) {
       const int buf = i & 1;
       if (i + 1 < my_chains) {
         bulk_wait_read_all();            // this lane's final-state store out of the other buffer (chain i-1) has been read
         fetch_state(i + 1);
+        fetched = i + 2;
       }
       if (!warp_wait(bar(BAR_STFULL + buf), (i >> 1) & 1, abort_flag)) { failed = true; break; }
+      consumed = i + 1;
       if (!warp_wait(bar(BAR_FULL + g % kRing), (g / kRing) & 1, abort_flag)) { failed = true; break; }
       // ---- initial state -> TMEM: bf16 copy (undecayed) and fp32 pre-decayed by the first chunk's e --------------
       {
@@ -294,6 +301,14 @@ __global__ void __launch_bounds__(kThreads, 1) scan_short_kernel(const ScanParam
         }
       }
     }
+    if (failed) {
+      // state copies asked for and never waited for: let them land (bounded) before the CTA may exit
+      for (int j = consumed; j < fetched; ++j) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar(BAR_STFULL + (j & 1)), (j >> 1) & 1))
+          if (globaltimer_ns() - t0 > 20000000ull) break;
+      }
+    }
     bulk_wait_read_all();
   } else if (warp >= 12) {
     // ===== output warps =============================================================================================
@@ -332,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan_short_kernel(const ScanParam
     }
   }
 
-  if (failed || *abort_flag) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -344,7 +359,8 @@ __global__ void __launch_bounds__(kThreads, 1) scan_short_kernel(const ScanParam
 }  // namespace scan_short
 
 cudaError_t launch_scan_short(const ScanParams& p, int sm_count, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(scan_short::scan_short_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan_short::kSmemBytes);
+  static SmemOptIn opt_in;
+  cudaError_t e = opt_in.ensure(scan_short::scan_short_kernel, scan_short::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int64_t chains = static_cast<int64_t>(p.N) * p.H;
   if (chains == 0) return cudaSuccess;

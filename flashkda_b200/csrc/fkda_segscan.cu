@@ -167,14 +167,16 @@ cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_ch
   // either recurrence kernel can walk the runs: whichever gets the pass's CTAs through in less time
   const int64_t chains = static_cast<int64_t>(p.N) * p.H;
   bool compact1, compact2;
-  pass_cost_x100(chains * (2 * n_segs - 3), &compact1);
-  pass_cost_x100(chains * (n_segs - 1), &compact2);
+  const int sms = device_sm_count();
+  pass_cost_x100(chains * (2 * n_segs - 3), &compact1, sms);
+  pass_cost_x100(chains * (n_segs - 1), &compact2, sms);
   if (kernel_choice) compact1 = compact2 = kernel_choice == 1;   // forced: 1 compact, 2 look-ahead
   p.seg_pass = 1;
   cudaError_t e = compact1 ? launch_scan(p, stream) : launch_scan2(p, stream);
   if (e != cudaSuccess) return e;
   if (n_segs > 2) {
-    e = cudaFuncSetAttribute(seg_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmbSmemBytes);
+    static SmemOptIn opt_in;
+    e = opt_in.ensure(seg_combine_kernel, kCmbSmemBytes);
     if (e != cudaSuccess) return e;
     const dim3 grid(static_cast<unsigned>(chains), kD / kCmbRows);
     seg_combine_kernel<<<grid, 256, kCmbSmemBytes, stream>>>(seg_buf, n_segs, p.status);

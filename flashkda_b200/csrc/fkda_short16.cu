@@ -446,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 2) short16_kernel(const Params p) {
   }
   }  // blocks
 
-  if (failed || *abort_flag) {
+  if (failed || *abort_flag > 0) {
     // the state copy may still be landing: give it a moment before this CTA's shared memory goes away
     const uint64_t t_begin = globaltimer_ns();
     while (!mbar_try_wait(bar, 0) && globaltimer_ns() - t_begin < 20000000ull) {}
@@ -475,7 +475,8 @@ cudaError_t launch_short16(const __nv_bfloat16* q, const __nv_bfloat16* k, const
   if (N * H == 0) return cudaSuccess;
   short16::Params p{q, k, v, g, beta, A_log, dt_bias, initial_state, final_state, out, T, H, state_fp32, scale, gate_scale, status};
   auto kernel = T <= short16::kRows ? short16::short16_kernel<true> : short16::short16_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, short16::kSmemBytes);
+  static SmemOptIn opt_in[2];
+  cudaError_t e = opt_in[T <= short16::kRows ? 1 : 0].ensure(kernel, short16::kSmemBytes);
   if (e != cudaSuccess) return e;
   kernel<<<static_cast<unsigned>(N * H), short16::kThreads, short16::kSmemBytes, stream>>>(p);
   return cudaGetLastError();

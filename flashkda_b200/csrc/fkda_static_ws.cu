@@ -16,7 +16,8 @@
 //
 // In host code the array's name is only a handle: the device address has to be asked for with
 // cudaGetSymbolAddress while the device in question is current.  That is done on the first call
-// on each device and cached, so make that first call outside any stream capture.  All calls on a
+// on each device and cached (the cache does not survive a cudaDeviceReset), so make that first call outside any
+// stream capture.  All calls on a
 // device share the one array and it keeps whatever the previous call left in it: the status
 // header is cleared at the start of every call and every record that is read is rewritten
 // first, but two calls that overlap on the GPU (different streams, or different threads) race
@@ -92,9 +93,11 @@ int fkda_fwd_static_ws(const fkda_fwd_params* p, void* cuda_stream) {
   q.workspace_bytes = kStaticWsBytes;
   {
     // few long chains would be cut into runs, which needs room beyond the records: where that room is missing the
-    // sequences are walked whole instead (slower, same result) rather than refused
-    int64_t with_runs = 0;
-    if (fkda_get_workspace_size_flags(p->B * p->T, p->H, p->N, p->flags, &with_runs) == FKDA_OK && with_runs > kStaticWsBytes)
+    // sequences are walked whole instead (slower, same result) rather than refused.  Decided on this call's exact
+    // layout, not on the upper bound that a size query gives.
+    int64_t exact = 0;
+    if (fkda_workspace_bytes_exact(p->B * p->T, p->H, p->N, p->cu_seqlens != nullptr, p->T, p->flags, &exact) == FKDA_OK &&
+        exact > kStaticWsBytes)
       q.flags |= FKDA_FLAG_SCAN_NO_SEGMENTS;
   }
   const int rc = fkda_fwd(&q, cuda_stream);
@@ -104,11 +107,16 @@ int fkda_fwd_static_ws(const fkda_fwd_params* p, void* cuda_stream) {
 
 int fkda_static_ws_read_status(void* cuda_stream, int* status) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || g_ws_ptr[dev] == nullptr) {
+  void* ws = nullptr;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    ws = g_ws_ptr[dev];
+  }
+  if (ws == nullptr) {
     snprintf(g_msg, sizeof(g_msg), "no call of fkda_fwd_static_ws has been made on this device yet");
     return FKDA_ERR_INVALID_ARGUMENT;
   }
-  const int rc = fkda_read_status(g_ws_ptr[dev], cuda_stream, status);
+  const int rc = fkda_read_status(ws, cuda_stream, status);
   if (rc != FKDA_OK) snprintf(g_msg, sizeof(g_msg), "%s", fkda_last_error());
   return rc;
 }

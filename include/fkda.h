@@ -43,6 +43,10 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
  * fkda_fwd only. */
 #define FKDA_FLAG_REFERENCE_ROUNDING 0x20u
 #define FKDA_FLAG_SCAN_NO_SEGMENTS 0x8u /* never cut sequences into runs that are walked in parallel */
+/* Send a fixed-length call of any T to the fused short-sequence kernel, which by default takes T <= 32 only (it is a
+ * complete forward pass, just slower than the two-kernel path beyond that; the flag exists so that tests can walk
+ * many blocks with it). */
+#define FKDA_FLAG_FUSED_ANY_T 0x40u
 /* Cut every sequence of the batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
  * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster
@@ -83,6 +87,11 @@ int fkda_get_workspace_size(int64_t T_total, int64_t H, int64_t N, int64_t* byte
  * No counterpart in the reference. */
 int fkda_get_workspace_size_flags(int64_t T_total, int64_t H, int64_t N, int64_t flags, int64_t* bytes);
 
+/* Bytes a call of exactly this form uses (fixed-length: T_per_seq tokens per sequence; varlen: the bound
+ * T_total/32 + N chunks), where fkda_get_workspace_size covers both forms.  No counterpart in the reference. */
+int fkda_workspace_bytes_exact(int64_t T_total, int64_t H, int64_t N, int varlen, int64_t T_per_seq, int64_t flags,
+                               int64_t* bytes);
+
 /* The planner of the segment-parallel recurrence: into how many runs (1 = none) a batch with `chains`
  * = N*H chains of `chunks_per_sequence` 32-token chunks is cut, and the run length in chunks.  (For a varlen batch the call plans with the average sequence length and
  * sets the run length on the device from the longest sequence.)  The reference has no
@@ -117,37 +126,14 @@ int fkda_workspace_layout(int64_t T_total, int64_t H, int64_t N, int varlen, int
  * The only call here that blocks the host. */
 int fkda_read_status(const void* workspace, void* cuda_stream, int* status);
 
-/* One-CTA tcgen05 products in the descriptor flavours of the scan kernel (mode 0,1,2; see
- * fkda_aux.cu).  A, B bf16 row-major, D fp32 row-major, all device pointers; status int32. */
-int fkda_selftest_umma(const void* A, const void* B, float* D, int mode, int reps, int* status,
-                       void* cuda_stream);
-
-/* Tuning aid: registers (or, with NULL, removes) a device buffer of 6*32*8 uint64 into which CTA 0 of
- * the scan kernel records clock64() at a few points of each warp role for its first 32 chunks. */
-int fkda_debug_set_scan_trace(void* device_buffer);
-
-/* Tuning aid: one CTA of `nwarps` (<= 16) warps times `reps` 32-column TMEM loads / stores per warp;
- * out = int64[nwarps][4] cycles for {loads, stores, 16-column stores, load+store round trips}. */
-int fkda_debug_tmem_bench(int nwarps, int reps, void* out, void* cuda_stream);
-
-/* Tuning aid: `issuers` (1..4) threads of one CTA each issue `reps` products of `ksteps` (1..8) tcgen05.mma
- * instructions (M = 128, K = 16, N = n in {32, 64, 128}; A from shared or tensor memory) and wait for their commit;
- * out = int64[issuers][2] cycles {until the last instruction was issued, until the commit arrived}; status[0] = 1 if
- * a bounded wait gave up. */
-int fkda_debug_umma_bench(int issuers, int reps, int ksteps, int n, int a_in_tmem, void* out, int* status, void* cuda_stream);
-
-/* Self-test of the 16-lane tensor-memory fragment shapes the scan kernel relies on (tcgen05.ld/st 16x256b and
- * 16x128b): out = uint32[4][2048], the register <-> (lane, column) maps as read back through the 32x32b shape
- * (see tmem_layout_probe_kernel).  One warp, a few microseconds.  No counterpart in the reference. */
-int fkda_debug_tmem_layout_probe(void* out, void* cuda_stream);
-
 /* The forward pass with built-in scratch, for callers that cannot allocate device memory (a
  * server whose memory pool was fixed at start-up, a plugin living inside another component's
  * budget).  No counterpart in the reference, whose Python wrapper allocates a workspace per call.
  * Same parameter block as fkda_fwd; `workspace` and `workspace_bytes` are ignored.  The scratch
  * is a 64 MiB array inside the library image (fkda_static_ws_capacity()), held by every GPU the
  * library is loaded on; problems that need more are rejected with FKDA_ERR_WORKSPACE_TOO_SMALL.
- * The first call on a device looks the array's address up, so issue it outside stream capture.
+ * The first call on a device looks the array's address up, so issue it outside stream capture; the
+ * address is cached per device and does not survive a cudaDeviceReset.
  * All calls on a device share the array: calls that overlap on the GPU race and must be
  * serialised by the caller.  Allocates nothing.  fkda_static_ws_read_status is
  * fkda_read_status for the built-in scratch of the current device. */

@@ -1,0 +1,149 @@
+"""GPU parity at the sizes the benchmark runs and at the sizes the reference's own tests reach.
+
+Each case runs the real workload on the GPU (inputs drawn there, so nothing large crosses
+PCIe) and checks a sample of (sequence, head) chains -- always including the longest sequence
+and the last chain -- against the fp64 recurrence, within the contract's tolerances (bf16 `out`
+max-abs <= 2e-2, final state relative error <= 1e-2).  Shapes follow the headline
+configurations and the reference's tests/test_fwd_full.py:59-60 (H up to 96, T up to 8192),
+:212-274 (T = 131 072, two sequences of 524 288) and tests/test_fwd.py:45-68, 315-363 (ten
+gate regimes at T = 8192 against an fp64 gold, RMSE ratio 0.005).
+"""
+import math
+
+import pytest
+import torch
+
+import flash_kda
+import flashkda_b200 as F
+import oracle
+from flashkda_b200.workloads import Workload, baseline_workload, make_inputs
+from helpers import OUT_MAX_ABS, STATE_REL
+
+pytestmark = pytest.mark.gpu
+
+
+def run_and_sample(w, pairs, flags=0, mutate=None, default_alloc=False, heads=None):
+    x = make_inputs(w, device="cuda", heads=heads)
+    if mutate is not None:
+        mutate(x)
+    out = torch.full_like(x["v"], float("nan"))
+    fin = x["final_state"]
+    if fin is not None:
+        fin.fill_(float("nan"))
+    B, T, H = x["q"].shape[:3]
+    kw = dict(initial_state=x["initial_state"], final_state=fin, cu_seqlens=x["cu_seqlens"])
+    ws = None
+    if not default_alloc:
+        ws = torch.empty(F.get_workspace_size(B * T, H, w.N, flags), dtype=torch.uint8, device="cuda")
+        kw.update(workspace=ws, flags=flags)
+    flash_kda.fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], out, x["A_log"], x["dt_bias"], x["lower_bound"], **kw)
+    if ws is not None:
+        assert F.read_status(ws) == 0
+    torch.cuda.synchronize()
+    # every row of every sequence was written (varlen: rows up to cu_seqlens[-1] = all rows here)
+    assert not torch.isnan(out.view(-1, 128)[:, 0].float()).any(), "some out rows were not written"
+    if fin is not None:
+        assert not torch.isnan(fin.view(-1, 128 * 128)[:, 0].float()).any(), "some final states were not written"
+    r = oracle.sampled_parity(x, out, fin, pairs)
+    print(f"{w.name}: {r}")
+    assert r["out_max_abs"] <= OUT_MAX_ABS and r["state_rel"] <= STATE_REL, r
+    return r
+
+
+def test_config1_fixed_B4_T8192_H32():
+    w = baseline_workload(1)
+    run_and_sample(w, [(0, 0), (2, 17), (3, 31)])
+
+
+def test_config2_varlen_N16_H32():
+    w = baseline_workload(2)
+    longest = max(range(w.N), key=lambda i: w.seq_lens[i])
+    shortest = min(range(w.N), key=lambda i: w.seq_lens[i])
+    run_and_sample(w, [(longest, 5), (shortest, 30), (w.N - 1, 31)])
+
+
+def test_config3_share_of_one_gpu_B1_T131072_H8():
+    """One GPU's share of the long-context configuration when its 64 heads are split over 8 GPUs: 8 chains of 4096
+    chunks, walked as runs in parallel."""
+    w = baseline_workload(3)
+    runs, _ = F.plan_segments(8, w.T // 32)
+    assert runs > 1
+    run_and_sample(w, [(0, 0), (0, 7)], heads=range(8, 16))
+
+
+def test_config4_short_B512_T16_H32():
+    w = baseline_workload(4)
+    run_and_sample(w, [(0, 0), (255, 13), (511, 31)])
+
+
+def test_many_equal_chains_take_the_compact_kernel_by_default():
+    """Fixed-length batch with more chains than SMs and T > 160: the automatic choice of the two-CTAs-per-SM
+    recurrence kernel, on default flags and the default per-call workspace allocation."""
+    w = Workload("many", H=32, B=6, T=1024 + 19, state_in="bf16", state_out="bf16", seed=41)
+    run_and_sample(w, [(0, 0), (5, 31), (3, 9)], default_alloc=True)
+
+
+def test_H96_T8192():
+    w = Workload("h96", H=96, B=1, T=8192, state_in="bf16", state_out="bf16", seed=42)
+    run_and_sample(w, [(0, 0), (0, 50), (0, 95)])
+
+
+def test_one_sequence_of_131072_tokens_H1():
+    w = Workload("t128k", H=1, B=1, T=131072, state_in="fp32", state_out="fp32", seed=43)
+    run_and_sample(w, [(0, 0)])
+
+
+def test_varlen_two_sequences_of_524288_tokens_H1():
+    w = Workload("t512kx2", H=1, seq_lens=[524288, 524288], state_in="fp32", state_out="fp32", seed=44)
+    run_and_sample(w, [(1, 0)])
+
+
+def _rmse_ratio_case(name):
+    """The reference's accuracy sweep (tests/test_fwd.py:45-68, 315-363): T = 8192, H = 1, A_log = 0, q, k, v ~ U(0,1),
+    initial state ~ N(0,1) fp32, one of ten gate regimes."""
+    gen = torch.Generator(device="cuda").manual_seed(42)
+    T, H = 8192, 1
+    rnd = lambda *s: torch.rand(*s, generator=gen, device="cuda")
+    randn = lambda *s: torch.randn(*s, generator=gen, device="cuda")
+    x = dict(q=rnd(1, T, H, 128).bfloat16(), k=rnd(1, T, H, 128).bfloat16(), v=rnd(1, T, H, 128).bfloat16(),
+             beta=randn(1, T, H).bfloat16(), A_log=torch.zeros(H, device="cuda"), scale=1.0 / math.sqrt(128),
+             lower_bound=-5.0, initial_state=randn(1, H, 128, 128), cu_seqlens=None)
+    g = torch.zeros(1, T, H, 128, device="cuda")
+    bias = torch.zeros(H, 128, device="cuda")
+    if name.startswith("g="):
+        spec = name[2:]
+        if spec == "U(-8,8)":
+            g = rnd(1, T, H, 128) * 16 - 8
+        elif spec == "N(0,8)":
+            g = randn(1, T, H, 128) * 8
+        else:
+            g = torch.full((1, T, H, 128), float(spec), device="cuda")
+    else:
+        spec = name[5:]
+        if spec in ("+-4", "+-8"):
+            a = float(spec[2:])
+            bias = torch.where(rnd(H, 128) < 0.5, -a, a)
+        elif spec == "U(-8,8)":
+            bias = rnd(H, 128) * 16 - 8
+        else:
+            bias = randn(H, 128) * 8
+    x["g"], x["dt_bias"] = g.bfloat16(), bias.float()
+    return x
+
+
+GATE_REGIMES = ["g=-8", "g=-4", "g=0", "g=8", "g=U(-8,8)", "g=N(0,8)", "bias=+-4", "bias=+-8", "bias=U(-8,8)", "bias=N(0,8)"]
+
+
+@pytest.mark.parametrize("regime", GATE_REGIMES)
+def test_accuracy_sweep_T8192_rmse_ratio(regime):
+    x = _rmse_ratio_case(regime)
+    out = torch.empty_like(x["v"])
+    fin = torch.empty(1, 1, 128, 128, device="cuda")
+    flash_kda.fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], out, x["A_log"], x["dt_bias"], x["lower_bound"],
+                  initial_state=x["initial_state"], final_state=fin)
+    torch.cuda.synchronize()
+    r = oracle.sampled_parity(x, out, fin, [(0, 0)])
+    print(f"{regime}: {r}")
+    # the reference's bound for its own kernels against the fp64 gold (state checks are warnings there)
+    assert r["out_rmse_ratio"] <= 0.005, r
+    assert r["state_rel"] <= STATE_REL, r

@@ -198,6 +198,36 @@ def test_long_chains_repeated_calls_stay_in_step(flags):
     assert max_abs(ref[0][:, :, :2], o64) <= OUT_MAX_ABS and rel_fro(ref[1][:, :2], s64) <= STATE_REL
 
 
+def test_bounded_wait_gives_up_and_the_context_stays_usable():
+    """A wait that nothing will complete: the copy producer of a two-chunk chain stops after the first record and the
+    waits are given three milliseconds.  The call must return (no hang), the status word must say 2, and the CTA must
+    have released its tensor memory - seen by a normal call right afterwards, which needs all of it.  Nothing faults
+    and no copy is in flight when the wait runs out."""
+    w = Workload("giveup", H=1, B=1, T=64, state_in="fp32", state_out="fp32", seed=3)
+    x = make_inputs(w)
+    xc = to_cuda(x)
+    ws = torch.empty(F.get_workspace_size(64, 1, 1), dtype=torch.uint8, device="cuda")
+    fin = torch.zeros(1, 1, 128, 128, device="cuda")
+    F.scan_giveup(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], x["scale"], xc["out"], xc["A_log"], xc["dt_bias"],
+                  x["lower_bound"], initial_state=xc["initial_state"], final_state=fin, workspace=ws,
+                  stop_copies_after=1, wait_limit_us=3000)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        F.read_status(ws)
+    torch.cuda.synchronize()
+    # a single-chunk chain never meets the missing record: same entry point, status 0
+    w1 = Workload("giveup1", H=1, B=1, T=32, state_in="fp32", state_out="fp32", seed=3)
+    x1 = make_inputs(w1)
+    x1c = to_cuda(x1)
+    fin1 = torch.zeros(1, 1, 128, 128, device="cuda")
+    F.scan_giveup(x1c["q"], x1c["k"], x1c["v"], x1c["g"], x1c["beta"], x1["scale"], x1c["out"], x1c["A_log"], x1c["dt_bias"],
+                  x1["lower_bound"], initial_state=x1c["initial_state"], final_state=fin1, workspace=ws,
+                  stop_copies_after=1, wait_limit_us=3000)
+    assert F.read_status(ws) == 0
+    # and the normal path works right after the give-up (tensor memory was released, the context is intact)
+    out, fin2 = run_gpu(x, torch.float32, F.FLAG_SCAN_LOOKAHEAD)
+    check_against_f64(x, out, fin2, "after a give-up")
+
+
 def test_deterministic_and_tail_rows_untouched():
     w = Workload("d", H=2, seq_lens=[45, 3], state_in="bf16", state_out="bf16", seed=4)
     x = make_inputs(w)
@@ -237,6 +267,15 @@ def test_argument_errors_raise_before_launch():
         call(final_state=torch.zeros(2, 2, 128, 128, device="cuda"))
     with pytest.raises(RuntimeError, match="int64"):
         call(cu_seqlens=torch.tensor([0, 32], dtype=torch.int32, device="cuda"))
+    with pytest.raises(RuntimeError, match="workspace must be a contiguous CUDA tensor"):      # a host tensor
+        flash_kda.fwd(*[xc[n] for n in ("q", "k", "v", "g", "beta", "scale", "out", "A_log", "dt_bias", "lower_bound")],
+                      workspace=torch.empty(F.get_workspace_size(32, 2, 1), dtype=torch.uint8))
+    with pytest.raises(RuntimeError, match="workspace must be a contiguous CUDA tensor"):      # a strided view
+        flash_kda.fwd(*[xc[n] for n in ("q", "k", "v", "g", "beta", "scale", "out", "A_log", "dt_bias", "lower_bound")],
+                      workspace=torch.empty(2 * F.get_workspace_size(32, 2, 1), dtype=torch.uint8, device="cuda")[::2])
+    with pytest.raises(RuntimeError, match="workspace must be uint8"):
+        flash_kda.fwd(*[xc[n] for n in ("q", "k", "v", "g", "beta", "scale", "out", "A_log", "dt_bias", "lower_bound")],
+                      workspace=torch.empty(F.get_workspace_size(32, 2, 1), dtype=torch.float32, device="cuda"))
     with pytest.raises(RuntimeError, match="D == 128"):
         z = torch.zeros(1, 32, 2, 64, dtype=torch.bfloat16, device="cuda")
         flash_kda.fwd(z, z, z, z, xc["beta"], 0.1, z.clone(), xc["A_log"], torch.zeros(2, 64, device="cuda"), -5.0)
@@ -365,28 +404,18 @@ def test_fused_short_sequences_match_two_kernel_path(T, state):
         assert max_abs(torch.cat([oa, ob], 1), o1) <= 1e-2 and rel_fro(sb, s1) <= 5e-3
 
 
-def test_fused_kernel_walks_many_blocks():
+@pytest.mark.parametrize("T,state", [(75, "fp32"), (1001, "bf16")])
+def test_fused_kernel_walks_many_blocks(T, state):
     """The fused kernel is a complete forward pass; the dispatch only sends T <= 32 to it because the two-kernel path
-    is faster beyond.  With the tuning variable that lifts the limit it must reproduce a 5-block and a 63-block walk
-    (ragged last block, bf16 and fp32 state).  Runs in a child process: the variable is read once per process."""
-    import os, subprocess, sys, textwrap
-    code = textwrap.dedent("""
-        import sys, torch
-        sys.path.insert(0, "tests")
-        import test_gpu_fwd as t
-        from flashkda_b200.workloads import Workload, make_inputs
-        for T, state in ((75, "fp32"), (1001, "bf16")):
-            w = Workload("fb", H=2, B=3, T=T, state_in=state, state_out=state, state_std=0.5, seed=T, lower_bound=-1.0)
-            x = make_inputs(w)
-            dt = torch.bfloat16 if state == "bf16" else torch.float32
-            out, fin = t.run_gpu(x, dt)
-            t.check_against_f64(x, out, fin, f"fused-many-blocks T={T}")
-        print("OK")
-    """)
-    env = dict(os.environ, FKDA_FUSED_MAX_T="100000")
-    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600,
-                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    assert res.returncode == 0 and "OK" in res.stdout, res.stdout + res.stderr
+    is faster beyond.  With the flag that lifts the limit it must reproduce a 5-block and a 63-block walk (ragged last
+    block, bf16 and fp32 state)."""
+    w = Workload("fb", H=2, B=3, T=T, state_in=state, state_out=state, state_std=0.5, seed=T, lower_bound=-1.0)
+    x = make_inputs(w)
+    dt = torch.bfloat16 if state == "bf16" else torch.float32
+    out, fin = run_gpu(x, dt, F.FLAG_FUSED_ANY_T)
+    check_against_f64(x, out, fin, f"fused-many-blocks T={T}")
+    o0, s0 = run_gpu(x, dt)
+    assert not torch.equal(out.view(torch.int16), o0.view(torch.int16)), "the flag did not change the path"
 
 
 def test_runs_on_the_current_stream():

@@ -116,8 +116,11 @@ def test_tmem_16_lane_fragment_shapes():
 
 
 def test_umma_bench_runs_inside_its_operand_arrays():
-    """The tcgen05.mma micro-benchmark (tuning aid) completes for every shape it accepts; accumulating instructions of
-    one thread are serialised by the accumulator (over 100 cycles each), those of several threads overlap."""
+    """The tcgen05.mma micro-benchmark (tuning aid, builds made with -DFKDA_TUNING only) completes for every shape it
+    accepts; accumulating instructions of one thread are serialised by the accumulator (over 100 cycles each), those
+    of several threads overlap."""
+    if not hasattr(F.lib(), "fkda_debug_umma_bench"):
+        pytest.skip("library built without -DFKDA_TUNING")
     one = F.umma_bench(issuers=1, reps=16, ksteps=8, n=128, a_in_tmem=False)
     four = F.umma_bench(issuers=4, reps=16, ksteps=8, n=32, a_in_tmem=True)
     assert one[1] > 60 and four[1] > 60

@@ -15,9 +15,15 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_functions():
-    text = open(os.path.join(ROOT, "include", "fkda.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(fkda_[a-z_0-9]+)\s*\(", text)))
+    """Every function the two headers declare (the part of the test-support header that only tuning builds have
+    left out)."""
+    names = set()
+    for header in ("fkda.h", "fkda_testing.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = re.sub(r"#ifdef FKDA_TUNING.*?#endif", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(fkda_[a-z_0-9]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol():
@@ -121,6 +127,7 @@ def test_flag_constants_match_the_header():
     assert values["FKDA_FLAG_SCAN_NO_SEGMENTS"] == F.FLAG_SCAN_NO_SEGMENTS
     assert values["FKDA_FLAG_NO_FUSED_SHORT"] == F.FLAG_NO_FUSED_SHORT
     assert values["FKDA_FLAG_REFERENCE_ROUNDING"] == F.FLAG_REFERENCE_ROUNDING
+    assert values["FKDA_FLAG_FUSED_ANY_T"] == F.FLAG_FUSED_ANY_T
     assert F.FLAG_SEGMENTS(5) == 5 << 8 and "FKDA_FLAG_SEGMENTS(n)" in text
 
 
