@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libfkda.so")
-SOURCES = ["fkda_api.cu", "fkda_prepare.cu", "fkda_scan.cu", "fkda_scan2.cu", "fkda_scan_short.cu", "fkda_segscan.cu", "fkda_short16.cu", "fkda_refmode.cu", "fkda_aux.cu", "fkda_static_ws.cu"]
+SOURCES = ["fkda_api.cu", "fkda_prepare.cu", "fkda_prepare_tc.cu", "fkda_scan.cu", "fkda_scan2.cu", "fkda_scan_short.cu", "fkda_segscan.cu", "fkda_short16.cu", "fkda_refmode.cu", "fkda_aux.cu", "fkda_static_ws.cu"]
 HEADERS = [os.path.join(CSRC, "fkda_common.cuh"), os.path.join(os.path.dirname(HERE), "include", "fkda.h"),
            os.path.join(os.path.dirname(HERE), "include", "fkda_testing.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -14,6 +14,7 @@ namespace fkda {
 cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int n_segs, int* prefix, int* status,
                                 cudaStream_t stream);
 cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
+cudaError_t launch_prepare_tc(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
@@ -130,8 +131,8 @@ int validate(const fkda_fwd_params* p, Layout* L) {
   if ((p->initial_state || p->final_state) && p->state_dtype != FKDA_STATE_BF16 && p->state_dtype != FKDA_STATE_FP32)
     return fail(FKDA_ERR_INVALID_ARGUMENT, "state_dtype must be bf16 or fp32 when a state tensor is given");
   if (!std::isfinite(p->scale) || !std::isfinite(p->lower_bound)) return fail(FKDA_ERR_INVALID_ARGUMENT, "scale and lower_bound must be finite");
-  if (p->lower_bound > 0.f || p->lower_bound < -5.45f)
-    return fail(FKDA_ERR_INVALID_ARGUMENT, "lower_bound must lie in [-5.45, 0]: a 16-token sub-block decays by at most 2^126");
+  if (p->lower_bound > 0.f || p->lower_bound < -5.2f)
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "lower_bound must lie in [-5.2, 0]: a 16-token sub-block may decay by at most 2^120");
   const void* ptrs[] = {p->q, p->k, p->v, p->g, p->out, p->dt_bias, p->initial_state, p->final_state};
   for (const void* x : ptrs)
     if (x && !aligned16(x)) return fail(FKDA_ERR_INVALID_ARGUMENT, "tensor base addresses must be 16-byte aligned");
@@ -182,7 +183,7 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     q.dbg = dbg_env ? atoi(dbg_env) : 0;
   }
 #endif
-  e = fkda::launch_prepare(q, stream);
+  e = (p->flags & FKDA_FLAG_PREPARE_MMA_SYNC) ? fkda::launch_prepare(q, stream) : fkda::launch_prepare_tc(q, stream);
   if (e != cudaSuccess) return cuda_fail(e, "prepare launch");
   return FKDA_OK;
 }

@@ -47,6 +47,9 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
  * complete forward pass, just slower than the two-kernel path beyond that; the flag exists so that tests can walk
  * many blocks with it). */
 #define FKDA_FLAG_FUSED_ANY_T 0x40u
+/* Use the earlier token-parallel kernel (mma.sync products, four CTAs per SM) instead of the TMA + tcgen05 one; kept
+ * as an independent implementation to cross-check against. */
+#define FKDA_FLAG_PREPARE_MMA_SYNC 0x80u
 /* Cut every sequence of the batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
  * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster
@@ -73,7 +76,7 @@ typedef struct fkda_fwd_params {
   int64_t H;                 /* heads                                                           */
   int64_t N;                 /* sequences: B, or len(cu_seqlens)-1                              */
   float scale;               /* applied to q (reference passes K^-0.5)                          */
-  float lower_bound;         /* gate lower bound, expected in [-5, 0]                           */
+  float lower_bound;         /* gate lower bound, expected in [-5, 0]; rejected outside [-5.2, 0] */
   int32_t state_dtype;       /* fkda_state_dtype of initial_state / final_state                 */
   uint32_t flags;
 } fkda_fwd_params;
