@@ -30,6 +30,7 @@ cudaError_t launch_refmode(const __nv_bfloat16* q, const __nv_bfloat16* k, const
 cudaError_t launch_scan_segmented(const ScanParams& base, int n_segs, int seg_chunks, float* seg_buf, int kernel_choice,
                                   cudaStream_t stream);
 #ifdef FKDA_TUNING
+void set_prepare_trace(long long* buf);
 void set_scan_trace(unsigned long long* buf);
 cudaError_t launch_tmem_bench(int nwarps, int reps, long long* out, cudaStream_t stream);
 cudaError_t launch_umma_bench(int nissuers, int reps, int ksteps, int n, int ts, long long* out, int* status, cudaStream_t stream);
@@ -183,7 +184,7 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     q.dbg = dbg_env ? atoi(dbg_env) : 0;
   }
 #endif
-  e = (p->flags & FKDA_FLAG_PREPARE_MMA_SYNC) ? fkda::launch_prepare(q, stream) : fkda::launch_prepare_tc(q, stream);
+  e = (p->flags & FKDA_FLAG_PREPARE_TCGEN05) ? fkda::launch_prepare_tc(q, stream) : fkda::launch_prepare(q, stream);
   if (e != cudaSuccess) return cuda_fail(e, "prepare launch");
   return FKDA_OK;
 }
@@ -421,6 +422,11 @@ int fkda_debug_tmem_layout_probe(void* out, void* cuda_stream) {
 }
 
 #ifdef FKDA_TUNING
+int fkda_debug_set_prepare_trace(void* device_buffer) {
+  fkda::set_prepare_trace(static_cast<long long*>(device_buffer));
+  return FKDA_OK;
+}
+
 int fkda_debug_set_scan_trace(void* device_buffer) {
   fkda::set_scan_trace(static_cast<unsigned long long*>(device_buffer));
   return FKDA_OK;

@@ -101,6 +101,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint: the hardware parks the warp until the phase completes or about `ns` nanoseconds
+// have passed, so a waiter takes no issue slots from the warps that work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait built on it, for kernels in which most warps wait most of the time.  Same contract as mbar_wait.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (!mbar_try_wait_hint(bar, parity, 4000u)) {
+    const int f = *abort_flag;
+    if (f > 0) return false;
+    const uint64_t limit = f < 0 ? static_cast<uint64_t>(-f) * 1000ull : 2000000000ull;
+    if (globaltimer_ns() - t0 > limit) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
 // Non-blocking probe of a barrier phase (for polling loops that watch several barriers).
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;

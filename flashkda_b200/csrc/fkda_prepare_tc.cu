@@ -6,12 +6,14 @@
 // so every recurrence kernel consumes its output unchanged.  An item is one (32-token chunk, head) pair; a CTA takes
 // items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps several of them in flight, each in a different stage:
 //
-//   producer (1 thread)      TMA tile loads of q, k, g, v ([32 tok][64 ch] boxes, 128-byte swizzle) into a 2-slot ring
+//   producer (1 thread)      TMA tile loads of q, k, g, v ([32 tok][64 ch] boxes, 128-byte swizzle) into a 2-slot ring;
+//                            the same thread issues the second products below
 //   element warps (2 x 8)    two groups, alternate items: L2 norms, gate, in-sub-block running sums, decayed operands
 //                            KPm, QPm, KMm (bf16, core-matrix layout) for the products, v re-laid as a product operand,
 //                            and the record parts that are final at this point (QP, KR, E) straight to global memory
-//   MMA thread               [A; M] = [KPm; QPm] KMm^T (K = 128 split over two accumulators), then, once T is there,
-//                            (w')^T = KPm^T TB^T and (u')^T = v^T TB^T (M = 128, N = 32, K = 32, TB as hi + lo bf16 parts)
+//   MMA threads (2)          first products [A; M] = [KPm; QPm] KMm^T (K = 128 split over two accumulators); second
+//                            products, once T is there, (w')^T = KPm^T TB^T and (u')^T = v^T TB^T (M = 128, N = 32,
+//                            K = 32, TB as hi + lo bf16 parts)
 //   inverse warps (2)        alternate items: A from tensor memory, T = (I + A)^-1 by fp32 forward substitution with
 //                            one column per lane, TB^T = (T diag(beta))^T as an MN-major operand
 //   M warp / output warps    tril(M) -> MQK; (w')^T scaled back and transposed through stmatrix.trans -> WP; (u')^T -> UP;
@@ -48,10 +50,10 @@ constexpr int kSmTbt = kSmOut + 2 * kOutBytes;            // 2 slots
 constexpr int kLdA = 36;                 // floats per row of the fp32 A matrix
 constexpr int kA32Bytes = 32 * kLdA * 4;
 constexpr int kSmA32 = kSmTbt + 2 * kTbtBytes;            // one per inverse warp
-constexpr int kInfoSlots = 16;
+constexpr int kInfoSlots = 12;         // an item's entry is last read up to nine items after it was written
 constexpr int kInfoBytes = 704;          // t0 (8) len h gc (12) pad (12) | beta[32] fp32 | cfac[128] fp32
 constexpr int kSmInfo = kSmA32 + 2 * kA32Bytes;
-constexpr int kSmElem = kSmInfo + kInfoSlots * kInfoBytes; // per element group: 2 copies x (ssq 1024 | tot 1024)
+constexpr int kSmElem = kSmInfo + kInfoSlots * kInfoBytes; // per element group: 2 copies x (ssq 1024 | 2^tot 1024)
 constexpr int kSmBars = kSmElem + 2 * 4096;
 constexpr int kSmMisc = kSmBars + 256;
 constexpr int kSmemBytes = kSmMisc + 64 + 1024;           // + slack for the manual 1024-byte alignment
@@ -80,7 +82,19 @@ static_assert(B_COUNT * 8 <= 256, "barrier area");
 struct Params {
   PrepParams p;
   int n_items_bound;   // total_chunks * H (varlen: an upper bound; the device knows the exact figure)
+  long long* trace;    // timeline buffer of a tuning build (else nullptr)
 };
+
+// Timeline of CTA 0 (tuning builds only): entry [item * 16 + event] = clock64() for its first 32 items.
+#ifdef FKDA_TUNING
+static long long* g_trace = nullptr;
+#define PTRACE(n, ev)                                                                                                  \
+  do {                                                                                                                 \
+    if (prm.trace != nullptr && blockIdx.x == 0 && (n) < 32) prm.trace[(n) * 16 + (ev)] = clock64();                    \
+  } while (0)
+#else
+#define PTRACE(n, ev) do { } while (0)
+#endif
 
 // ---- PTX wrappers used only here ------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
@@ -112,8 +126,9 @@ __device__ __forceinline__ void st_global_16(void* p, const uint4& v) {
   asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t backoff_ns = 0) {
-  const bool ok = mbar_wait(bar, parity, abort_flag, backoff_ns);
+// every wait of this kernel parks the warp (most warps of the CTA wait most of the time)
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const bool ok = mbar_wait_parked(bar, parity, abort_flag);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -131,7 +146,7 @@ __device__ __forceinline__ bool output_quadrant(uint8_t* smem, uint32_t tmem, in
   const uint32_t sbase = smem_u32(smem);
   const int slot = n & 1;
   auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
-  if (!warp_wait(bar(B_D2_FULL + slot), (n >> 1) & 1, abort_flag, 32)) return false;
+  if (!warp_wait(bar(B_D2_FULL + slot), (n >> 1) & 1, abort_flag)) return false;
   tc_fence_after();
   const uint32_t tq = tmem + (static_cast<uint32_t>(q * 32) << 16) + kColD2 + 64 * slot;
   uint32_t f0[16], f1[16], u[32];
@@ -142,8 +157,8 @@ __device__ __forceinline__ bool output_quadrant(uint8_t* smem, uint32_t tmem, in
   tc_fence_before();
   __syncwarp();
   if (lane == 0) mbar_arrive(bar(B_D2_EMPTY + slot));
-  if (n >= 2 && !warp_wait(bar(B_OUT_FREE + slot), ((n >> 1) - 1) & 1, abort_flag, 32)) return false;
-  const ItemInfo* info = reinterpret_cast<const ItemInfo*>(smem + kSmInfo + (n & (kInfoSlots - 1)) * kInfoBytes);
+  if (n >= 2 && !warp_wait(bar(B_OUT_FREE + slot), ((n >> 1) - 1) & 1, abort_flag)) return false;
+  const ItemInfo* info = reinterpret_cast<const ItemInfo*>(smem + kSmInfo + (n % kInfoSlots) * kInfoBytes);
   uint8_t* out = smem + kSmOut + slot * kOutBytes;
   {
     // WP [32 tok][128 k]: fragments hold (k, tok); the transposing store writes rows of 8 k per token
@@ -187,53 +202,36 @@ __device__ __forceinline__ bool output_quadrant(uint8_t* smem, uint32_t tmem, in
   return true;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-prepare_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const Params prm) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const uint32_t sbase = smem_u32(smem);
-  const PrepParams& p = prm.p;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
-  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
-  auto info_of = [&](int n) { return reinterpret_cast<ItemInfo*>(smem + kSmInfo + (n & (kInfoSlots - 1)) * kInfoBytes); };
+// Common to every role: the kernel's context, unpacked once per role function.
+#define ROLE_PROLOGUE                                                                                                  \
+  const uint32_t sbase = smem_u32(smem);                                                                               \
+  const PrepParams& p = prm.p;                                                                                         \
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;                                                       \
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);                                      \
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };                                                           \
+  auto info_of = [&](int n) { return reinterpret_cast<ItemInfo*>(smem + kSmInfo + (n % kInfoSlots) * kInfoBytes); }; \
+  const int H = p.H;                                                                                                   \
+  bool failed = false;                                                                                                 \
+  (void)sbase; (void)tid; (void)lane; (void)warp; (void)H; (void)info_of;
 
-  // items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... below the number of (chunk, head) pairs that exist
-  const int H = p.H;
-  long long n_eff = prm.n_items_bound;
-  if (p.cu_seqlens != nullptr) n_eff = static_cast<long long>(p.chunk_prefix[p.N]) * H;
-  if (n_eff > prm.n_items_bound) n_eff = prm.n_items_bound;
-  const int my_items = n_eff > blockIdx.x ? static_cast<int>((n_eff - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
-
-  if (tid == 0) {
-    *abort_flag = 0;
-    const int counts[B_COUNT] = {1, 1, 8, 8, 8, 8, 1, 1, 1, 1, 1, 1, 1, 2, 2, 1, 1, 1, 1, 1, 1, 4, 4, 5, 5, 1, 1, 8, 8};
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), counts[i]);
-    fence_mbar_init();
-    prefetch_tensormap(&tm_q);
-    prefetch_tensormap(&tm_k);
-    prefetch_tensormap(&tm_g);
-    prefetch_tensormap(&tm_v);
-  }
-  if (warp == 3) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  bool failed = false;
-
-  if (warp == 2) {
-    // ===== producer: item -> (sequence, first token, length), tile loads =============================================
-    if (lane == 0) {
-      const int cps = p.cu_seqlens == nullptr ? static_cast<int>((p.T + kChunk - 1) / kChunk) : 0;
-      int seq = 0;           // varlen: sequence of the previous item (items come in increasing chunk order)
-      int issued = 0;
-      for (int n = 0; n < my_items; ++n) {
+__device__ __forceinline__ bool producer_and_second_products(uint8_t* smem, uint32_t tmem, const Params& prm, const CUtensorMap* tm_q_,
+                                                             const CUtensorMap* tm_k_, const CUtensorMap* tm_g_, const CUtensorMap* tm_v_,
+                                                             int my_items) {
+  ROLE_PROLOGUE
+  // ===== producer and second products, one thread: whichever has its inputs ready =====================================
+  // (tile loads of an item: item -> (sequence, first token, length), eight box loads;  second products of an item:
+  // (w')^T = KPm^T TB^T and (u')^T = VC^T TB^T once the inverse warp has written TB^T)
+  if (lane == 0) {
+    constexpr uint32_t idesc2 = umma_idesc_bf16(128, 32, 1, 1);
+    const int cps = p.cu_seqlens == nullptr ? static_cast<int>((p.T + kChunk - 1) / kChunk) : 0;
+    int seq = 0;           // varlen: sequence of the previous item (items come in increasing chunk order)
+    int np = 0, n2 = 0;    // next item to load / next item of the second products
+    uint64_t idle_since = 0;
+    uint32_t idle_polls = 0;
+    while (n2 < my_items) {
+      bool progressed = false;
+      if (np < my_items && (np < 2 || mbar_test(bar(B_STG_EMPTY + (np & 1)), ((np >> 1) - 1) & 1))) {
+        const int n = np;
         const long long it = blockIdx.x + static_cast<long long>(n) * gridDim.x;
         const int gc = static_cast<int>(it / H), h = static_cast<int>(it - static_cast<long long>(gc) * H);
         long long t0;
@@ -258,7 +256,7 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           len = rem < kChunk ? static_cast<int>(rem) : kChunk;
         }
         const int slot = n & 1;
-        if (n >= 2 && !mbar_wait(bar(B_STG_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag, 64)) { failed = true; break; }
+        PTRACE(n, 0);
         ItemInfo* info = info_of(n);
         info->t0 = t0;
         info->len = len;
@@ -268,291 +266,308 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_arrive_expect_tx(full, kStgBytes);
         const uint32_t dst = sbase + kSmStg + slot * kStgBytes;
         const int tc = static_cast<int>(t0);
-        tma_load_3d(dst, &tm_q, 0, h, tc, full);
-        tma_load_3d(dst + 4096, &tm_q, 64, h, tc, full);
-        tma_load_3d(dst + 8192, &tm_k, 0, h, tc, full);
-        tma_load_3d(dst + 12288, &tm_k, 64, h, tc, full);
-        tma_load_3d(dst + 16384, &tm_g, 0, h, tc, full);
-        tma_load_3d(dst + 20480, &tm_g, 64, h, tc, full);
-        tma_load_3d(dst + 24576, &tm_v, 0, h, tc, full);
-        tma_load_3d(dst + 28672, &tm_v, 64, h, tc, full);
-        issued = n + 1;
+        tma_load_3d(dst, tm_q_, 0, h, tc, full);
+        tma_load_3d(dst + 4096, tm_q_, 64, h, tc, full);
+        tma_load_3d(dst + 8192, tm_k_, 0, h, tc, full);
+        tma_load_3d(dst + 12288, tm_k_, 64, h, tc, full);
+        tma_load_3d(dst + 16384, tm_g_, 0, h, tc, full);
+        tma_load_3d(dst + 20480, tm_g_, 64, h, tc, full);
+        tma_load_3d(dst + 24576, tm_v_, 0, h, tc, full);
+        tma_load_3d(dst + 28672, tm_v_, 64, h, tc, full);
+        ++np;
+        progressed = true;
       }
-      if (failed || *abort_flag > 0) {
-        // wait (bounded) for loads still in flight so that the CTA does not exit under them
-        for (int n = issued > 2 ? issued - 2 : 0; n < issued; ++n) {
-          const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try_wait(bar(B_STG_FULL + (n & 1)), (n >> 1) & 1))
-            if (globaltimer_ns() - t0 > 20000000ull) break;
+      if (n2 < np && mbar_test(bar(B_TBT_FULL + (n2 & 1)), (n2 >> 1) & 1) &&
+          (n2 < 2 || mbar_test(bar(B_D2_EMPTY + (n2 & 1)), ((n2 >> 1) - 1) & 1))) {
+        const int n = n2, slot = n & 1;
+        tc_fence_after();
+        // A read MN-major from the [32 tok'][128] core-layout tiles (channel-adjacent core matrices 128 B apart, token
+        // groups 2048 B), B = TB^T [32 tok'][32 tok] read MN-major (token-adjacent core matrices 128 B apart, tok' groups
+        // 512 B); the hi and lo parts of TB accumulate.
+        const uint32_t opb = sbase + kSmOpb + (n % 3) * kOpbBytes;
+        const uint64_t ak = umma_desc(opb, 2048, 128), av = umma_desc(opb + 16384, 2048, 128);
+        const uint64_t bt = umma_desc(sbase + kSmTbt + slot * kTbtBytes, 512, 128);
+        const uint32_t d = tmem + kColD2 + 64 * slot;
+#pragma unroll
+        for (int part = 0; part < 2; ++part)
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            umma_ss(d, ak + ks * 256, bt + part * 128 + ks * 64, idesc2, (part | ks) != 0);
+            umma_ss(d + 32, av + ks * 256, bt + part * 128 + ks * 64, idesc2, (part | ks) != 0);
+          }
+        umma_commit(bar(B_D2_FULL + slot));
+        umma_commit(bar(B_OPB_EMPTY + n % 3));
+        umma_commit(bar(B_TBT_EMPTY + slot));
+        PTRACE(n, 8);
+        ++n2;
+        progressed = true;
+      }
+      if (progressed) {
+        idle_since = 0;
+        idle_polls = 0;
+      } else {
+        // nothing ready: park (up to 100 ns) on the barrier that is due next
+        (void)mbar_try_wait_hint(bar(B_TBT_FULL + (n2 & 1)), (n2 >> 1) & 1, 100u);
+        if (((++idle_polls) & 63u) != 0u) continue;
+        const int f = *abort_flag;
+        if (f > 0) { failed = true; break; }
+        const uint64_t now = globaltimer_ns();
+        if (idle_since == 0) idle_since = now;
+        else if (now - idle_since > (f < 0 ? static_cast<uint64_t>(-f) * 1000ull : kWaitLimitNs)) {
+          *abort_flag = 1;
+          failed = true;
+          break;
         }
       }
     }
-  } else if (warp == 3) {
-    // ===== MMA thread: whichever product has its inputs ready, first products first ===================================
-    if (lane == 0) {
-      constexpr uint32_t idesc1 = umma_idesc_bf16(128, 32, 0, 0);
-      constexpr uint32_t idesc2 = umma_idesc_bf16(128, 32, 1, 1);
-      int n1 = 0, n2 = 0;           // next item of the first / second products
-      uint64_t idle_since = 0;
-      while (n2 < my_items) {
-        bool progressed = false;
-        if (n1 < my_items && mbar_test(bar(B_ELEM_DONE + (n1 & 1)), (n1 >> 1) & 1) &&
-            (n1 < 2 || mbar_test(bar(B_D1_EMPTY + (n1 & 1)), ((n1 >> 1) - 1) & 1))) {
-          const int n = n1, slot = n & 1;
-          tc_fence_after();
-          // [A; M] = [KPm; QPm] KMm^T: rows 64-127 of the A operand are whatever follows QPm in shared memory and land in
-          // accumulator lanes nobody reads.  K = 128 as two chains of four K = 16 steps into two accumulators, issued
-          // alternately so that the chains overlap.
-          const uint64_t a = umma_desc(sbase + kSmOpb + (n % 3) * kOpbBytes, 128, 2048);
-          const uint64_t b = umma_desc(sbase + kSmOpa + slot * 8192, 128, 2048);
-          const uint32_t d = tmem + kColD1 + 64 * slot;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            umma_ss(d, a + i * 16, b + i * 16, idesc1, i > 0);
-            umma_ss(d + 32, a + (4 + i) * 16, b + (4 + i) * 16, idesc1, i > 0);
-          }
-          umma_commit(bar(B_D1_FULL + slot));
-          umma_commit(bar(B_OPA_EMPTY + slot));
-          ++n1;
-          progressed = true;
-        }
-        if (n2 < n1 && mbar_test(bar(B_TBT_FULL + (n2 & 1)), (n2 >> 1) & 1) &&
-            (n2 < 2 || mbar_test(bar(B_D2_EMPTY + (n2 & 1)), ((n2 >> 1) - 1) & 1))) {
-          const int n = n2, slot = n & 1;
-          tc_fence_after();
-          // (w')^T [k][tok] = KPm^T TB^T, (u')^T [v][tok] = VC^T TB^T: A read MN-major from the [32 tok'][128] core-layout
-          // tiles (channel-adjacent core matrices 128 B apart, token groups 2048 B), B = TB^T [32 tok'][32 tok] read
-          // MN-major (token-adjacent core matrices 128 B apart, tok' groups 512 B); hi and lo parts of TB accumulate.
-          const uint32_t opb = sbase + kSmOpb + (n % 3) * kOpbBytes;
-          const uint64_t ak = umma_desc(opb, 2048, 128), av = umma_desc(opb + 16384, 2048, 128);
-          const uint64_t bt = umma_desc(sbase + kSmTbt + slot * kTbtBytes, 512, 128);
-          const uint32_t d = tmem + kColD2 + 64 * slot;
-#pragma unroll
-          for (int part = 0; part < 2; ++part)
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks) {
-              umma_ss(d, ak + ks * 256, bt + part * 128 + ks * 64, idesc2, (part | ks) != 0);
-              umma_ss(d + 32, av + ks * 256, bt + part * 128 + ks * 64, idesc2, (part | ks) != 0);
-            }
-          umma_commit(bar(B_D2_FULL + slot));
-          umma_commit(bar(B_OPB_EMPTY + n % 3));
-          umma_commit(bar(B_TBT_EMPTY + slot));
-          ++n2;
-          progressed = true;
-        }
-        if (progressed) {
-          idle_since = 0;
-        } else {
-          __nanosleep(32);
-          const int f = *abort_flag;
-          if (f > 0) { failed = true; break; }
-          const uint64_t now = globaltimer_ns();
-          if (idle_since == 0) idle_since = now;
-          else if (now - idle_since > (f < 0 ? static_cast<uint64_t>(-f) * 1000ull : kWaitLimitNs)) {
-            *abort_flag = 1;
-            failed = true;
-            break;
-          }
-        }
-      }
-      // the last commits' arrivals must have landed in shared memory before the CTA may exit
-      if (!failed && my_items > 0) {
-        const int n = my_items - 1;
-        if (!mbar_wait(bar(B_TBT_EMPTY + (n & 1)), (n >> 1) & 1, abort_flag)) failed = true;
-        if (!failed && my_items > 1 && !mbar_wait(bar(B_TBT_EMPTY + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag)) failed = true;
+    if (failed || *abort_flag > 0) {
+      // wait (bounded) for loads still in flight so that the CTA does not exit under them
+      for (int n = np > 2 ? np - 2 : 0; n < np; ++n) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar(B_STG_FULL + (n & 1)), (n >> 1) & 1))
+          if (globaltimer_ns() - t0 > 20000000ull) break;
       }
     }
-  } else if (warp == 0 || warp == 4) {
-    // ===== inverse warps (items of one parity each); they also take quadrant 0 of the output stage ===================
-    const int par = warp == 4 ? 1 : 0;
-    float* sA = reinterpret_cast<float*>(smem + kSmA32 + par * kA32Bytes);
-    for (int n = par; n < my_items; n += 2) {
-      const int slot = n & 1;
-      if (!warp_wait(bar(B_D1_FULL + slot), (n >> 1) & 1, abort_flag)) { failed = true; break; }
-      tc_fence_after();
-      {
-        uint32_t a0[32], a1[32];
-        tmem_ld32(tmem + kColD1 + 64 * slot, a0);
-        tmem_ld32(tmem + kColD1 + 64 * slot + 32, a1);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_D1_EMPTY + slot));
-        // row `lane` of A = tril(k+ k-^T, -1) scaled by beta of the row
-        const float bi = info_of(n)->beta[lane];
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          float4 r;
-          r.x = (4 * q4 + 0 < lane) ? (__uint_as_float(a0[4 * q4 + 0]) + __uint_as_float(a1[4 * q4 + 0])) * bi : 0.f;
-          r.y = (4 * q4 + 1 < lane) ? (__uint_as_float(a0[4 * q4 + 1]) + __uint_as_float(a1[4 * q4 + 1])) * bi : 0.f;
-          r.z = (4 * q4 + 2 < lane) ? (__uint_as_float(a0[4 * q4 + 2]) + __uint_as_float(a1[4 * q4 + 2])) * bi : 0.f;
-          r.w = (4 * q4 + 3 < lane) ? (__uint_as_float(a0[4 * q4 + 3]) + __uint_as_float(a1[4 * q4 + 3])) * bi : 0.f;
-          *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
-        }
-      }
-      __syncwarp();
-      // forward substitution, column `lane` of T = (I + A)^-1:  x_i = [i == c] - sum_{j<i} A_ij x_j.  Rows of A are read
-      // four entries at a time (all lanes the same address); entries on and above the diagonal are zero.
-      float x[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float acc = (i == lane) ? 1.f : 0.f;
-#pragma unroll
-        for (int q4 = 0; 4 * q4 < i; ++q4) {
-          const float4 a4 = *reinterpret_cast<const float4*>(sA + i * kLdA + 4 * q4);
-          acc = fmaf(-a4.x, x[4 * q4], acc);
-          acc = fmaf(-a4.y, x[4 * q4 + 1], acc);
-          acc = fmaf(-a4.z, x[4 * q4 + 2], acc);
-          acc = fmaf(-a4.w, x[4 * q4 + 3], acc);
-        }
-        x[i] = acc;
-      }
-      __syncwarp();
-      if (n >= 2 && !warp_wait(bar(B_TBT_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
-      {
-        // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c, as bf16 hi + lo parts
-        const float bc = info_of(n)->beta[lane];
-        uint8_t* row = smem + kSmTbt + slot * kTbtBytes + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t hi[4], lo[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float v0 = x[8 * cb + 2 * e] * bc, v1 = x[8 * cb + 2 * e + 1] * bc;
-            hi[e] = pack_bf16(v0, v1);
-            lo[e] = pack_bf16(v0 - bf_lo(hi[e]), v1 - bf_hi(hi[e]));
-          }
-          *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-          *reinterpret_cast<uint4*>(row + 2048 + cb * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_TBT_FULL + slot));
-      if (!output_quadrant(smem, tmem, 0, n, lane, abort_flag)) { failed = true; break; }
+    // the last commits' arrivals must have landed in shared memory before the CTA may exit
+    if (!failed && my_items > 0) {
+      const int n = my_items - 1;
+      if (!mbar_wait_parked(bar(B_TBT_EMPTY + (n & 1)), (n >> 1) & 1, abort_flag)) failed = true;
+      if (!failed && my_items > 1 && !mbar_wait_parked(bar(B_TBT_EMPTY + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag)) failed = true;
     }
-  } else if (warp == 1) {
-    // ===== M warp: tril(q+ k-^T) -> MQK ==============================================================================
+  }
+  return failed;
+}
+
+__device__ __forceinline__ bool first_products(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
+  ROLE_PROLOGUE
+  (void)tmem;
+  // ===== first products, one thread ====================================================================================
+  if (lane == 0) {
+    constexpr uint32_t idesc1 = umma_idesc_bf16(128, 32, 0, 0);
     for (int n = 0; n < my_items; ++n) {
       const int slot = n & 1;
-      if (!warp_wait(bar(B_D1_FULL + slot), (n >> 1) & 1, abort_flag, 32)) { failed = true; break; }
+      if (!mbar_wait_parked(bar(B_ELEM_DONE + slot), (n >> 1) & 1, abort_flag)) { failed = true; break; }
+      if (n >= 2 && !mbar_wait_parked(bar(B_D1_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
       tc_fence_after();
+      // [A; M] = [KPm; QPm] KMm^T: rows 64-127 of the A operand are whatever follows QPm in shared memory and land in
+      // accumulator lanes nobody reads.  K = 128 as two chains of four K = 16 steps into two accumulators, issued
+      // alternately so that the chains overlap.
+      const uint64_t a = umma_desc(sbase + kSmOpb + (n % 3) * kOpbBytes, 128, 2048);
+      const uint64_t b = umma_desc(sbase + kSmOpa + slot * 8192, 128, 2048);
+      const uint32_t d = tmem + kColD1 + 64 * slot;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        umma_ss(d, a + i * 16, b + i * 16, idesc1, i > 0);
+        umma_ss(d + 32, a + (4 + i) * 16, b + (4 + i) * 16, idesc1, i > 0);
+      }
+      umma_commit(bar(B_D1_FULL + slot));
+      umma_commit(bar(B_OPA_EMPTY + slot));
+      PTRACE(n, 4);
+    }
+    if (!failed && my_items > 0) {
+      const int n = my_items - 1;
+      if (!mbar_wait_parked(bar(B_OPA_EMPTY + (n & 1)), (n >> 1) & 1, abort_flag)) failed = true;
+      if (!failed && my_items > 1 && !mbar_wait_parked(bar(B_OPA_EMPTY + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag)) failed = true;
+    }
+  }
+  return failed;
+}
+
+__device__ __forceinline__ bool inverse_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
+  ROLE_PROLOGUE
+  (void)tmem;
+  // ===== inverse warps (items of one parity each); they also take quadrant 0 of the output stage ===================
+  const int par = warp == 4 ? 1 : 0;
+  float* sA = reinterpret_cast<float*>(smem + kSmA32 + par * kA32Bytes);
+  for (int n = par; n < my_items; n += 2) {
+    const int slot = n & 1;
+    if (!warp_wait(bar(B_D1_FULL + slot), (n >> 1) & 1, abort_flag)) { failed = true; break; }
+    tc_fence_after();
+    if (lane == 0) PTRACE(n, 5);
+    {
       uint32_t a0[32], a1[32];
-      const uint32_t tq = tmem + (32u << 16) + kColD1 + 64 * slot;
-      tmem_ld32(tq, a0);
-      tmem_ld32(tq + 32, a1);
+      tmem_ld32(tmem + kColD1 + 64 * slot, a0);
+      tmem_ld32(tmem + kColD1 + 64 * slot + 32, a1);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_D1_EMPTY + slot));
-      if (n >= 2 && !warp_wait(bar(B_OUT_FREE + slot), ((n >> 1) - 1) & 1, abort_flag, 32)) { failed = true; break; }
-      uint8_t* row = smem + kSmOut + slot * kOutBytes + (lane >> 3) * 512 + (lane & 7) * 16;
+      // row `lane` of A = tril(k+ k-^T, -1) scaled by beta of the row, stored transposed: sA[j][i] = A[i][j]
+      // (bank = (4 j + i) mod 32: conflict-free across the lanes i)
+      const float bi = info_of(n)->beta[lane];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        sA[j * kLdA + lane] = (j < lane) ? (__uint_as_float(a0[j]) + __uint_as_float(a1[j])) * bi : 0.f;
+    }
+    __syncwarp();
+    if (lane == 0) PTRACE(n, 6);
+    // forward substitution, column `lane` of T = (I + A)^-1, right-looking: once x_j is final, every later row takes
+    // its term A_ij x_j.  The updates of one step are independent of each other and the loads (column j of A, four
+    // rows at a time, all lanes the same address) do not depend on the arithmetic.
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = (i == lane) ? 1.f : 0.f;
+#pragma unroll
+    for (int j = 0; j < 31; ++j) {
+      const float xj = x[j];
+#pragma unroll
+      for (int i4 = 0; i4 < 8; ++i4) {
+        if (4 * i4 + 3 > j) {
+          const float4 a4 = *reinterpret_cast<const float4*>(sA + j * kLdA + 4 * i4);
+          if (4 * i4 + 0 > j) x[4 * i4 + 0] = fmaf(-a4.x, xj, x[4 * i4 + 0]);
+          if (4 * i4 + 1 > j) x[4 * i4 + 1] = fmaf(-a4.y, xj, x[4 * i4 + 1]);
+          if (4 * i4 + 2 > j) x[4 * i4 + 2] = fmaf(-a4.z, xj, x[4 * i4 + 2]);
+          if (4 * i4 + 3 > j) x[4 * i4 + 3] = fmaf(-a4.w, xj, x[4 * i4 + 3]);
+        }
+      }
+    }
+    __syncwarp();
+    if (n >= 2 && !warp_wait(bar(B_TBT_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
+    {
+      // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c, as bf16 hi + lo parts
+      const float bc = info_of(n)->beta[lane];
+      uint8_t* row = smem + kSmTbt + slot * kTbtBytes + (lane >> 3) * 512 + (lane & 7) * 16;
 #pragma unroll
       for (int cb = 0; cb < 4; ++cb) {
-        uint32_t w[4];
+        uint32_t hi[4], lo[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int c = 8 * cb + 2 * e;
-          const float v0 = (c <= lane) ? __uint_as_float(a0[c]) + __uint_as_float(a1[c]) : 0.f;
-          const float v1 = (c + 1 <= lane) ? __uint_as_float(a0[c + 1]) + __uint_as_float(a1[c + 1]) : 0.f;
-          w[e] = pack_bf16(v0, v1);
+          const float v0 = x[8 * cb + 2 * e] * bc, v1 = x[8 * cb + 2 * e + 1] * bc;
+          hi[e] = pack_bf16(v0, v1);
+          lo[e] = pack_bf16(v0 - bf_lo(hi[e]), v1 - bf_hi(hi[e]));
         }
-        *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(row + 2048 + cb * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_OUT_FULL + slot));
     }
-  } else if (warp >= 5 && warp < 8) {
-    // ===== output warps: quadrants 1-3 of (w')^T, (u')^T; warp 7 also sends MQK, WP, UP to the record ==================
-    const int q = warp & 3;
-    for (int n = 0; n < my_items; ++n) {
-      if (!output_quadrant(smem, tmem, q, n, lane, abort_flag)) { failed = true; break; }
-      if (warp == 7 && lane == 0) {
-        const int slot = n & 1;
-        if (!mbar_wait(bar(B_OUT_FULL + slot), (n >> 1) & 1, abort_flag, 32)) { failed = true; }
-        else {
-          const ItemInfo* info = info_of(n);
-          uint8_t* rec = p.records + (static_cast<size_t>(info->h) * p.total_chunks + info->gc) * kRecBytes;
-          const uint32_t src = sbase + kSmOut + slot * kOutBytes;
-          bulk_s2g(rec + kRecMQK, src, 2048);
-          bulk_s2g(rec + kRecWP, src + 2048, 8192);
-          bulk_s2g(rec + kRecUP, src + 10240, 8192);
-          bulk_commit();
-          bulk_wait_read0();
-          mbar_arrive(bar(B_OUT_FREE + slot));
-        }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) { PTRACE(n, 7); mbar_arrive(bar(B_TBT_FULL + slot)); }
+    if (!output_quadrant(smem, tmem, 0, n, lane, abort_flag)) { failed = true; break; }
+  }
+  return failed;
+}
+
+__device__ __forceinline__ bool m_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
+  ROLE_PROLOGUE
+  (void)tmem;
+  // ===== M warp: tril(q+ k-^T) -> MQK ==============================================================================
+  for (int n = 0; n < my_items; ++n) {
+    const int slot = n & 1;
+    if (!warp_wait(bar(B_D1_FULL + slot), (n >> 1) & 1, abort_flag)) { failed = true; break; }
+    tc_fence_after();
+    uint32_t a0[32], a1[32];
+    const uint32_t tq = tmem + (32u << 16) + kColD1 + 64 * slot;
+    tmem_ld32(tq, a0);
+    tmem_ld32(tq + 32, a1);
+    tmem_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B_D1_EMPTY + slot));
+    if (n >= 2 && !warp_wait(bar(B_OUT_FREE + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
+    uint8_t* row = smem + kSmOut + slot * kOutBytes + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+    for (int cb = 0; cb < 4; ++cb) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int c = 8 * cb + 2 * e;
+        const float v0 = (c <= lane) ? __uint_as_float(a0[c]) + __uint_as_float(a1[c]) : 0.f;
+        const float v1 = (c + 1 <= lane) ? __uint_as_float(a0[c + 1]) + __uint_as_float(a1[c + 1]) : 0.f;
+        w[e] = pack_bf16(v0, v1);
       }
-      failed = __any_sync(0xffffffffu, failed);
-      if (failed) break;
+      *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-  } else if (warp >= kElemWarp0) {
-    // ===== element warps ================================================================================================
-    const int grp = (warp - kElemWarp0) >> 3;
-    const int t = tid - (kElemWarp0 + 8 * grp) * 32;          // 0..255 inside the group
-    const int wg = t >> 5;
-    const int r8 = t & 7, cm = t >> 3, j = cm & 15, sb = cm >> 4;   // rows sb*16 + r8 (+8), channels 8j .. 8j+7
-    const int row0 = sb * 16 + r8, row1 = row0 + 8;
-    const int hh = j >> 3, cj = j & 7;
-    const float hgs = 0.5f * p.gate_scale;
-    uint8_t* const selem = smem + kSmElem + grp * 4096;
-    // per-head constants of the next item of this group, fetched one item ahead
-    float ha_n = 0.f;
-    float4 b0_n = make_float4(0.f, 0.f, 0.f, 0.f), b1_n = b0_n;
-    auto fetch_head = [&](int n) {
-      if (n < my_items) {
-        const long long it = blockIdx.x + static_cast<long long>(n) * gridDim.x;
-        const int h = static_cast<int>(it % H);
-        ha_n = __ldg(p.A_log + h);
-        b0_n = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
-        b1_n = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B_OUT_FULL + slot));
+  }
+  return failed;
+}
+
+__device__ __forceinline__ bool output_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
+  ROLE_PROLOGUE
+  (void)tmem;
+  // ===== output warps: quadrants 1-3 of (w')^T, (u')^T; warp 7 also sends MQK, WP, UP to the record ==================
+  const int q = warp & 3;
+  for (int n = 0; n < my_items; ++n) {
+    if (!output_quadrant(smem, tmem, q, n, lane, abort_flag)) { failed = true; break; }
+    if (warp == 7 && lane == 0) PTRACE(n, 9);
+    if (warp == 7 && lane == 0) {
+      const int slot = n & 1;
+      if (!mbar_wait_parked(bar(B_OUT_FULL + slot), (n >> 1) & 1, abort_flag)) { failed = true; }
+      else {
+        const ItemInfo* info = info_of(n);
+        uint8_t* rec = p.records + (static_cast<size_t>(info->h) * p.total_chunks + info->gc) * kRecBytes;
+        const uint32_t src = sbase + kSmOut + slot * kOutBytes;
+        bulk_s2g(rec + kRecMQK, src, 2048);
+        bulk_s2g(rec + kRecWP, src + 2048, 8192);
+        bulk_s2g(rec + kRecUP, src + 10240, 8192);
+        bulk_commit();
+        PTRACE(n, 10);
+        bulk_wait_read0();
+        PTRACE(n, 11);
+        mbar_arrive(bar(B_OUT_FREE + slot));
       }
-    };
-    fetch_head(grp);
-    for (int n = grp; n < my_items; n += 2) {
-      const int slot = n & 1, u = n >> 1;
-      float* s_ssq = reinterpret_cast<float*>(selem + (u & 1) * 2048);
-      float* s_tot = reinterpret_cast<float*>(selem + (u & 1) * 2048 + 1024);
-      if (!warp_wait(bar(B_STG_FULL + slot), u & 1, abort_flag)) { failed = true; break; }
-      ItemInfo* info = info_of(n);
-      const long long t0 = info->t0;
-      const int len = info->len, h = info->h;
-      uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + info->gc) * kRecBytes;
-      float braw = 0.f;
-      if (t < kChunk && t < len) braw = __bfloat162float(p.beta[static_cast<size_t>(t0 + t) * H + h]);
-      // gate: gamma = gate_scale sigmoid(a (g + bias)) = hgs tanh(ha g + ha bias) + hgs
-      const float ha = 0.5f * ex2f(ha_n * kLog2e);
-      float hab[8] = {ha * b0_n.x, ha * b0_n.y, ha * b0_n.z, ha * b0_n.w, ha * b1_n.x, ha * b1_n.y, ha * b1_n.z, ha * b1_n.w};
-      fetch_head(n + 2);
-      // ---- staged tiles -> registers (16-byte chunks of a row are XOR-swizzled by the row index: conflict-free) -------
-      const uint8_t* stg = smem + kSmStg + slot * kStgBytes + hh * 4096;
-      const int sw = (cj ^ r8) << 4;
-      uint4 qw[2], kw[2], gw[2];
-      const bool valid0 = row0 < len, valid1 = row1 < len;
-      const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
-      {
-        qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
-        qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
-        kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
-        kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
-        gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
-        gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
-        uint4 v0 = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
-        uint4 v1 = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
-        if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; v0 = z4; }      // rows past the sequence end belong to somebody else
-        if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; v1 = z4; }
-        // v goes on to the products as it is, in the core-matrix layout
-        if (n >= 3 && !warp_wait(bar(B_OPB_EMPTY + n % 3), ((n / 3) - 1) & 1, abort_flag)) { failed = true; break; }
-        uint8_t* vc = smem + kSmOpb + (n % 3) * kOpbBytes + 16384;
-        *reinterpret_cast<uint4*>(vc + core_off(row0, 8 * j, kD)) = v0;
-        *reinterpret_cast<uint4*>(vc + core_off(row1, 8 * j, kD)) = v1;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_STG_EMPTY + slot));
-      // ---- partial sums of squares, gate and its running sum inside the sub-block ------------------------------------
-      float G[2][8];
+    }
+    failed = __any_sync(0xffffffffu, failed);
+    if (failed) break;
+  }
+  return failed;
+}
+
+__device__ __forceinline__ bool element_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
+  ROLE_PROLOGUE
+  (void)tmem;
+  // ===== element warps ================================================================================================
+  const int grp = (warp - kElemWarp0) >> 3;
+  const int t = tid - (kElemWarp0 + 8 * grp) * 32;          // 0..255 inside the group
+  const int wg = t >> 5;
+  const int r8 = t & 7, cm = t >> 3, j = cm & 15, sb = cm >> 4;   // rows sb*16 + r8 (+8), channels 8j .. 8j+7
+  const int row0 = sb * 16 + r8, row1 = row0 + 8;
+  const int hh = j >> 3, cj = j & 7;
+  const float hgs = 0.5f * p.gate_scale;
+  uint8_t* const selem = smem + kSmElem + grp * 4096;
+  for (int n = grp; n < my_items; n += 2) {
+    const int slot = n & 1, u = n >> 1;
+    float* s_ssq = reinterpret_cast<float*>(selem + (u & 1) * 2048);
+    float* s_ex = reinterpret_cast<float*>(selem + (u & 1) * 2048 + 1024);      // [2 sub-blocks][128] 2^(sub-block total)
+    // per-head constants: asked for before the wait for the tiles (the head follows from the item number)
+    const int h = static_cast<int>((blockIdx.x + static_cast<long long>(n) * gridDim.x) % H);
+    const float a_log = __ldg(p.A_log + h);
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+    if (!warp_wait(bar(B_STG_FULL + slot), u & 1, abort_flag)) { failed = true; break; }
+    if (t == 0) PTRACE(n, 1);
+    ItemInfo* info = info_of(n);
+    const int len = info->len;
+    uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + info->gc) * kRecBytes;
+    float braw = 0.f;
+    if (t < kChunk && t < len) braw = __bfloat162float(p.beta[static_cast<size_t>(info->t0 + t) * H + h]);
+    // ---- staged tiles -> registers (16-byte chunks of a row are XOR-swizzled by the row index: conflict-free) -------
+    const uint8_t* stg = smem + kSmStg + slot * kStgBytes + hh * 4096;
+    const int sw = (cj ^ r8) << 4;
+    const bool valid0 = row0 < len, valid1 = row1 < len;
+    const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+    uint4 qw[2], kw[2], gw[2], vw[2];
+    qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
+    qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
+    kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
+    kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
+    gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
+    gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
+    vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
+    vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
+    if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
+    if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B_STG_EMPTY + slot));
+    // ---- partial sums of squares, gate and its running sum inside the sub-block ------------------------------------
+    // gate: gamma = gate_scale sigmoid(a (g + bias)) = hgs tanh(ha g + ha bias) + hgs
+    float G[2][8];
+    {
+      const float ha = 0.5f * ex2f(a_log * kLog2e);
+      const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int row = hf ? row1 : row0;
@@ -584,91 +599,149 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           G[hf][i] = x;
         }
       }
-      float tot[8];       // log2 decay of this thread's whole sub-block
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float first_half = __shfl_sync(0xffffffffu, G[0][i], 7, 8);
-        G[1][i] += first_half;
-        tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
-      }
-      if (r8 == 0) {
-        *reinterpret_cast<float4*>(s_tot + sb * kD + 8 * j) = make_float4(tot[0], tot[1], tot[2], tot[3]);
-        *reinterpret_cast<float4*>(s_tot + sb * kD + 8 * j + 4) = make_float4(tot[4], tot[5], tot[6], tot[7]);
-      }
-      // rendezvous of the group (a barrier with a bounded wait, so that a give-up elsewhere cannot strand a warp here)
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_GROUP + grp));
-      if (!warp_wait(bar(B_GROUP + grp), u & 1, abort_flag)) { failed = true; break; }
-      // ---- decayed operands --------------------------------------------------------------------------------------------
-      // With P = total of sub-block 0 and Q = total of sub-block 1 (per channel): exponent relative to P is G - P in
-      // sub-block 0 and G in sub-block 1; the record's q+ and k-to-the-end follow by 2^P and 2^Q.
-      float cq[8], cr[8];
-      {
-        const float4 o0 = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j);
-        const float4 o1 = *reinterpret_cast<const float4*>(s_tot + (1 - sb) * kD + 8 * j + 4);
-        const float to[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float P = sb == 0 ? tot[i] : to[i], Q = sb == 0 ? to[i] : tot[i];
-          cq[i] = ex2f(P);
-          cr[i] = ex2f(Q);
-          if (sb == 0) { G[0][i] -= P; G[1][i] -= P; }
-        }
-        if (sb == 0 && r8 == 0) {
-          float* cf = info->cfac + 8 * j;
-          *reinterpret_cast<float4*>(cf) = make_float4(cq[0], cq[1], cq[2], cq[3]);
-          *reinterpret_cast<float4*>(cf + 4) = make_float4(cq[4], cq[5], cq[6], cq[7]);
-          float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
-          *reinterpret_cast<float4*>(e) = make_float4(ex2f(tot[0] + to[0]), ex2f(tot[1] + to[1]), ex2f(tot[2] + to[2]), ex2f(tot[3] + to[3]));
-          *reinterpret_cast<float4*>(e + 4) = make_float4(ex2f(tot[4] + to[4]), ex2f(tot[5] + to[5]), ex2f(tot[6] + to[6]), ex2f(tot[7] + to[7]));
-        }
-      }
-      if (t < kChunk) info->beta[t] = t < len ? sigmoid_fast(braw) : 0.f;
-      if (n >= 2 && !warp_wait(bar(B_OPA_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
-      {
-        uint8_t* opb = smem + kSmOpb + (n % 3) * kOpbBytes;
-        uint8_t* opa = smem + kSmOpa + slot * 8192;
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int row = hf ? row1 : row0;
-          const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
-          const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
-          const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
-          const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
-          // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
-          const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
-          const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
-          __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
-#pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
-            const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
-            const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
-            const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
-            const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
-            kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
-            qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
-            kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
-            qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq[2 * m], qp1 * cq[2 * m + 1]));
-            kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr[2 * m], km1 * cr[2 * m + 1]));
-          }
-          auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
-            return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
-                              *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
-          };
-          const int off = core_off(row, 8 * j, kD);
-          *reinterpret_cast<uint4*>(opb + off) = as_u4(kpm);
-          *reinterpret_cast<uint4*>(opb + 8192 + off) = as_u4(qpm);
-          *reinterpret_cast<uint4*>(opa + off) = as_u4(kmm);
-          st_global_16(rec_dst + kRecQP + off, as_u4(qp));
-          st_global_16(rec_dst + kRecKR + off, as_u4(kr));
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_ELEM_DONE + slot));
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
+    {
+      // the thread that holds the last row of the sub-block publishes 2^(sub-block total) per channel
+      float tot[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
+      if (sb == 0) {      // exponents of sub-block 0 become relative to its end
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
+      }
+      if (r8 == 7) {
+        const float4 e0 = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
+        const float4 e1 = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
+        *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = e0;
+        *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = e1;
+        if (sb == 0) {
+          *reinterpret_cast<float4*>(info->cfac + 8 * j) = e0;
+          *reinterpret_cast<float4*>(info->cfac + 8 * j + 4) = e1;
+        }
+      }
+    }
+    if (t < kChunk) info->beta[t] = t < len ? sigmoid_fast(braw) : 0.f;
+    // rendezvous of the group (a barrier with a bounded wait, so that a give-up elsewhere cannot strand a warp here)
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B_GROUP + grp));
+    if (!warp_wait(bar(B_GROUP + grp), u & 1, abort_flag)) { failed = true; break; }
+    if (t == 0) PTRACE(n, 2);
+    // ---- decayed operands --------------------------------------------------------------------------------------------
+    // With P = total of sub-block 0 and Q = total of sub-block 1 (per channel), the exponents held now are G - P in
+    // sub-block 0 and G in sub-block 1: the products' k+, q+, k- come straight from them, the record's q+ and
+    // k-to-the-end take 2^P and 2^Q on top.
+    if (n >= 3 && !warp_wait(bar(B_OPB_EMPTY + n % 3), ((n / 3) - 1) & 1, abort_flag)) { failed = true; break; }
+    if (n >= 2 && !warp_wait(bar(B_OPA_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
+    {
+      uint8_t* opb = smem + kSmOpb + (n % 3) * kOpbBytes;
+      uint8_t* opa = smem + kSmOpa + slot * 8192;
+      if (sb == 0 && r8 == 0) {
+        const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
+        const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
+        float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
+        *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
+        *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
+      }
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int row = hf ? row1 : row0;
+        const int off = core_off(row, 8 * j, kD);
+        *reinterpret_cast<uint4*>(opb + 16384 + off) = vw[hf];       // v goes on to the products as it is
+        const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
+        const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
+        const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
+        const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
+        // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
+        const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
+        const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
+        __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
+          const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
+          const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
+          const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
+          const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
+          const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
+          const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
+          kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
+          qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
+          kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
+          qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
+          kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
+        }
+        auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
+          return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
+                            *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
+        };
+        *reinterpret_cast<uint4*>(opb + off) = as_u4(kpm);
+        *reinterpret_cast<uint4*>(opb + 8192 + off) = as_u4(qpm);
+        *reinterpret_cast<uint4*>(opa + off) = as_u4(kmm);
+        st_global_16(rec_dst + kRecQP + off, as_u4(qp));
+        st_global_16(rec_dst + kRecKR + off, as_u4(kr));
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (t == 0) PTRACE(n, 3);
+    if (lane == 0) mbar_arrive(bar(B_ELEM_DONE + slot));
   }
+  return failed;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+prepare_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v,
+                  const __grid_constant__ Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const PrepParams& p = prm.p;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
+
+  // items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... below the number of (chunk, head) pairs that exist
+  long long n_eff = prm.n_items_bound;
+  if (p.cu_seqlens != nullptr) n_eff = static_cast<long long>(p.chunk_prefix[p.N]) * p.H;
+  if (n_eff > prm.n_items_bound) n_eff = prm.n_items_bound;
+  const int my_items = n_eff > blockIdx.x ? static_cast<int>((n_eff - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+#pragma unroll
+    for (int i = 0; i < B_COUNT; ++i) {
+      const int count = (i >= B_STG_EMPTY && i < B_OPB_EMPTY) || i >= B_GROUP ? 8
+                        : (i >= B_D1_EMPTY && i < B_TBT_FULL)                 ? 2
+                        : (i >= B_D2_EMPTY && i < B_OUT_FULL)                 ? 4
+                        : (i >= B_OUT_FULL && i < B_OUT_FREE)                 ? 5
+                                                                              : 1;
+      mbar_init(bar(i), count);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_g);
+    prefetch_tensormap(&tm_v);
+  }
+  if (warp == 3) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool failed;
+  if (warp == 2) failed = producer_and_second_products(smem, tmem, prm, &tm_q, &tm_k, &tm_g, &tm_v, my_items);
+  else if (warp == 3) failed = first_products(smem, tmem, prm, my_items);
+  else if (warp == 0 || warp == 4) failed = inverse_warp(smem, tmem, prm, my_items);
+  else if (warp == 1) failed = m_warp(smem, tmem, prm, my_items);
+  else if (warp < kElemWarp0) failed = output_warp(smem, tmem, prm, my_items);
+  else failed = element_warp(smem, tmem, prm, my_items);
 
   if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
 
@@ -717,6 +790,10 @@ bool make_map(CUtensorMap* map, const void* base, int64_t T_total, int H) {
 
 }  // namespace prep_tc
 
+#ifdef FKDA_TUNING
+void set_prepare_trace(long long* buf) { prep_tc::g_trace = buf; }
+#endif
+
 cudaError_t launch_prepare_tc(const PrepParams& p, cudaStream_t stream) {
   if (p.total_chunks == 0 || p.H == 0 || p.T_total == 0) return cudaSuccess;
   CUtensorMap tq, tk, tg, tv;
@@ -730,6 +807,11 @@ cudaError_t launch_prepare_tc(const PrepParams& p, cudaStream_t stream) {
   prm.p = p;
   const long long items = static_cast<long long>(p.total_chunks) * p.H;
   prm.n_items_bound = static_cast<int>(items);
+#ifdef FKDA_TUNING
+  prm.trace = prep_tc::g_trace;
+#else
+  prm.trace = nullptr;
+#endif
   const int sms = device_sm_count();
   const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
   prep_tc::prepare_tc_kernel<<<grid, prep_tc::kThreads, prep_tc::kSmemBytes, stream>>>(tq, tk, tg, tv, prm);

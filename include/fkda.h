@@ -47,9 +47,10 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
  * complete forward pass, just slower than the two-kernel path beyond that; the flag exists so that tests can walk
  * many blocks with it). */
 #define FKDA_FLAG_FUSED_ANY_T 0x40u
-/* Use the earlier token-parallel kernel (mma.sync products, four CTAs per SM) instead of the TMA + tcgen05 one; kept
- * as an independent implementation to cross-check against. */
-#define FKDA_FLAG_PREPARE_MMA_SYNC 0x80u
+/* Token-parallel stage on the TMA + tcgen05 kernel (csrc/fkda_prepare_tc.cu: tile loads by TMA, products on tcgen05
+ * with accumulators in tensor memory, one persistent warp-specialised CTA per SM) instead of the default one
+ * (mma.sync products, four CTAs per SM), which is the faster of the two today.  Same operand records. */
+#define FKDA_FLAG_PREPARE_TCGEN05 0x80u
 /* Cut every sequence of the batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
  * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster

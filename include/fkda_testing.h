@@ -36,6 +36,10 @@ int fkda_debug_scan_giveup(const fkda_fwd_params* p, int stop_copies_after, int 
 /* The following exist only in builds made with -DFKDA_TUNING (FKDA_NVCC_EXTRA=-DFKDA_TUNING python -m
  * flashkda_b200.build --force). */
 
+/* Registers (or, with NULL, removes) a device buffer of 32*16 int64 into which CTA 0 of the TMA + tcgen05 token-parallel
+ * kernel records clock64() at the stage boundaries of its first 32 items (events: see PTRACE in csrc/fkda_prepare_tc.cu). */
+int fkda_debug_set_prepare_trace(void* device_buffer);
+
 /* Registers (or, with NULL, removes) a device buffer of 6*32*8 uint64 into which CTA 0 of the look-ahead
  * recurrence kernel records clock64() at a few points of each warp role for its first 32 chunks. */
 int fkda_debug_set_scan_trace(void* device_buffer);

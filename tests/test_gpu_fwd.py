@@ -73,6 +73,40 @@ def test_golden_cases(name, flags):
     assert d_out <= (1e-2 if big else OUT_MAX_ABS) and d_st <= STATE_REL
 
 
+@pytest.mark.parametrize("name", golden_names())
+def test_golden_cases_on_the_tma_tcgen05_token_parallel_kernel(name):
+    """The token-parallel stage on its TMA + tcgen05 kernel (flag FLAG_PREPARE_TCGEN05): same golden cases."""
+    x, ref_out, ref_fin = load_golden(name)
+    fin_dtype = None if ref_fin is None else ref_fin.dtype
+    out, fin = run_gpu(x, fin_dtype, F.FLAG_PREPARE_TCGEN05)
+    big = x["initial_state"] is not None and x["initial_state"].float().abs().max() > 100
+    check_against_f64(x, out, fin, f"{name}[tcgen05 prepare]", big_state=big)
+
+
+@pytest.mark.parametrize("case", ["fixed_tails", "varlen_ragged", "many_items", "long_repeat"])
+def test_tma_tcgen05_token_parallel_kernel_shapes(case):
+    """Shapes that stress the persistent kernel's pipeline: ragged last chunks, many short sequences (items of every
+    length), more items than one pass of the CTAs holds, and repeated calls that must be bit-reproducible."""
+    if case == "fixed_tails":
+        w = Workload("tc1", H=3, B=5, T=32 * 3 + 17, state_in="fp32", state_out="fp32", state_std=0.5, seed=61)
+    elif case == "varlen_ragged":
+        w = Workload("tc2", H=4, seq_lens=[1, 31, 32, 33, 0, 100, 7, 64, 250], state_in="bf16", state_out="bf16", state_std=0.5, seed=62)
+    elif case == "many_items":
+        w = Workload("tc3", H=8, B=6, T=2048 + 5, state_in="fp32", state_out="fp32", seed=63)
+    else:
+        w = Workload("tc4", H=16, B=2, T=1024, state_in="fp32", state_out="fp32", seed=64)
+    x = make_inputs(w)
+    dt = torch.bfloat16 if w.state_in == "bf16" else torch.float32
+    out, fin = run_gpu(x, dt, F.FLAG_PREPARE_TCGEN05)
+    check_against_f64(x, out, fin, f"tcgen05 prepare, {case}")
+    o0, s0 = run_gpu(x, dt)
+    assert max_abs(out, o0) <= 1e-2 and rel_fro(fin, s0) <= (2e-2 if dt == torch.bfloat16 else 5e-3)
+    if case == "long_repeat":
+        for _ in range(4):
+            o2, s2 = run_gpu(x, dt, F.FLAG_PREPARE_TCGEN05)
+            assert torch.equal(o2.view(torch.int16), out.view(torch.int16)) and torch.equal(s2, fin)
+
+
 STATE_IO = [(True, True), (True, False), (False, True), (False, False)]
 
 

@@ -47,8 +47,12 @@ def test_prologue_kernel():
     assert (bact.cpu().double() - br).abs().max() < 1e-3
 
 
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
 @pytest.mark.parametrize("case", ["fixed", "varlen", "strong_decay"])
-def test_prepare_records_match_fp64_operands(case):
+def test_prepare_records_match_fp64_operands(case, kernel):
+    """Operand records of both token-parallel kernels (the default one and the TMA + tcgen05 one) against the fp64
+    chunk operands of the oracle."""
+    flags = F.FLAG_PREPARE_TCGEN05 if kernel == "tcgen05" else 0
     if case == "fixed":
         w = Workload("f", H=2, B=2, T=80, seed=11)
     elif case == "varlen":
@@ -61,7 +65,7 @@ def test_prepare_records_match_fp64_operands(case):
         x["A_log"] = torch.full_like(x["A_log"], 2.0)
     xc = to_cuda(x)
     ws = F.prepare(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], xc["scale"], xc["out"], xc["A_log"],
-                   xc["dt_bias"], xc["lower_bound"], cu_seqlens=xc["cu_seqlens"])
+                   xc["dt_bias"], xc["lower_bound"], cu_seqlens=xc["cu_seqlens"], flags=flags)
     assert F.read_status(ws) == 0
     ws = ws.cpu()
     B, T = x["q"].shape[:2]
@@ -85,7 +89,7 @@ def test_prepare_records_match_fp64_operands(case):
                     worst[key] = max(worst.get(key, 0.0), err)
             gc += 1
         t_seq += L
-    print("prepare", case, {k: f"{v:.2e}" for k, v in worst.items()})
+    print("prepare", case, kernel, {k: f"{v:.2e}" for k, v in worst.items()})
     # bf16 operands: relative to the tile's largest entry; products of bf16-rounded factors ~1e-2.  qp and kr are built
     # with packed bf16 multiplies (two and three roundings of 2^-9 each).
     assert worst["qp"] < 8e-3 and worst["kr"] < 1.2e-2 and worst["ec"] < 2e-3, worst
