@@ -15,6 +15,7 @@ cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H
                                 cudaStream_t stream);
 cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_prepare_tc(const PrepParams& p, cudaStream_t stream);
+cudaError_t launch_prepare_tc4(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan2(const ScanParams& p, cudaStream_t stream);
@@ -184,7 +185,9 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     q.dbg = dbg_env ? atoi(dbg_env) : 0;
   }
 #endif
-  e = (p->flags & FKDA_FLAG_PREPARE_TCGEN05) ? fkda::launch_prepare_tc(q, stream) : fkda::launch_prepare(q, stream);
+  if (p->flags & FKDA_FLAG_PREPARE_TCGEN05_PERSISTENT) e = fkda::launch_prepare_tc(q, stream);
+  else if (p->flags & FKDA_FLAG_PREPARE_TCGEN05) e = fkda::launch_prepare_tc4(q, stream);
+  else e = fkda::launch_prepare(q, stream);
   if (e != cudaSuccess) return cuda_fail(e, "prepare launch");
   return FKDA_OK;
 }

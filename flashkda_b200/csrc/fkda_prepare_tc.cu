@@ -790,6 +790,471 @@ bool make_map(CUtensorMap* map, const void* base, int64_t T_total, int H) {
 
 }  // namespace prep_tc
 
+// =====================================================================================================================
+// The same stage with the structure of the default kernel: one CTA of eight warps per (chunk, head) item, four CTAs per
+// SM, every warp doing element-wise work, phases separated by CTA-wide barriers -- and the data path of the kernel
+// above: TMA tile loads, the intra-chunk products and w' / u' on tcgen05 with TMEM accumulators (128 columns per CTA).
+// Other resident CTAs fill the waits of the serial part (first products -> inverse on one warp -> second products).
+namespace prep_tc4 {
+
+using prep_tc::tma_load_3d;
+using prep_tc::prefetch_tensormap;
+using prep_tc::tmem_ld_16x256b_x4;
+using prep_tc::stsm_x4_trans;
+using prep_tc::st_global_16;
+
+constexpr int kThreads = 256;
+constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kColD1 = 0;            // 2 accumulators x 32 columns: rows 0-31 A, 32-63 M
+constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
+// shared memory (bytes).  [0, 32768): the staged q, k, g, v tiles (two [32 tok][128 B] swizzled halves each), then, once
+// every thread holds its share in registers, KPm | QPm | KMm | VC (core layout [32][128], 8192 each); after the first
+// products the QPm and KMm regions receive WP and UP.
+constexpr int kSmX = 0;
+constexpr int kLdA = 36;
+constexpr int kSmA = 32768;                              // fp32 A [32][36]; its unused upper right block holds the merge scratch
+constexpr int kSmT = kSmA + 32 * kLdA * 4;               // fp32 T [32][36]
+constexpr int kSmTbt = kSmT + 32 * kLdA * 4;             // TB^T bf16 [32][32], core layout
+constexpr int kSmMqk = kSmTbt + 2048;                    // MQK bf16 [32][32], core layout
+constexpr int kSmSsq = kSmMqk + 2048;                    // [2][32][4] partial sums of squares
+constexpr int kSmEx = kSmSsq + 1024;                     // [2][128] 2^(sub-block total)
+constexpr int kSmBeta = kSmEx + 1024;                    // [32] sigmoid(beta)
+constexpr int kSmBars = kSmBeta + 128;                   // 3 mbarriers
+constexpr int kSmMisc = kSmBars + 32;                    // tmem base, abort flag
+constexpr int kSmemBytes = 49152;                        // a multiple of 1024: the next CTA's tiles stay 1024-byte aligned
+static_assert(kSmMisc + 16 <= kSmemBytes, "shared memory plan");
+static_assert(4 * (kSmemBytes + 1024) <= 227 * 1024, "four CTAs per SM");
+enum { B_LOAD = 0, B_D1 = 1, B_D2 = 2 };
+
+__global__ void __launch_bounds__(kThreads, 4)
+prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
+  float* s_ssq = reinterpret_cast<float*>(smem + kSmSsq);
+  float* s_ex = reinterpret_cast<float*>(smem + kSmEx);
+  float* s_beta = reinterpret_cast<float*>(smem + kSmBeta);
+  float* sA = reinterpret_cast<float*>(smem + kSmA);
+  float* sT = reinterpret_cast<float*>(smem + kSmT);
+  float* sX = sA + 16;
+
+  // consecutive CTAs take consecutive heads of the same chunk
+  const int h = static_cast<int>(blockIdx.x % static_cast<unsigned>(p.H));
+  const int gc = static_cast<int>(blockIdx.x / static_cast<unsigned>(p.H));
+  int64_t t0;
+  int len;
+  if (p.cu_seqlens != nullptr) {
+    if (gc >= p.chunk_prefix[p.N]) return;
+    int lo = 0, hi = p.N - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.chunk_prefix[mid] <= gc) lo = mid; else hi = mid - 1;
+    }
+    int64_t bos = p.cu_seqlens[lo], eos = p.cu_seqlens[lo + 1];
+    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
+    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
+    t0 = bos + static_cast<int64_t>(gc - p.chunk_prefix[lo]) * kChunk;
+    const int64_t rem = eos - t0;
+    len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  } else {
+    const int cps = static_cast<int>((p.T + kChunk - 1) / kChunk);
+    const int n = gc / cps, lc = gc - n * cps;
+    t0 = static_cast<int64_t>(n) * p.T + static_cast<int64_t>(lc) * kChunk;
+    const int64_t rem = p.T - static_cast<int64_t>(lc) * kChunk;
+    len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  }
+  if ((sbase & 1023u) != 0u) {       // the swizzled tiles need this alignment: report instead of computing garbage
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+    return;
+  }
+  uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + gc) * kRecBytes;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(B_LOAD), 1);
+    mbar_init(bar(B_D1), 1);
+    mbar_init(bar(B_D2), 1);
+    fence_mbar_init();
+    const uint32_t full = bar(B_LOAD);
+    mbar_arrive_expect_tx(full, 32768);
+    const int tc = static_cast<int>(t0);
+    tma_load_3d(sbase + kSmX, &tm_q, 0, h, tc, full);
+    tma_load_3d(sbase + kSmX + 4096, &tm_q, 64, h, tc, full);
+    tma_load_3d(sbase + kSmX + 8192, &tm_k, 0, h, tc, full);
+    tma_load_3d(sbase + kSmX + 12288, &tm_k, 64, h, tc, full);
+    tma_load_3d(sbase + kSmX + 16384, &tm_g, 0, h, tc, full);
+    tma_load_3d(sbase + kSmX + 20480, &tm_g, 64, h, tc, full);
+    tma_load_3d(sbase + kSmX + 24576, &tm_v, 0, h, tc, full);
+    tma_load_3d(sbase + kSmX + 28672, &tm_v, 64, h, tc, full);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  // thread -> two (row, 8-column) pieces of one sub-block, as in the default kernel
+  const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
+  const int row0 = sb * 16 + r8, row1 = row0 + 8;
+  const int hh = j >> 3, cj = j & 7;
+  const float a_log = __ldg(p.A_log + h);
+  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
+  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+  if (tid < kChunk) s_beta[tid] = tid < len ? sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(t0 + tid) * p.H + h])) : 0.f;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool failed = false;
+
+  // ---- P1: staged tiles -> registers, partial sums of squares, gate and its running sum ----------------------------
+  uint4 qw[2], kw[2], vw[2];
+  float G[2][8];
+  {
+    if (!mbar_wait(bar(B_LOAD), 0, abort_flag)) failed = true;
+    const uint8_t* stg = smem + kSmX + hh * 4096;
+    const int sw = (cj ^ r8) << 4;
+    const bool valid0 = row0 < len, valid1 = row1 < len;
+    const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+    uint4 gw[2];
+    qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
+    qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
+    kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
+    kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
+    gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
+    gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
+    vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
+    vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
+    if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
+    if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
+    const float hgs = 0.5f * p.gate_scale;
+    const float ha = 0.5f * ex2f(a_log * kLog2e);
+    const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;
+      float f[8], sq = 0.f, sk = 0.f;
+      unpack8(qw[hf], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq = fmaf(f[i], f[i], sq);
+      unpack8(kw[hf], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sk = fmaf(f[i], f[i], sk);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+      if (lane < 8) {
+        s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
+        s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
+      }
+      unpack8(gw[hf], f);
+      const bool valid = hf ? valid1 : valid0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float x = valid ? fmaf(tanh_approx(fmaf(f[i], ha, hab[i])), hgs, hgs) : 0.f;
+#pragma unroll
+        for (int d = 1; d < 8; d <<= 1) {
+          const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
+          if (r8 >= d) x += y;
+        }
+        G[hf][i] = x;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
+    float tot[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
+    if (sb == 0) {      // exponents of sub-block 0 become relative to its end
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
+    }
+    if (r8 == 7) {      // 2^(sub-block total) per channel, once for the CTA
+      *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
+      *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
+    }
+  }
+  __syncthreads();      // every thread holds its share of the tiles; sums of squares and sub-block totals are complete
+
+  // ---- P2: decayed operands over the staging area, record parts that are final now straight to global memory ------
+  {
+    if (sb == 0 && r8 == 0) {
+      const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
+      const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
+      float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
+      *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
+      *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
+    }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;
+      const int off = core_off(row, 8 * j, kD);
+      *reinterpret_cast<uint4*>(smem + kSmX + 24576 + off) = vw[hf];       // v goes on to the products as it is
+      const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
+      const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
+      const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
+      const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
+      // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
+      const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
+      const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
+      __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
+        const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
+        const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
+        const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
+        const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
+        const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
+        const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
+        kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
+        qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
+        kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
+        qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
+        kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
+      }
+      auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
+        return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
+                          *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
+      };
+      *reinterpret_cast<uint4*>(smem + kSmX + off) = as_u4(kpm);
+      *reinterpret_cast<uint4*>(smem + kSmX + 8192 + off) = as_u4(qpm);
+      *reinterpret_cast<uint4*>(smem + kSmX + 16384 + off) = as_u4(kmm);
+      st_global_16(rec_dst + kRecQP + off, as_u4(qp));
+      st_global_16(rec_dst + kRecKR + off, as_u4(kr));
+    }
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+
+  // ---- first products [A; M] = [KPm; QPm] KMm^T (rows 64-127 of the A operand are KMm and VC: lanes nobody reads) --
+  if (tid == 0 && !failed) {
+    constexpr uint32_t idesc1 = umma_idesc_bf16(128, 32, 0, 0);
+    tc_fence_after();
+    const uint64_t a = umma_desc(sbase + kSmX, 128, 2048);
+    const uint64_t b = umma_desc(sbase + kSmX + 16384, 128, 2048);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      umma_ss(tmem + kColD1, a + i * 16, b + i * 16, idesc1, i > 0);
+      umma_ss(tmem + kColD1 + 32, a + (4 + i) * 16, b + (4 + i) * 16, idesc1, i > 0);
+    }
+    umma_commit(bar(B_D1));
+  }
+  if (warp == 0) {
+    // ---- T = (I + A)^-1 and TB^T on one warp -------------------------------------------------------------------------
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_D1), 0, abort_flag));
+    if (ok) {
+      tc_fence_after();
+      const float bi = s_beta[lane];
+      {
+        uint32_t a0[32], a1[32];
+        tmem_ld32(tmem + kColD1, a0);
+        tmem_ld32(tmem + kColD1 + 32, a1);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          float4 r;
+          r.x = (4 * q4 + 0 < lane) ? (__uint_as_float(a0[4 * q4 + 0]) + __uint_as_float(a1[4 * q4 + 0])) * bi : 0.f;
+          r.y = (4 * q4 + 1 < lane) ? (__uint_as_float(a0[4 * q4 + 1]) + __uint_as_float(a1[4 * q4 + 1])) * bi : 0.f;
+          r.z = (4 * q4 + 2 < lane) ? (__uint_as_float(a0[4 * q4 + 2]) + __uint_as_float(a1[4 * q4 + 2])) * bi : 0.f;
+          r.w = (4 * q4 + 3 < lane) ? (__uint_as_float(a0[4 * q4 + 3]) + __uint_as_float(a1[4 * q4 + 3])) * bi : 0.f;
+          *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
+        }
+      }
+      __syncwarp();
+      {
+        // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
+        const int b = lane >> 4, c = lane & 15;
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            if (4 * q4 < i) {
+              const float4 a4 = *reinterpret_cast<const float4*>(sA + (b * 16 + i) * kLdA + b * 16 + 4 * q4);
+              part[q4] = fmaf(a4.x, x[4 * q4], part[q4]);
+              part[q4] = fmaf(a4.y, x[4 * q4 + 1], part[q4]);
+              part[q4] = fmaf(a4.z, x[4 * q4 + 2], part[q4]);
+              part[q4] = fmaf(a4.w, x[4 * q4 + 3], part[q4]);
+            }
+          }
+          x[i] = ((i == c) ? 1.f : 0.f) - ((part[0] + part[1]) + (part[2] + part[3]));
+          sT[(b * 16 + i) * kLdA + b * 16 + c] = x[i];
+        }
+      }
+      __syncwarp();
+      {
+        // T_10 = -T_11 (A_10 T_00): two 16x16x16 products in tf32 on mma.sync, fp32 accumulation
+        const int g = lane >> 2, t4 = lane & 3;
+        auto small_product = [&](const float* A, const float* B, float* D, float sign) {
+          float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            const int k0 = 8 * ks;
+            const uint32_t f0 = to_tf32(A[g * kLdA + k0 + t4]), f1 = to_tf32(A[(g + 8) * kLdA + k0 + t4]);
+            const uint32_t f2 = to_tf32(A[g * kLdA + k0 + t4 + 4]), f3 = to_tf32(A[(g + 8) * kLdA + k0 + t4 + 4]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+              mma_tf32_1688(acc[nt], f0, f1, f2, f3, to_tf32(B[(k0 + t4) * kLdA + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLdA + 8 * nt + g]));
+          }
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            *reinterpret_cast<float2*>(D + g * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+            *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+          }
+        };
+        small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
+        __syncwarp();
+        small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
+      }
+      __syncwarp();
+      {
+        // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c (zero above the diagonal), bf16
+        uint8_t* row = smem + kSmTbt + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i0 = 8 * cb + 2 * e;
+            const float v0 = (i0 >= lane) ? sT[i0 * kLdA + lane] * bi : 0.f;
+            const float v1 = (i0 + 1 >= lane) ? sT[(i0 + 1) * kLdA + lane] * bi : 0.f;
+            w[e] = pack_bf16(v0, v1);
+          }
+          *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+    } else {
+      failed = true;
+    }
+  } else if (warp == 1) {
+    // ---- tril(q+ k-^T) -> MQK ------------------------------------------------------------------------------------------
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_D1), 0, abort_flag));
+    if (ok) {
+      tc_fence_after();
+      uint32_t a0[32], a1[32];
+      tmem_ld32(tmem + (32u << 16) + kColD1, a0);
+      tmem_ld32(tmem + (32u << 16) + kColD1 + 32, a1);
+      tmem_wait_ld();
+      uint8_t* row = smem + kSmMqk + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = 8 * cb + 2 * e;
+          const float v0 = (c <= lane) ? __uint_as_float(a0[c]) + __uint_as_float(a1[c]) : 0.f;
+          const float v1 = (c + 1 <= lane) ? __uint_as_float(a0[c + 1]) + __uint_as_float(a1[c + 1]) : 0.f;
+          w[e] = pack_bf16(v0, v1);
+        }
+        *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();
+    } else {
+      failed = true;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- second products (w')^T = KPm^T TB^T, (u')^T = VC^T TB^T -----------------------------------------------------------
+  if (tid == 0 && !failed && *abort_flag <= 0) {
+    constexpr uint32_t idesc2 = umma_idesc_bf16(128, 32, 1, 1);
+    tc_fence_after();
+    const uint64_t ak = umma_desc(sbase + kSmX, 2048, 128), av = umma_desc(sbase + kSmX + 24576, 2048, 128);
+    const uint64_t bt = umma_desc(sbase + kSmTbt, 512, 128);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      umma_ss(tmem + kColD2, ak + ks * 256, bt + ks * 64, idesc2, ks != 0);
+      umma_ss(tmem + kColD2 + 32, av + ks * 256, bt + ks * 64, idesc2, ks != 0);
+    }
+    umma_commit(bar(B_D2));
+  }
+  {
+    // ---- output: warps 0-3 turn (w')^T into WP (over the QPm region), warps 4-7 (u')^T into UP (over the KMm region) ---
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_D2), 0, abort_flag));
+    const int q = warp & 3;
+    const uint32_t tq = tmem + (static_cast<uint32_t>(q * 32) << 16) + kColD2;
+    if (!ok) {
+      failed = true;
+    } else if (warp < 4) {
+      tc_fence_after();
+      const uint32_t wp = sbase + kSmX + 8192;
+      const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t f[16];
+        tmem_ld_16x256b_x4(tq + (static_cast<uint32_t>(16 * half) << 16), f);
+        const int k0 = 32 * q + 16 * half;
+        const float ca = s_ex[k0 + (lane >> 2)], cb = s_ex[k0 + 8 + (lane >> 2)];      // back from "relative to the sub-block boundary"
+        tmem_wait_ld();
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp) {
+          uint32_t w[4];
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const int jt = 2 * jp + jj;
+            w[2 * jj] = pack_bf16(__uint_as_float(f[4 * jt]) * ca, __uint_as_float(f[4 * jt + 1]) * ca);
+            w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * jt + 2]) * cb, __uint_as_float(f[4 * jt + 3]) * cb);
+          }
+          const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
+          stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
+        }
+      }
+    } else {
+      tc_fence_after();
+      uint32_t u[32];
+      tmem_ld32(tq + 32, u);
+      tmem_wait_ld();
+      const int v = 32 * q + lane;
+      uint8_t* row = smem + kSmX + 16384 + (v >> 3) * 512 + (v & 7) * 16;
+#pragma unroll
+      for (int cb = 0; cb < 4; ++cb)
+        *reinterpret_cast<uint4*>(row + cb * 128) =
+            make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
+                       pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
+    }
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && !failed && *abort_flag <= 0) {
+    bulk_s2g(rec_dst + kRecMQK, sbase + kSmMqk, 2048);
+    bulk_s2g(rec_dst + kRecWP, sbase + kSmX + 8192, 8192);
+    bulk_s2g(rec_dst + kRecUP, sbase + kSmX + 16384, 8192);
+    bulk_commit();
+    bulk_wait_read0();
+  }
+  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace prep_tc4
+
+cudaError_t launch_prepare_tc4(const PrepParams& p, cudaStream_t stream) {
+  if (p.total_chunks == 0 || p.H == 0 || p.T_total == 0) return cudaSuccess;
+  CUtensorMap tq, tk, tg, tv;
+  if (!prep_tc::make_map(&tq, p.q, p.T_total, p.H) || !prep_tc::make_map(&tk, p.k, p.T_total, p.H) ||
+      !prep_tc::make_map(&tg, p.g, p.T_total, p.H) || !prep_tc::make_map(&tv, p.v, p.T_total, p.H))
+    return cudaErrorInvalidValue;
+  static SmemOptIn opt_in;
+  cudaError_t e = opt_in.ensure(prep_tc4::prepare_tc4_kernel, prep_tc4::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const unsigned grid = static_cast<unsigned>(p.total_chunks) * static_cast<unsigned>(p.H);
+  prep_tc4::prepare_tc4_kernel<<<grid, prep_tc4::kThreads, prep_tc4::kSmemBytes, stream>>>(tq, tk, tg, tv, p);
+  return cudaGetLastError();
+}
+
 #ifdef FKDA_TUNING
 void set_prepare_trace(long long* buf) { prep_tc::g_trace = buf; }
 #endif

@@ -51,6 +51,8 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
  * with accumulators in tensor memory, one persistent warp-specialised CTA per SM) instead of the default one
  * (mma.sync products, four CTAs per SM), which is the faster of the two today.  Same operand records. */
 #define FKDA_FLAG_PREPARE_TCGEN05 0x80u
+/* The same on the persistent, warp-specialised form of that kernel (one CTA per SM). */
+#define FKDA_FLAG_PREPARE_TCGEN05_PERSISTENT 0x10000u
 /* Cut every sequence of the batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
  * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster

@@ -47,12 +47,12 @@ def test_prologue_kernel():
     assert (bact.cpu().double() - br).abs().max() < 1e-3
 
 
-@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05", "tcgen05_persistent"])
 @pytest.mark.parametrize("case", ["fixed", "varlen", "strong_decay"])
 def test_prepare_records_match_fp64_operands(case, kernel):
     """Operand records of both token-parallel kernels (the default one and the TMA + tcgen05 one) against the fp64
     chunk operands of the oracle."""
-    flags = F.FLAG_PREPARE_TCGEN05 if kernel == "tcgen05" else 0
+    flags = {"mma_sync": 0, "tcgen05": F.FLAG_PREPARE_TCGEN05, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT}[kernel]
     if case == "fixed":
         w = Workload("f", H=2, B=2, T=80, seed=11)
     elif case == "varlen":
