@@ -805,6 +805,7 @@ using prep_tc::st_global_16;
 
 constexpr int kThreads = 256;
 constexpr uint32_t kTmemCols = 128;
+constexpr unsigned kGridY = 32768;        // chunks of a packed batch per grid row of the y dimension
 constexpr uint32_t kColD1 = 0;            // 2 accumulators x 32 columns: rows 0-31 A, 32-63 M
 constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
 // shared memory (bytes).  [0, 32768): the staged q, k, g, v tiles (two [32 tok][128 B] swizzled halves each), then, once
@@ -826,9 +827,23 @@ static_assert(kSmMisc + 16 <= kSmemBytes, "shared memory plan");
 static_assert(4 * (kSmemBytes + 1024) <= 227 * 1024, "four CTAs per SM");
 enum { B_LOAD = 0, B_D1 = 1, B_D2 = 2 };
 
+// Phase timeline of 32 CTAs from the middle of the grid (tuning builds only): entry [cta * 16 + event] = clock64().
+#ifdef FKDA_TUNING
+#define P4TRACE(ev)                                                                                                    \
+  do {                                                                                                                 \
+    const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                              \
+    if (trace != nullptr && lin_ >= 16384u && lin_ < 16416u) trace[(lin_ - 16384u) * 16 + (ev)] = clock64();           \
+  } while (0)
+#else
+#define P4TRACE(ev) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(kThreads, 4)
 prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p) {
+                   const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p,
+                   long long* trace) {
+  (void)trace;
+  if (threadIdx.x == 0) P4TRACE(0);
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -842,12 +857,19 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   float* sT = reinterpret_cast<float*>(smem + kSmT);
   float* sX = sA + 16;
 
-  // consecutive CTAs take consecutive heads of the same chunk
-  const int h = static_cast<int>(blockIdx.x % static_cast<unsigned>(p.H));
-  const int gc = static_cast<int>(blockIdx.x / static_cast<unsigned>(p.H));
+  // grid: x = head (consecutive CTAs take consecutive heads of the same chunk: adjacent rows in memory); equal
+  // lengths: y = chunk of the sequence, z = sequence; cu_seqlens: y + kGridY z = chunk of the packed batch.  No division
+  // on the way to the first load: everything up to the set-up barrier is latency that every item pays.
+  const int h = static_cast<int>(blockIdx.x);
+  const float a_log = __ldg(p.A_log + h);
+  const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
+  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
+  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+  int gc;
   int64_t t0;
   int len;
   if (p.cu_seqlens != nullptr) {
+    gc = static_cast<int>(blockIdx.y + blockIdx.z * kGridY);
     if (gc >= p.chunk_prefix[p.N]) return;
     int lo = 0, hi = p.N - 1;
     while (lo < hi) {
@@ -861,12 +883,15 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int64_t rem = eos - t0;
     len = rem < kChunk ? static_cast<int>(rem) : kChunk;
   } else {
-    const int cps = static_cast<int>((p.T + kChunk - 1) / kChunk);
-    const int n = gc / cps, lc = gc - n * cps;
+    const int lc = static_cast<int>(blockIdx.y), n = static_cast<int>(blockIdx.z);
+    gc = n * static_cast<int>(gridDim.y) + lc;
     t0 = static_cast<int64_t>(n) * p.T + static_cast<int64_t>(lc) * kChunk;
     const int64_t rem = p.T - static_cast<int64_t>(lc) * kChunk;
     len = rem < kChunk ? static_cast<int>(rem) : kChunk;
   }
+  // sigmoid(beta) of the 32 tokens: the load is issued before the serial set-up below, on a warp that has none of it
+  float beta_raw = 0.f;
+  if (warp == 2 && lane < len) beta_raw = __bfloat162float(p.beta[static_cast<size_t>(t0 + lane) * p.H + h]);
   if ((sbase & 1023u) != 0u) {       // the swizzled tiles need this alignment: report instead of computing garbage
     if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
     return;
@@ -874,7 +899,6 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + gc) * kRecBytes;
 
   if (tid == 0) {
-    *abort_flag = 0;
     mbar_init(bar(B_LOAD), 1);
     mbar_init(bar(B_D1), 1);
     mbar_init(bar(B_D2), 1);
@@ -890,30 +914,30 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     tma_load_3d(sbase + kSmX + 20480, &tm_g, 64, h, tc, full);
     tma_load_3d(sbase + kSmX + 24576, &tm_v, 0, h, tc, full);
     tma_load_3d(sbase + kSmX + 28672, &tm_v, 64, h, tc, full);
+    P4TRACE(14);
   }
   if (warp == 1) {
+    if (lane == 0) *abort_flag = 0;
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
   // thread -> two (row, 8-column) pieces of one sub-block, as in the default kernel
-  const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
   const int row0 = sb * 16 + r8, row1 = row0 + 8;
   const int hh = j >> 3, cj = j & 7;
-  const float a_log = __ldg(p.A_log + h);
-  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
-  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
-  if (tid < kChunk) s_beta[tid] = tid < len ? sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(t0 + tid) * p.H + h])) : 0.f;
+  if (warp == 2) s_beta[lane] = lane < len ? sigmoid_fast(beta_raw) : 0.f;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   bool failed = false;
+  if (tid == 0) P4TRACE(13);
 
   // ---- P1: staged tiles -> registers, partial sums of squares, gate and its running sum ----------------------------
   uint4 qw[2], kw[2], vw[2];
   float G[2][8];
   {
-    if (!mbar_wait(bar(B_LOAD), 0, abort_flag)) failed = true;
+    if (!mbar_wait_parked(bar(B_LOAD), 0, abort_flag)) failed = true;
+    if (tid == 0) P4TRACE(1);
     const uint8_t* stg = smem + kSmX + hh * 4096;
     const int sw = (cj ^ r8) << 4;
     const bool valid0 = row0 < len, valid1 = row1 < len;
@@ -978,6 +1002,7 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   }
   __syncthreads();      // every thread holds its share of the tiles; sums of squares and sub-block totals are complete
+  if (tid == 0) P4TRACE(2);
 
   // ---- P2: decayed operands over the staging area, record parts that are final now straight to global memory ------
   {
@@ -1029,6 +1054,7 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
   fence_proxy_async_smem();
   __syncthreads();
+  if (tid == 0) P4TRACE(3);
 
   // ---- first products [A; M] = [KPm; QPm] KMm^T (rows 64-127 of the A operand are KMm and VC: lanes nobody reads) --
   if (tid == 0 && !failed) {
@@ -1042,12 +1068,14 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       umma_ss(tmem + kColD1 + 32, a + (4 + i) * 16, b + (4 + i) * 16, idesc1, i > 0);
     }
     umma_commit(bar(B_D1));
+    P4TRACE(4);
   }
   if (warp == 0) {
     // ---- T = (I + A)^-1 and TB^T on one warp -------------------------------------------------------------------------
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_D1), 0, abort_flag));
+    const bool ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1), 0, abort_flag));
     if (ok) {
       tc_fence_after();
+      if (lane == 0) P4TRACE(5);
       const float bi = s_beta[lane];
       {
         uint32_t a0[32], a1[32];
@@ -1065,6 +1093,7 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
       __syncwarp();
+      if (lane == 0) P4TRACE(6);
       {
         // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
         const int b = lane >> 4, c = lane & 15;
@@ -1109,6 +1138,7 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
           }
         };
+        if (lane == 0) P4TRACE(7);
         small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
         __syncwarp();
         small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
@@ -1131,12 +1161,13 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
       fence_proxy_async_smem();
+      if (lane == 0) P4TRACE(8);
     } else {
       failed = true;
     }
   } else if (warp == 1) {
     // ---- tril(q+ k-^T) -> MQK ------------------------------------------------------------------------------------------
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_D1), 0, abort_flag));
+    const bool ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1), 0, abort_flag));
     if (ok) {
       tc_fence_after();
       uint32_t a0[32], a1[32];
@@ -1176,12 +1207,14 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       umma_ss(tmem + kColD2 + 32, av + ks * 256, bt + ks * 64, idesc2, ks != 0);
     }
     umma_commit(bar(B_D2));
+    P4TRACE(9);
   }
   {
     // ---- output: warps 0-3 turn (w')^T into WP (over the QPm region), warps 4-7 (u')^T into UP (over the KMm region) ---
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_D2), 0, abort_flag));
+    const bool ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(B_D2), 0, abort_flag));
     const int q = warp & 3;
     const uint32_t tq = tmem + (static_cast<uint32_t>(q * 32) << 16) + kColD2;
+    if (tid == 0) P4TRACE(10);
     if (!ok) {
       failed = true;
     } else if (warp < 4) {
@@ -1225,12 +1258,14 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) P4TRACE(11);
   if (tid == 0 && !failed && *abort_flag <= 0) {
     bulk_s2g(rec_dst + kRecMQK, sbase + kSmMqk, 2048);
     bulk_s2g(rec_dst + kRecWP, sbase + kSmX + 8192, 8192);
     bulk_s2g(rec_dst + kRecUP, sbase + kSmX + 16384, 8192);
     bulk_commit();
     bulk_wait_read0();
+    P4TRACE(12);
   }
   if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
   if (warp == 1) {
@@ -1241,6 +1276,14 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 }  // namespace prep_tc4
 
+// whether the grid of the kernel above can hold the call (x = heads; equal lengths: y = chunks of a sequence,
+// z = sequences; packed batch: y + kGridY z = chunk)
+bool prepare_tc4_applicable(const PrepParams& p) {
+  if (p.H > 65535) return false;
+  if (p.cu_seqlens == nullptr) return (p.T + kChunk - 1) / kChunk <= 65535 && p.N <= 65535;
+  return (static_cast<long long>(p.total_chunks) + prep_tc4::kGridY - 1) / prep_tc4::kGridY <= 65535;
+}
+
 cudaError_t launch_prepare_tc4(const PrepParams& p, cudaStream_t stream) {
   if (p.total_chunks == 0 || p.H == 0 || p.T_total == 0) return cudaSuccess;
   CUtensorMap tq, tk, tg, tv;
@@ -1250,8 +1293,20 @@ cudaError_t launch_prepare_tc4(const PrepParams& p, cudaStream_t stream) {
   static SmemOptIn opt_in;
   cudaError_t e = opt_in.ensure(prep_tc4::prepare_tc4_kernel, prep_tc4::kSmemBytes);
   if (e != cudaSuccess) return e;
-  const unsigned grid = static_cast<unsigned>(p.total_chunks) * static_cast<unsigned>(p.H);
-  prep_tc4::prepare_tc4_kernel<<<grid, prep_tc4::kThreads, prep_tc4::kSmemBytes, stream>>>(tq, tk, tg, tv, p);
+  if (!prepare_tc4_applicable(p)) return cudaErrorInvalidConfiguration;
+  dim3 grid;
+  if (p.cu_seqlens == nullptr) {
+    grid = dim3(static_cast<unsigned>(p.H), static_cast<unsigned>((p.T + kChunk - 1) / kChunk), static_cast<unsigned>(p.N));
+  } else {
+    const unsigned chunks = static_cast<unsigned>(p.total_chunks);
+    grid = dim3(static_cast<unsigned>(p.H), chunks < prep_tc4::kGridY ? chunks : prep_tc4::kGridY, (chunks + prep_tc4::kGridY - 1) / prep_tc4::kGridY);
+  }
+#ifdef FKDA_TUNING
+  long long* trace = prep_tc::g_trace;
+#else
+  long long* trace = nullptr;
+#endif
+  prep_tc4::prepare_tc4_kernel<<<grid, prep_tc4::kThreads, prep_tc4::kSmemBytes, stream>>>(tq, tk, tg, tv, p, trace);
   return cudaGetLastError();
 }
 

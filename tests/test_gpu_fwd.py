@@ -73,20 +73,36 @@ def test_golden_cases(name, flags):
     assert d_out <= (1e-2 if big else OUT_MAX_ABS) and d_st <= STATE_REL
 
 
+OTHER_PREPARE_KERNELS = {"mma_sync": F.FLAG_PREPARE_MMA_SYNC, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT}
+
+
+@pytest.mark.parametrize("kernel", list(OTHER_PREPARE_KERNELS))
 @pytest.mark.parametrize("name", golden_names())
-def test_golden_cases_on_the_tma_tcgen05_token_parallel_kernel(name):
-    """The token-parallel stage on its TMA + tcgen05 kernel (flag FLAG_PREPARE_TCGEN05): same golden cases."""
+def test_golden_cases_on_the_other_token_parallel_kernels(name, kernel):
+    """The token-parallel stage on the mma.sync kernel and on the persistent form of the TMA + tcgen05 kernel (the
+    default is the four-CTAs-per-SM TMA + tcgen05 kernel): same golden cases."""
     x, ref_out, ref_fin = load_golden(name)
     fin_dtype = None if ref_fin is None else ref_fin.dtype
-    out, fin = run_gpu(x, fin_dtype, F.FLAG_PREPARE_TCGEN05)
+    out, fin = run_gpu(x, fin_dtype, OTHER_PREPARE_KERNELS[kernel] | F.FLAG_NO_FUSED_SHORT)
     big = x["initial_state"] is not None and x["initial_state"].float().abs().max() > 100
-    check_against_f64(x, out, fin, f"{name}[tcgen05 prepare]", big_state=big)
+    check_against_f64(x, out, fin, f"{name}[{kernel} prepare]", big_state=big)
 
 
+def test_required_tcgen05_kernel_is_the_default_one():
+    """FLAG_PREPARE_TCGEN05 only turns the default choice into a requirement: same bits."""
+    x = make_inputs(Workload("req", H=4, B=2, T=300, state_in="fp32", state_out="fp32", seed=65))
+    o0, s0 = run_gpu(x, torch.float32)
+    o1, s1 = run_gpu(x, torch.float32, F.FLAG_PREPARE_TCGEN05)
+    assert torch.equal(o0.view(torch.int16), o1.view(torch.int16)) and torch.equal(s0, s1)
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_persistent"])
 @pytest.mark.parametrize("case", ["fixed_tails", "varlen_ragged", "many_items", "long_repeat"])
-def test_tma_tcgen05_token_parallel_kernel_shapes(case):
-    """Shapes that stress the persistent kernel's pipeline: ragged last chunks, many short sequences (items of every
-    length), more items than one pass of the CTAs holds, and repeated calls that must be bit-reproducible."""
+def test_tma_tcgen05_token_parallel_kernel_shapes(case, kernel):
+    """Shapes that stress the TMA + tcgen05 kernels: ragged last chunks, many short sequences (items of every
+    length), more items than one pass of the CTAs holds, and repeated calls that must be bit-reproducible; each
+    against the fp64 oracle and against the mma.sync kernel."""
+    tc_flag = F.FLAG_PREPARE_TCGEN05 if kernel == "tcgen05" else F.FLAG_PREPARE_TCGEN05_PERSISTENT
     if case == "fixed_tails":
         w = Workload("tc1", H=3, B=5, T=32 * 3 + 17, state_in="fp32", state_out="fp32", state_std=0.5, seed=61)
     elif case == "varlen_ragged":
@@ -97,13 +113,13 @@ def test_tma_tcgen05_token_parallel_kernel_shapes(case):
         w = Workload("tc4", H=16, B=2, T=1024, state_in="fp32", state_out="fp32", seed=64)
     x = make_inputs(w)
     dt = torch.bfloat16 if w.state_in == "bf16" else torch.float32
-    out, fin = run_gpu(x, dt, F.FLAG_PREPARE_TCGEN05)
-    check_against_f64(x, out, fin, f"tcgen05 prepare, {case}")
-    o0, s0 = run_gpu(x, dt)
+    out, fin = run_gpu(x, dt, tc_flag)
+    check_against_f64(x, out, fin, f"{kernel} prepare, {case}")
+    o0, s0 = run_gpu(x, dt, F.FLAG_PREPARE_MMA_SYNC)
     assert max_abs(out, o0) <= 1e-2 and rel_fro(fin, s0) <= (2e-2 if dt == torch.bfloat16 else 5e-3)
     if case == "long_repeat":
         for _ in range(4):
-            o2, s2 = run_gpu(x, dt, F.FLAG_PREPARE_TCGEN05)
+            o2, s2 = run_gpu(x, dt, tc_flag)
             assert torch.equal(o2.view(torch.int16), out.view(torch.int16)) and torch.equal(s2, fin)
 
 

@@ -85,7 +85,8 @@ FORMS = {
     "segmented": F.FLAG_SCAN_LOOKAHEAD | F.FLAG_SEGMENTS(3),
     "segmented_compact": F.FLAG_SCAN_PLAIN | F.FLAG_SEGMENTS(3),
     "simt": F.FLAG_SCAN_SIMT,
-    "tcgen05_prepare": F.FLAG_PREPARE_TCGEN05,
+    "mma_sync_prepare": F.FLAG_PREPARE_MMA_SYNC,
+    "tcgen05_persistent_prepare": F.FLAG_PREPARE_TCGEN05_PERSISTENT,
     "reference_rounding": F.FLAG_REFERENCE_ROUNDING,
 }
 

@@ -50,9 +50,9 @@ def test_prologue_kernel():
 @pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05", "tcgen05_persistent"])
 @pytest.mark.parametrize("case", ["fixed", "varlen", "strong_decay"])
 def test_prepare_records_match_fp64_operands(case, kernel):
-    """Operand records of both token-parallel kernels (the default one and the TMA + tcgen05 one) against the fp64
-    chunk operands of the oracle."""
-    flags = {"mma_sync": 0, "tcgen05": F.FLAG_PREPARE_TCGEN05, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT}[kernel]
+    """Operand records of the three token-parallel kernels (the default TMA + tcgen05 one, its persistent form and
+    the mma.sync one) against the fp64 chunk operands of the oracle."""
+    flags = {"mma_sync": F.FLAG_PREPARE_MMA_SYNC, "tcgen05": F.FLAG_PREPARE_TCGEN05, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT}[kernel]
     if case == "fixed":
         w = Workload("f", H=2, B=2, T=80, seed=11)
     elif case == "varlen":
