@@ -103,6 +103,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
       "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
       : "memory");
 }
+// the same box into the L2 only (no shared-memory destination, nothing to wait for)
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0),
+               "r"(c1), "r"(c2)
+               : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -1275,6 +1281,588 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 }
 
 }  // namespace prep_tc4
+
+// =====================================================================================================================
+// The same stage as a short software pipeline inside each CTA: eight element warps that do every item's element-wise
+// work in lock step, and a ninth warp that owns the serial part (A from tensor memory, T = (I + A)^-1, TB^T, issue of the
+// second products) of the item the element warps have just left.  Three CTAs per SM, each a loop over items
+// blockIdx.x, blockIdx.x + gridDim.x, ...; two 32 KB operand buffers per CTA alternate between consecutive items.
+//
+//   element warps, iteration i:  wait tiles(i) | sums of squares, gate, running sums | barrier | decayed operands over the
+//                                tiles, QP / KR / E to the record | barrier | one thread: first products(i) -> D1[i & 1]
+//                                | then item i - 1: wait D2 | WP, UP over the dead QPm / KMm of its buffer, MQK | barrier |
+//                                one thread: bulk stores(i - 1), then the tile loads of item i + 1 into that buffer and an
+//                                L2 prefetch of item i + 2
+//   matrix warp, item i:         sigmoid(beta) | wait D1[i & 1] | A -> T -> TB^T in the dead QPm / KMm of buffer i & 1 |
+//                                second products(i) -> D2
+// Tensor memory: D1 twice (its M half is read one iteration later), D2 once (guarded by a "read" barrier).
+namespace prep_pipe {
+
+using prep_tc::tma_load_3d;
+using prep_tc::tma_prefetch_3d;
+using prep_tc::tmem_ld_16x256b_x4;
+using prep_tc::stsm_x4_trans;
+using prep_tc::st_global_16;
+
+constexpr int kElemThreads = 256;
+constexpr int kMatrixWarp = 8;
+constexpr int kThreads = 288;
+constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kColD1 = 0;            // 2 buffers x 32 columns: lanes 0-31 A, 32-63 M
+constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
+constexpr int kBufBytes = 32768;          // tiles q | k | g | v, then KPm | QPm | KMm | VC (8192 each)
+constexpr int kSmBuf = 0;
+constexpr int kLdA = 36;
+constexpr int kOffA = 8192;               // inside a buffer after the first products: fp32 A [32][36] over QPm
+constexpr int kOffT = 16384;              // fp32 T [32][36] over KMm
+constexpr int kOffTbt = 16384 + 6144;     // TB^T bf16 [32][32], core layout
+constexpr int kSmMqk = 2 * kBufBytes;     // MQK bf16 [32][32] on its way to the record
+constexpr int kSmSsq = kSmMqk + 2048;     // [2][32][4] partial sums of squares
+constexpr int kSmEx = kSmSsq + 1024;      // 2 items x [2][128] 2^(sub-block total)
+constexpr int kSmInfo = kSmEx + 2048;     // 4 items x {t0, len, h, gc}
+constexpr int kSmBars = kSmInfo + 128;
+constexpr int kSmMisc = kSmBars + 64;
+constexpr int kSmemBytes = 70 * 1024;
+static_assert(kSmMisc + 16 <= kSmemBytes, "shared memory plan");
+static_assert(3 * (kSmemBytes + 1024) <= 227 * 1024, "three CTAs per SM");
+static_assert(32 * kLdA * 4 <= 6144, "A and T fit before TB^T");
+enum { B_LOAD = 0 /*[2]*/, B_D1 = 2 /*[2]*/, B_D2 = 4, B_D2_READ = 5, B_COUNT = 6 };
+
+struct ItemInfo {
+  long long t0;
+  int len, h, gc, pad[3];
+};
+static_assert(sizeof(ItemInfo) == 32, "item info");
+
+__device__ __forceinline__ ItemInfo decode_item(const PrepParams& p, unsigned item) {
+  ItemInfo r;
+  r.h = static_cast<int>(item % static_cast<unsigned>(p.H));
+  r.gc = static_cast<int>(item / static_cast<unsigned>(p.H));
+  r.pad[0] = r.pad[1] = r.pad[2] = 0;
+  if (p.cu_seqlens != nullptr) {
+    int lo = 0, hi = p.N - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.chunk_prefix[mid] <= r.gc) lo = mid; else hi = mid - 1;
+    }
+    long long bos = p.cu_seqlens[lo], eos = p.cu_seqlens[lo + 1];
+    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
+    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
+    r.t0 = bos + static_cast<long long>(r.gc - p.chunk_prefix[lo]) * kChunk;
+    const long long rem = eos - r.t0;
+    r.len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  } else {
+    const unsigned cps = static_cast<unsigned>((p.T + kChunk - 1) / kChunk);
+    const unsigned n = static_cast<unsigned>(r.gc) / cps, lc = static_cast<unsigned>(r.gc) - n * cps;
+    r.t0 = static_cast<long long>(n) * p.T + static_cast<long long>(lc) * kChunk;
+    const long long rem = p.T - static_cast<long long>(lc) * kChunk;
+    r.len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  }
+  return r;
+}
+
+// rendezvous of the element warps; returns whether any of them has given up
+__device__ __forceinline__ bool elem_barrier_any(bool failed) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(any)
+      : "r"(static_cast<uint32_t>(failed))
+      : "memory");
+  return any != 0;
+}
+
+__global__ void __launch_bounds__(kThreads, 3)
+prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p,
+                    long long* trace) {
+  (void)trace;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
+  auto info_of = [&](int it) { return reinterpret_cast<ItemInfo*>(smem + kSmInfo + (it & 3) * 32); };
+  float* s_ssq = reinterpret_cast<float*>(smem + kSmSsq);
+
+  const unsigned total_items = static_cast<unsigned>(p.cu_seqlens != nullptr ? p.chunk_prefix[p.N] : p.total_chunks) * static_cast<unsigned>(p.H);
+  if (blockIdx.x >= total_items) return;
+  const int n_it = static_cast<int>((total_items - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  if ((sbase & 1023u) != 0u) {       // the swizzled tiles need this alignment: report instead of computing garbage
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+    return;
+  }
+
+  // the tile loads of one item into one buffer (one thread)
+  auto issue_load = [&](int it) {
+    const ItemInfo* f = info_of(it);
+    const uint32_t full = bar(B_LOAD + (it & 1));
+    const uint32_t dst = sbase + kSmBuf + (it & 1) * kBufBytes;
+    const int tc = static_cast<int>(f->t0), h = f->h;
+    mbar_arrive_expect_tx(full, kBufBytes);
+    tma_load_3d(dst, &tm_q, 0, h, tc, full);
+    tma_load_3d(dst + 4096, &tm_q, 64, h, tc, full);
+    tma_load_3d(dst + 8192, &tm_k, 0, h, tc, full);
+    tma_load_3d(dst + 12288, &tm_k, 64, h, tc, full);
+    tma_load_3d(dst + 16384, &tm_g, 0, h, tc, full);
+    tma_load_3d(dst + 20480, &tm_g, 64, h, tc, full);
+    tma_load_3d(dst + 24576, &tm_v, 0, h, tc, full);
+    tma_load_3d(dst + 28672, &tm_v, 64, h, tc, full);
+  };
+  // decode item `it` into its info slot and ask the L2 for its tiles (one thread, an iteration ahead of the load)
+  auto decode_and_prefetch = [&](int it) {
+    const ItemInfo f = decode_item(p, blockIdx.x + static_cast<unsigned>(it) * gridDim.x);
+    *info_of(it) = f;
+    const int tc = static_cast<int>(f.t0);
+    tma_prefetch_3d(&tm_q, 0, f.h, tc);
+    tma_prefetch_3d(&tm_q, 64, f.h, tc);
+    tma_prefetch_3d(&tm_k, 0, f.h, tc);
+    tma_prefetch_3d(&tm_k, 64, f.h, tc);
+    tma_prefetch_3d(&tm_g, 0, f.h, tc);
+    tma_prefetch_3d(&tm_g, 64, f.h, tc);
+    tma_prefetch_3d(&tm_v, 0, f.h, tc);
+    tma_prefetch_3d(&tm_v, 64, f.h, tc);
+  };
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(B_LOAD), 1);
+    mbar_init(bar(B_LOAD + 1), 1);
+    mbar_init(bar(B_D1), 1);
+    mbar_init(bar(B_D1 + 1), 1);
+    mbar_init(bar(B_D2), 1);
+    mbar_init(bar(B_D2_READ), 8);
+    fence_mbar_init();
+    *info_of(0) = decode_item(p, blockIdx.x);
+    issue_load(0);
+    if (n_it > 1) {
+      *info_of(1) = decode_item(p, blockIdx.x + gridDim.x);
+      issue_load(1);
+    }
+    if (n_it > 2) decode_and_prefetch(2);
+  }
+  if (warp == kMatrixWarp) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool failed = false;
+
+  if (warp == kMatrixWarp) {
+    // ===== matrix warp ====================================================================================================
+    for (int it = 0; it < n_it; ++it) {
+      const int b = it & 1;
+      uint8_t* buf = smem + kSmBuf + b * kBufBytes;
+      float* sA = reinterpret_cast<float*>(buf + kOffA);
+      float* sT = reinterpret_cast<float*>(buf + kOffT);
+      float* sX = sA + 16;
+      // the load barrier of this item has an arrival by the thread that wrote the item's info: acquire it
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
+      const ItemInfo f = *info_of(it);
+      const float bi = lane < f.len ? sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(f.t0 + lane) * p.H + f.h])) : 0.f;
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
+      tc_fence_after();
+      {
+        uint32_t a0[32];
+        tmem_ld32(tmem + kColD1 + 32 * b, a0);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          float4 r;
+          r.x = (4 * q4 + 0 < lane) ? __uint_as_float(a0[4 * q4 + 0]) * bi : 0.f;
+          r.y = (4 * q4 + 1 < lane) ? __uint_as_float(a0[4 * q4 + 1]) * bi : 0.f;
+          r.z = (4 * q4 + 2 < lane) ? __uint_as_float(a0[4 * q4 + 2]) * bi : 0.f;
+          r.w = (4 * q4 + 3 < lane) ? __uint_as_float(a0[4 * q4 + 3]) * bi : 0.f;
+          *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
+        }
+      }
+      __syncwarp();
+      {
+        // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
+        const int bb = lane >> 4, c = lane & 15;
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            if (4 * q4 < i) {
+              const float4 a4 = *reinterpret_cast<const float4*>(sA + (bb * 16 + i) * kLdA + bb * 16 + 4 * q4);
+              part[q4] = fmaf(a4.x, x[4 * q4], part[q4]);
+              part[q4] = fmaf(a4.y, x[4 * q4 + 1], part[q4]);
+              part[q4] = fmaf(a4.z, x[4 * q4 + 2], part[q4]);
+              part[q4] = fmaf(a4.w, x[4 * q4 + 3], part[q4]);
+            }
+          }
+          x[i] = ((i == c) ? 1.f : 0.f) - ((part[0] + part[1]) + (part[2] + part[3]));
+          sT[(bb * 16 + i) * kLdA + bb * 16 + c] = x[i];
+        }
+      }
+      __syncwarp();
+      {
+        // T_10 = -T_11 (A_10 T_00): two 16x16x16 products in tf32 on mma.sync, fp32 accumulation
+        const int g = lane >> 2, t4 = lane & 3;
+        auto small_product = [&](const float* A, const float* B, float* D, float sign) {
+          float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            const int k0 = 8 * ks;
+            const uint32_t f0 = to_tf32(A[g * kLdA + k0 + t4]), f1 = to_tf32(A[(g + 8) * kLdA + k0 + t4]);
+            const uint32_t f2 = to_tf32(A[g * kLdA + k0 + t4 + 4]), f3 = to_tf32(A[(g + 8) * kLdA + k0 + t4 + 4]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+              mma_tf32_1688(acc[nt], f0, f1, f2, f3, to_tf32(B[(k0 + t4) * kLdA + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLdA + 8 * nt + g]));
+          }
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            *reinterpret_cast<float2*>(D + g * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+            *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+          }
+        };
+        small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
+        __syncwarp();
+        small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
+      }
+      __syncwarp();
+      {
+        // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c (zero above the diagonal), bf16
+        uint8_t* row = buf + kOffTbt + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i0 = 8 * cb + 2 * e;
+            const float v0 = (i0 >= lane) ? sT[i0 * kLdA + lane] * bi : 0.f;
+            const float v1 = (i0 + 1 >= lane) ? sT[(i0 + 1) * kLdA + lane] * bi : 0.f;
+            w[e] = pack_bf16(v0, v1);
+          }
+          *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      // D2 still holds the previous item until the element warps have read it
+      if (it >= 1 && !__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D2_READ), (it - 1) & 1, abort_flag))) { failed = true; break; }
+      if (lane == 0) {
+        constexpr uint32_t idesc2 = umma_idesc_bf16(128, 32, 1, 1);
+        tc_fence_after();
+        const uint32_t bs = sbase + kSmBuf + b * kBufBytes;
+        const uint64_t ak = umma_desc(bs, 2048, 128), av = umma_desc(bs + 24576, 2048, 128);
+        const uint64_t bt = umma_desc(bs + kOffTbt, 512, 128);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          umma_ss(tmem + kColD2, ak + ks * 256, bt + ks * 64, idesc2, ks != 0);
+          umma_ss(tmem + kColD2 + 32, av + ks * 256, bt + ks * 64, idesc2, ks != 0);
+        }
+        umma_commit(bar(B_D2));
+      }
+      __syncwarp();
+    }
+  } else {
+    // ===== element warps ==================================================================================================
+    const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
+    const int row0 = sb * 16 + r8, row1 = row0 + 8;
+    const int hh = j >> 3, cj = j & 7;
+    const int q = warp & 3;
+    int loads_issued = n_it > 1 ? 2 : 1;     // (thread 0)
+
+    // item jt (the previous iteration's): WP, UP, MQK out of tensor memory, then to the record; the thread that stores
+    // them goes on to load the item after next into the buffer this frees
+    auto output = [&](int jt) {
+      const int pb = jt & 1;
+      uint8_t* buf = smem + kSmBuf + pb * kBufBytes;
+      const float* s_ex = reinterpret_cast<const float*>(smem + kSmEx + pb * 1024);
+      const bool ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(B_D2), jt & 1, abort_flag));
+      if (!ok) {
+        failed = true;
+      } else {
+        tc_fence_after();
+        const uint32_t tq = tmem + (static_cast<uint32_t>(q * 32) << 16) + kColD2;
+        if (warp < 4) {
+          uint32_t f0[16], f1[16];
+          tmem_ld_16x256b_x4(tq, f0);
+          tmem_ld_16x256b_x4(tq + (16u << 16), f1);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_D2_READ));
+          const uint32_t wp = sbase + kSmBuf + pb * kBufBytes + 8192;
+          const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t(&f)[16] = half ? f1 : f0;
+            const int k0 = 32 * q + 16 * half;
+            const float ca = s_ex[k0 + (lane >> 2)], cb = s_ex[k0 + 8 + (lane >> 2)];      // back from "relative to the sub-block boundary"
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp) {
+              uint32_t w[4];
+#pragma unroll
+              for (int jj = 0; jj < 2; ++jj) {
+                const int jt4 = 2 * jp + jj;
+                w[2 * jj] = pack_bf16(__uint_as_float(f[4 * jt4]) * ca, __uint_as_float(f[4 * jt4 + 1]) * ca);
+                w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * jt4 + 2]) * cb, __uint_as_float(f[4 * jt4 + 3]) * cb);
+              }
+              const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
+              stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
+            }
+          }
+        } else {
+          uint32_t u[32];
+          tmem_ld32(tq + 32, u);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_D2_READ));
+          const int v = 32 * q + lane;
+          uint8_t* row = buf + 16384 + (v >> 3) * 512 + (v & 7) * 16;
+#pragma unroll
+          for (int cb = 0; cb < 4; ++cb)
+            *reinterpret_cast<uint4*>(row + cb * 128) =
+                make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
+                           pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
+          if (warp == 5) {
+            // tril(q+ k-^T) -> MQK (lanes 32-63 of D1; complete since before the second products were issued)
+            if (__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + pb), (jt >> 1) & 1, abort_flag))) {
+              tc_fence_after();
+              tmem_ld32(tmem + (32u << 16) + kColD1 + 32 * pb, u);
+              tmem_wait_ld();
+              tc_fence_before();
+              uint8_t* mrow = smem + kSmMqk + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+              for (int cb = 0; cb < 4; ++cb) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int c = 8 * cb + 2 * e;
+                  w[e] = pack_bf16((c <= lane) ? __uint_as_float(u[c]) : 0.f, (c + 1 <= lane) ? __uint_as_float(u[c + 1]) : 0.f);
+                }
+                *reinterpret_cast<uint4*>(mrow + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+              failed = true;
+            }
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      const bool any = elem_barrier_any(failed);
+      if (tid == 0 && !any) {
+        const ItemInfo* f = info_of(jt);
+        uint8_t* const rec = p.records + (static_cast<size_t>(f->h) * p.total_chunks + f->gc) * kRecBytes;
+        const uint32_t bs = sbase + kSmBuf + pb * kBufBytes;
+        bulk_s2g(rec + kRecMQK, sbase + kSmMqk, 2048);
+        bulk_s2g(rec + kRecWP, bs + 8192, 8192);
+        bulk_s2g(rec + kRecUP, bs + 16384, 8192);
+        bulk_commit();
+        bulk_wait_read0();
+        if (jt + 2 < n_it) {
+          issue_load(jt + 2);
+          ++loads_issued;
+          if (jt + 3 < n_it) decode_and_prefetch(jt + 3);
+        }
+      }
+      return any;
+    };
+
+    bool any = false;
+    for (int it = 0; it <= n_it && !any; ++it) {
+      if (it < n_it) {
+      const int b = it & 1;
+      uint8_t* buf = smem + kSmBuf + b * kBufBytes;
+      float* s_ex = reinterpret_cast<float*>(smem + kSmEx + b * 1024);
+      if (!mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag)) failed = true;
+      const ItemInfo f = *info_of(it);
+      const int h = f.h, len = f.len;
+      const float a_log = __ldg(p.A_log + h);
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
+      const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+      uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + f.gc) * kRecBytes;
+
+      // ---- sums of squares, gate and its running sum ----------------------------------------------------------------
+      uint4 qw[2], kw[2], vw[2];
+      float G[2][8];
+      {
+        const uint8_t* stg = buf + hh * 4096;
+        const int sw = (cj ^ r8) << 4;
+        const bool valid0 = row0 < len, valid1 = row1 < len;
+        const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+        uint4 gw[2];
+        qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
+        qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
+        kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
+        kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
+        gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
+        gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
+        vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
+        vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
+        if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
+        if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
+        const float hgs = 0.5f * p.gate_scale;
+        const float ha = 0.5f * ex2f(a_log * kLog2e);
+        const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int row = hf ? row1 : row0;
+          float e8[8], sq = 0.f, sk = 0.f;
+          unpack8(qw[hf], e8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sq = fmaf(e8[i], e8[i], sq);
+          unpack8(kw[hf], e8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sk = fmaf(e8[i], e8[i], sk);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+          sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+          sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+          if (lane < 8) {
+            s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
+            s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
+          }
+          unpack8(gw[hf], e8);
+          const bool valid = hf ? valid1 : valid0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float x = valid ? fmaf(tanh_approx(fmaf(e8[i], ha, hab[i])), hgs, hgs) : 0.f;
+#pragma unroll
+            for (int d = 1; d < 8; d <<= 1) {
+              const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
+              if (r8 >= d) x += y;
+            }
+            G[hf][i] = x;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
+        float tot[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
+        if (sb == 0) {      // exponents of sub-block 0 become relative to its end
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
+        }
+        if (r8 == 7) {      // 2^(sub-block total) per channel, once for the CTA
+          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
+          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
+        }
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");      // every thread holds its share of the tiles; sums and totals are complete
+
+      // ---- decayed operands over the tiles, record parts that are final now straight to global memory ---------------
+      {
+        if (sb == 0 && r8 == 0) {
+          const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
+          const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
+          float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
+          *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
+          *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
+        }
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int row = hf ? row1 : row0;
+          const int off = core_off(row, 8 * j, kD);
+          *reinterpret_cast<uint4*>(buf + 24576 + off) = vw[hf];       // v goes on to the products as it is
+          const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
+          const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
+          const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
+          const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
+          // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
+          const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
+          const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
+          __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
+            const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
+            const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
+            const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
+            const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
+            const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
+            const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
+            kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
+            qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
+            kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
+            qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
+            kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
+          }
+          auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
+            return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
+                              *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
+          };
+          *reinterpret_cast<uint4*>(buf + off) = as_u4(kpm);
+          *reinterpret_cast<uint4*>(buf + 8192 + off) = as_u4(qpm);
+          *reinterpret_cast<uint4*>(buf + 16384 + off) = as_u4(kmm);
+          st_global_16(rec_dst + kRecQP + off, as_u4(qp));
+          st_global_16(rec_dst + kRecKR + off, as_u4(kr));
+        }
+      }
+      fence_proxy_async_smem();
+      any = elem_barrier_any(failed);
+      if (any) break;
+      // ---- first products [A; M] = [KPm; QPm] KMm^T (rows 64-127 of the A operand are KMm and VC: lanes nobody reads) --
+      if (tid == 0) {
+        constexpr uint32_t idesc1 = umma_idesc_bf16(128, 32, 0, 0);
+        tc_fence_after();
+        const uint32_t bs = sbase + kSmBuf + b * kBufBytes;
+        const uint64_t a = umma_desc(bs, 128, 2048);
+        const uint64_t bd = umma_desc(bs + 16384, 128, 2048);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) umma_ss(tmem + kColD1 + 32 * b, a + i * 16, bd + i * 16, idesc1, i > 0);
+        umma_commit(bar(B_D1 + b));
+      }
+      }
+      if (it >= 1) any = output(it - 1);
+    }
+    if (any) failed = true;
+    if (tid == 0 && (failed || *abort_flag > 0)) {
+      // wait (bounded) for loads still in flight so that the CTA does not exit under them
+      for (int n = loads_issued > 2 ? loads_issued - 2 : 0; n < loads_issued; ++n) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar(B_LOAD + (n & 1)), (n >> 1) & 1))
+          if (globaltimer_ns() - t0 > 20000000ull) break;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+  if (warp == kMatrixWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace prep_pipe
+
+cudaError_t launch_prepare_pipe(const PrepParams& p, cudaStream_t stream) {
+  if (p.total_chunks == 0 || p.H == 0 || p.T_total == 0) return cudaSuccess;
+  CUtensorMap tq, tk, tg, tv;
+  if (!prep_tc::make_map(&tq, p.q, p.T_total, p.H) || !prep_tc::make_map(&tk, p.k, p.T_total, p.H) ||
+      !prep_tc::make_map(&tg, p.g, p.T_total, p.H) || !prep_tc::make_map(&tv, p.v, p.T_total, p.H))
+    return cudaErrorInvalidValue;
+  static SmemOptIn opt_in;
+  cudaError_t e = opt_in.ensure(prep_pipe::prepare_pipe_kernel, prep_pipe::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const long long items = static_cast<long long>(p.total_chunks) * p.H;
+  const long long slots = 3ll * device_sm_count();
+  const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
+#ifdef FKDA_TUNING
+  long long* trace = prep_tc::g_trace;
+#else
+  long long* trace = nullptr;
+#endif
+  prep_pipe::prepare_pipe_kernel<<<grid, prep_pipe::kThreads, prep_pipe::kSmemBytes, stream>>>(tq, tk, tg, tv, p, trace);
+  return cudaGetLastError();
+}
 
 // whether the grid of the kernel above can hold the call (x = heads; equal lengths: y = chunks of a sequence,
 // z = sequences; packed batch: y + kGridY z = chunk)

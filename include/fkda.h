@@ -56,6 +56,9 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 #define FKDA_FLAG_PREPARE_TCGEN05_PERSISTENT 0x10000u
 /* The same stage on the earlier kernel (vectorised global loads, mma.sync products).  Same operand records. */
 #define FKDA_FLAG_PREPARE_MMA_SYNC 0x20000u
+/* The same stage on the pipelined form of the TMA + tcgen05 kernel (three CTAs per SM, each a loop over items with the
+ * serial part of an item on a ninth warp while the other eight are on the next item). */
+#define FKDA_FLAG_PREPARE_PIPELINED 0x40000u
 /* Cut every sequence of the batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
  * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster

@@ -96,13 +96,14 @@ def test_required_tcgen05_kernel_is_the_default_one():
     assert torch.equal(o0.view(torch.int16), o1.view(torch.int16)) and torch.equal(s0, s1)
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_persistent"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_persistent", "tcgen05_pipelined"])
 @pytest.mark.parametrize("case", ["fixed_tails", "varlen_ragged", "many_items", "long_repeat"])
 def test_tma_tcgen05_token_parallel_kernel_shapes(case, kernel):
     """Shapes that stress the TMA + tcgen05 kernels: ragged last chunks, many short sequences (items of every
     length), more items than one pass of the CTAs holds, and repeated calls that must be bit-reproducible; each
     against the fp64 oracle and against the mma.sync kernel."""
-    tc_flag = F.FLAG_PREPARE_TCGEN05 if kernel == "tcgen05" else F.FLAG_PREPARE_TCGEN05_PERSISTENT
+    tc_flag = {"tcgen05": F.FLAG_PREPARE_TCGEN05, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT,
+               "tcgen05_pipelined": F.FLAG_PREPARE_PIPELINED}[kernel]
     if case == "fixed_tails":
         w = Workload("tc1", H=3, B=5, T=32 * 3 + 17, state_in="fp32", state_out="fp32", state_std=0.5, seed=61)
     elif case == "varlen_ragged":
