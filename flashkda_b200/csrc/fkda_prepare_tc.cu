@@ -1319,10 +1319,11 @@ constexpr int kOffTbt = 16384 + 6144;     // TB^T bf16 [32][32], core layout
 constexpr int kSmMqk = 2 * kBufBytes;     // MQK bf16 [32][32] on its way to the record
 constexpr int kSmSsq = kSmMqk + 2048;     // [2][32][4] partial sums of squares
 constexpr int kSmEx = kSmSsq + 1024;      // 2 items x [2][128] 2^(sub-block total)
-constexpr int kSmInfo = kSmEx + 2048;     // 4 items x {t0, len, h, gc}
-constexpr int kSmBars = kSmInfo + 128;
+constexpr int kSmInfo = kSmEx + 2048;     // 4 items x {t0, len, h, gc, 2^A_log / 2}
+constexpr int kSmBias = kSmInfo + 128;    // 2 items x dt_bias[h][128] (arrives with the tiles)
+constexpr int kSmBars = kSmBias + 1024;
 constexpr int kSmMisc = kSmBars + 64;
-constexpr int kSmemBytes = 70 * 1024;
+constexpr int kSmemBytes = 71 * 1024;
 static_assert(kSmMisc + 16 <= kSmemBytes, "shared memory plan");
 static_assert(3 * (kSmemBytes + 1024) <= 227 * 1024, "three CTAs per SM");
 static_assert(32 * kLdA * 4 <= 6144, "A and T fit before TB^T");
@@ -1338,7 +1339,9 @@ __device__ __forceinline__ ItemInfo decode_item(const PrepParams& p, unsigned it
   ItemInfo r;
   r.h = static_cast<int>(item % static_cast<unsigned>(p.H));
   r.gc = static_cast<int>(item / static_cast<unsigned>(p.H));
-  r.pad[0] = r.pad[1] = r.pad[2] = 0;
+  // half of exp(A_log[h]): the per-head factor of the gate, once per item instead of once per thread
+  r.pad[0] = __float_as_int(0.5f * ex2f(__ldg(p.A_log + r.h) * kLog2e));
+  r.pad[1] = r.pad[2] = 0;
   if (p.cu_seqlens != nullptr) {
     int lo = 0, hi = p.N - 1;
     while (lo < hi) {
@@ -1403,7 +1406,8 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t full = bar(B_LOAD + (it & 1));
     const uint32_t dst = sbase + kSmBuf + (it & 1) * kBufBytes;
     const int tc = static_cast<int>(f->t0), h = f->h;
-    mbar_arrive_expect_tx(full, kBufBytes);
+    mbar_arrive_expect_tx(full, kBufBytes + 512);
+    bulk_g2s(sbase + kSmBias + (it & 1) * 512, p.dt_bias + static_cast<size_t>(h) * kD, 512, full);
     tma_load_3d(dst, &tm_q, 0, h, tc, full);
     tma_load_3d(dst + 4096, &tm_q, 64, h, tc, full);
     tma_load_3d(dst + 8192, &tm_k, 0, h, tc, full);
@@ -1465,6 +1469,10 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       float* sX = sA + 16;
       // the load barrier of this item has an arrival by the thread that wrote the item's info: acquire it
       if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
+      // this warp has time to spare: it decodes the item after next and asks the L2 for its tiles (its info slot was
+      // last read when item it - 2 went to the record, an iteration ago)
+      if (lane == 0 && it >= 1 && it + 2 < n_it) decode_and_prefetch(it + 2);
+      __syncwarp();
       const ItemInfo f = *info_of(it);
       const float bi = lane < f.len ? sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(f.t0 + lane) * p.H + f.h])) : 0.f;
       if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
@@ -1668,7 +1676,6 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (jt + 2 < n_it) {
           issue_load(jt + 2);
           ++loads_issued;
-          if (jt + 3 < n_it) decode_and_prefetch(jt + 3);
         }
       }
       return any;
@@ -1683,9 +1690,9 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag)) failed = true;
       const ItemInfo f = *info_of(it);
       const int h = f.h, len = f.len;
-      const float a_log = __ldg(p.A_log + h);
-      const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
-      const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+      const float ha = __int_as_float(f.pad[0]);
+      const float4 b0 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j);
+      const float4 b1 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j + 16);
       uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + f.gc) * kRecBytes;
 
       // ---- sums of squares, gate and its running sum ----------------------------------------------------------------
@@ -1708,7 +1715,6 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
         if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
         const float hgs = 0.5f * p.gate_scale;
-        const float ha = 0.5f * ex2f(a_log * kLog2e);
         const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
