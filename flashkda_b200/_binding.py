@@ -22,9 +22,7 @@ FLAG_NO_FUSED_SHORT = 0x10
 FLAG_REFERENCE_ROUNDING = 0x20
 FLAG_FUSED_ANY_T = 0x40
 FLAG_PREPARE_TCGEN05 = 0x80
-FLAG_PREPARE_TCGEN05_PERSISTENT = 0x10000
 FLAG_PREPARE_MMA_SYNC = 0x20000
-FLAG_PREPARE_PIPELINED = 0x40000
 
 
 def FLAG_SEGMENTS(n: int) -> int:

@@ -14,9 +14,7 @@ namespace fkda {
 cudaError_t launch_chunk_prefix(const int64_t* cu, int N, int64_t T_total, int H, int n_segs, int* prefix, int* status,
                                 cudaStream_t stream);
 cudaError_t launch_prepare(const PrepParams& p, cudaStream_t stream);
-cudaError_t launch_prepare_tc(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_prepare_tc4(const PrepParams& p, cudaStream_t stream);
-bool prepare_tc4_applicable(const PrepParams& p);
 cudaError_t launch_prepare_pipe(const PrepParams& p, cudaStream_t stream);
 cudaError_t launch_scan(const ScanParams& p, cudaStream_t stream);
 cudaError_t launch_scan_simt(const ScanParams& p, cudaStream_t stream);
@@ -187,11 +185,9 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
     q.dbg = dbg_env ? atoi(dbg_env) : 0;
   }
 #endif
-  if (p->flags & FKDA_FLAG_PREPARE_PIPELINED) e = fkda::launch_prepare_pipe(q, stream);
-  else if (p->flags & FKDA_FLAG_PREPARE_TCGEN05_PERSISTENT) e = fkda::launch_prepare_tc(q, stream);
-  else if (p->flags & FKDA_FLAG_PREPARE_MMA_SYNC) e = fkda::launch_prepare(q, stream);
-  else if ((p->flags & FKDA_FLAG_PREPARE_TCGEN05) || fkda::prepare_tc4_applicable(q)) e = fkda::launch_prepare_tc4(q, stream);
-  else e = fkda::launch_prepare(q, stream);
+  if (p->flags & FKDA_FLAG_PREPARE_MMA_SYNC) e = fkda::launch_prepare(q, stream);
+  else if (p->flags & FKDA_FLAG_PREPARE_TCGEN05) e = fkda::launch_prepare_tc4(q, stream);
+  else e = fkda::launch_prepare_pipe(q, stream);
   if (e != cudaSuccess) return cuda_fail(e, "prepare launch");
   return FKDA_OK;
 }

@@ -1,23 +1,21 @@
-// Token-parallel half of the KDA prefill on the Blackwell data path: TMA-staged inputs, tcgen05 products with
-// accumulators in tensor memory, one persistent CTA per SM whose warps are specialised by stage.
+// Token-parallel half of the KDA prefill on the Blackwell data path: TMA-staged inputs, the intra-chunk products on
+// tcgen05 with accumulators in tensor memory.
 //
 // Replaces the reference's K1 (csrc/smxx/fwd_kernel1.cuh:107-586: one 16-token tile per CTA, mma.sync products on
 // two of eight warps, a one-warp inverse) and writes the same operand record as fkda_prepare.cu (fkda_common.cuh),
-// so every recurrence kernel consumes its output unchanged.  An item is one (32-token chunk, head) pair; a CTA takes
-// items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps several of them in flight, each in a different stage:
+// so every recurrence kernel consumes its output unchanged.  An item is one (32-token chunk, head) pair.  Two kernels:
 //
-//   producer (1 thread)      TMA tile loads of q, k, g, v ([32 tok][64 ch] boxes, 128-byte swizzle) into a 2-slot ring;
-//                            the same thread issues the second products below
-//   element warps (2 x 8)    two groups, alternate items: L2 norms, gate, in-sub-block running sums, decayed operands
-//                            KPm, QPm, KMm (bf16, core-matrix layout) for the products, v re-laid as a product operand,
-//                            and the record parts that are final at this point (QP, KR, E) straight to global memory
-//   MMA threads (2)          first products [A; M] = [KPm; QPm] KMm^T (K = 128 split over two accumulators); second
-//                            products, once T is there, (w')^T = KPm^T TB^T and (u')^T = v^T TB^T (M = 128, N = 32,
-//                            K = 32, TB as hi + lo bf16 parts)
-//   inverse warps (2)        alternate items: A from tensor memory, T = (I + A)^-1 by fp32 forward substitution with
-//                            one column per lane, TB^T = (T diag(beta))^T as an MN-major operand
-//   M warp / output warps    tril(M) -> MQK; (w')^T scaled back and transposed through stmatrix.trans -> WP; (u')^T -> UP;
-//                            one thread sends MQK, WP, UP to the record with bulk stores
+//   prepare_pipe_kernel (default)   three CTAs per SM, each a loop over items with two operand buffers: eight element
+//                                   warps work on item i while a ninth warp does the serial part of item i - 1
+//   prepare_tc4_kernel              one CTA of eight warps per item, four CTAs per SM, phases separated by CTA-wide
+//                                   barriers; other resident CTAs fill the waits of the serial part
+//
+// Both: q, k, g, v arrive as [32 tok][64 ch] TMA boxes with the 128-byte swizzle; the element-wise work (L2 norms, gate,
+// running sums of the log2 decay, decayed operands KPm, QPm, KMm in bf16 core-matrix layout) runs on CUDA cores with
+// every thread owning two (row, 8 channel) pieces; first products [A; M] = [KPm; QPm] KMm^T (M = 128, N = 32, K = 128);
+// A from tensor memory, T = (I + A)^-1 by fp32 forward substitution on the two 16 x 16 diagonal blocks (one column per
+// lane) and two tf32 products for the block below them, TB^T as an MN-major operand; second products
+// (w')^T = KPm^T TB^T and (u')^T = v^T TB^T (M = 128, N = 32, K = 32).
 //
 // Decay ranges: with G the running log2 decay inside the chunk and P its value after the first 16 tokens, the
 // products use k+ = khat 2^(G - P) and k- = khat 2^(P - G): both stay inside 2^(+-115.4) for lower_bound >= -5
@@ -30,70 +28,8 @@
 namespace fkda {
 namespace prep_tc {
 
-constexpr int kWarps = 24;
-constexpr int kThreads = kWarps * 32;
-constexpr int kElemWarp0 = 8;            // warps 8-15: element group 0 (even items), 16-23: group 1 (odd items)
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColD1 = 0;           // 2 slots x 2 accumulators x 32 columns: rows 0-31 A, 32-63 M
-constexpr uint32_t kColD2 = 128;         // 2 slots x [(w')^T 32 | (u')^T 32]
-
-// ---- shared memory (byte offsets from a 1024-byte aligned base) ----------------------------------------------------
-constexpr int kStgBytes = 32768;         // q, k, g, v: two [32 tok][128 B] swizzled halves each
-constexpr int kSmStg = 0;                                 // 2 slots
-constexpr int kOpbBytes = 24576;         // KPm | QPm | VC, 8192 each (core layout [32][128])
-constexpr int kSmOpb = kSmStg + 2 * kStgBytes;            // 3 slots
-constexpr int kSmOpa = kSmOpb + 3 * kOpbBytes;            // 2 slots x KMm 8192
-constexpr int kOutBytes = 18432;         // MQK 2048 | WP 8192 | UP 8192 (record layouts)
-constexpr int kSmOut = kSmOpa + 2 * 8192;                 // 2 slots
-constexpr int kTbtBytes = 4096;          // TB^T hi | lo, [32 tok'][32 tok] core layout, 2048 each
-constexpr int kSmTbt = kSmOut + 2 * kOutBytes;            // 2 slots
-constexpr int kLdA = 36;                 // floats per row of the fp32 A matrix
-constexpr int kA32Bytes = 32 * kLdA * 4;
-constexpr int kSmA32 = kSmTbt + 2 * kTbtBytes;            // one per inverse warp
-constexpr int kInfoSlots = 12;         // an item's entry is last read up to nine items after it was written
-constexpr int kInfoBytes = 704;          // t0 (8) len h gc (12) pad (12) | beta[32] fp32 | cfac[128] fp32
-constexpr int kSmInfo = kSmA32 + 2 * kA32Bytes;
-constexpr int kSmElem = kSmInfo + kInfoSlots * kInfoBytes; // per element group: 2 copies x (ssq 1024 | 2^tot 1024)
-constexpr int kSmBars = kSmElem + 2 * 4096;
-constexpr int kSmMisc = kSmBars + 256;
-constexpr int kSmemBytes = kSmMisc + 64 + 1024;           // + slack for the manual 1024-byte alignment
-static_assert(kSmemBytes <= 227 * 1024, "shared memory plan");
-static_assert(kSmOpb % 1024 == 0 && kSmOpa % 1024 == 0 && kSmOut % 128 == 0 && kSmTbt % 128 == 0, "operand alignment");
-
-enum {
-  B_STG_FULL = 0,     // [2] tile loads of an item have landed                  (tx barrier, 1 arrival)
-  B_STG_EMPTY = 2,    // [2] the element warps have read the staged tiles         (8 warps)
-  B_ELEM_DONE = 4,    // [2] operands of an item written                          (8 warps)
-  B_OPB_EMPTY = 6,    // [3] KPm, QPm, VC of a slot no longer read                (commit)
-  B_OPA_EMPTY = 9,    // [2] KMm of a slot no longer read                         (commit)
-  B_D1_FULL = 11,     // [2] [A; M] accumulators complete                         (commit)
-  B_D1_EMPTY = 13,    // [2] ... and read                                         (inverse warp + M warp)
-  B_TBT_FULL = 15,    // [2] TB^T operand written                                 (inverse warp)
-  B_TBT_EMPTY = 17,   // [2] ... and no longer read                               (commit)
-  B_D2_FULL = 19,     // [2] (w')^T, (u')^T complete                              (commit)
-  B_D2_EMPTY = 21,    // [2] ... and read                                         (4 warps)
-  B_OUT_FULL = 23,    // [2] MQK, WP, UP of a slot written                        (5 warps)
-  B_OUT_FREE = 25,    // [2] ... and read by their bulk stores                    (storing thread)
-  B_GROUP = 27,       // [2] rendezvous of the eight warps of an element group    (8 warps)
-  B_COUNT = 29
-};
-static_assert(B_COUNT * 8 <= 256, "barrier area");
-
-struct Params {
-  PrepParams p;
-  int n_items_bound;   // total_chunks * H (varlen: an upper bound; the device knows the exact figure)
-  long long* trace;    // timeline buffer of a tuning build (else nullptr)
-};
-
-// Timeline of CTA 0 (tuning builds only): entry [item * 16 + event] = clock64() for its first 32 items.
 #ifdef FKDA_TUNING
-static long long* g_trace = nullptr;
-#define PTRACE(n, ev)                                                                                                  \
-  do {                                                                                                                 \
-    if (prm.trace != nullptr && blockIdx.x == 0 && (n) < 32) prm.trace[(n) * 16 + (ev)] = clock64();                    \
-  } while (0)
-#else
-#define PTRACE(n, ev) do { } while (0)
+static long long* g_trace = nullptr;      // timeline buffer of a tuning build (see the trace macros of the kernels)
 #endif
 
 // ---- PTX wrappers used only here ------------------------------------------------------------------------------------
@@ -130,634 +66,6 @@ __device__ __forceinline__ void stsm_x4_trans(uint32_t addr, uint32_t r0, uint32
 }
 __device__ __forceinline__ void st_global_16(void* p, const uint4& v) {
   asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
-// every wait of this kernel parks the warp (most warps of the CTA wait most of the time)
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  const bool ok = mbar_wait_parked(bar, parity, abort_flag);
-  return __all_sync(0xffffffffu, ok);
-}
-
-struct ItemInfo {
-  long long t0;
-  int len, h, gc;
-  int pad[3];
-  float beta[32];
-  float cfac[128];
-};
-static_assert(sizeof(ItemInfo) <= kInfoBytes, "item info");
-
-// One quadrant of the output stage of an item: (w')^T -> WP (scaled back by 2^P, transposed), (u')^T -> UP.
-__device__ __forceinline__ bool output_quadrant(uint8_t* smem, uint32_t tmem, int q, int n, int lane, volatile int* abort_flag) {
-  const uint32_t sbase = smem_u32(smem);
-  const int slot = n & 1;
-  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
-  if (!warp_wait(bar(B_D2_FULL + slot), (n >> 1) & 1, abort_flag)) return false;
-  tc_fence_after();
-  const uint32_t tq = tmem + (static_cast<uint32_t>(q * 32) << 16) + kColD2 + 64 * slot;
-  uint32_t f0[16], f1[16], u[32];
-  tmem_ld_16x256b_x4(tq, f0);
-  tmem_ld_16x256b_x4(tq + (16u << 16), f1);
-  tmem_ld32(tq + 32, u);
-  tmem_wait_ld();
-  tc_fence_before();
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar(B_D2_EMPTY + slot));
-  if (n >= 2 && !warp_wait(bar(B_OUT_FREE + slot), ((n >> 1) - 1) & 1, abort_flag)) return false;
-  const ItemInfo* info = reinterpret_cast<const ItemInfo*>(smem + kSmInfo + (n % kInfoSlots) * kInfoBytes);
-  uint8_t* out = smem + kSmOut + slot * kOutBytes;
-  {
-    // WP [32 tok][128 k]: fragments hold (k, tok); the transposing store writes rows of 8 k per token
-    const int kr = 32 * q + (lane >> 2);
-    const float c00 = info->cfac[kr], c08 = info->cfac[kr + 8], c10 = info->cfac[kr + 16], c18 = info->cfac[kr + 24];
-    const uint32_t wp = sbase + kSmOut + slot * kOutBytes + 2048;
-    const int m = lane >> 3, r = lane & 7;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint32_t(&f)[16] = half ? f1 : f0;
-      const float ca = half ? c10 : c00, cb = half ? c18 : c08;
-      const int k0 = 32 * q + 16 * half;
-#pragma unroll
-      for (int jp = 0; jp < 2; ++jp) {        // token blocks 2jp, 2jp + 1
-        uint32_t w[4];
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int j = 2 * jp + jj;
-          w[2 * jj] = pack_bf16(__uint_as_float(f[4 * j]) * ca, __uint_as_float(f[4 * j + 1]) * ca);          // k rows k0 .. k0+7
-          w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * j + 2]) * cb, __uint_as_float(f[4 * j + 3]) * cb);  // k rows k0+8 .. k0+15
-        }
-        // tile m = 2 jj + hi: tokens 8 (2jp + jj) + r, channels k0 + 8 hi .. + 7
-        const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
-        stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
-      }
-    }
-  }
-  {
-    // UP [128 v][32 tok]: this lane's row
-    const int v = 32 * q + lane;
-    uint8_t* row = out + 10240 + (v >> 3) * 512 + (v & 7) * 16;
-#pragma unroll
-    for (int cb = 0; cb < 4; ++cb)
-      *reinterpret_cast<uint4*>(row + cb * 128) =
-          make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
-                     pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
-  }
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar(B_OUT_FULL + slot));
-  return true;
-}
-
-// Common to every role: the kernel's context, unpacked once per role function.
-#define ROLE_PROLOGUE                                                                                                  \
-  const uint32_t sbase = smem_u32(smem);                                                                               \
-  const PrepParams& p = prm.p;                                                                                         \
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;                                                       \
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);                                      \
-  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };                                                           \
-  auto info_of = [&](int n) { return reinterpret_cast<ItemInfo*>(smem + kSmInfo + (n % kInfoSlots) * kInfoBytes); }; \
-  const int H = p.H;                                                                                                   \
-  bool failed = false;                                                                                                 \
-  (void)sbase; (void)tid; (void)lane; (void)warp; (void)H; (void)info_of;
-
-__device__ __forceinline__ bool producer_and_second_products(uint8_t* smem, uint32_t tmem, const Params& prm, const CUtensorMap* tm_q_,
-                                                             const CUtensorMap* tm_k_, const CUtensorMap* tm_g_, const CUtensorMap* tm_v_,
-                                                             int my_items) {
-  ROLE_PROLOGUE
-  // ===== producer and second products, one thread: whichever has its inputs ready =====================================
-  // (tile loads of an item: item -> (sequence, first token, length), eight box loads;  second products of an item:
-  // (w')^T = KPm^T TB^T and (u')^T = VC^T TB^T once the inverse warp has written TB^T)
-  if (lane == 0) {
-    constexpr uint32_t idesc2 = umma_idesc_bf16(128, 32, 1, 1);
-    const int cps = p.cu_seqlens == nullptr ? static_cast<int>((p.T + kChunk - 1) / kChunk) : 0;
-    int seq = 0;           // varlen: sequence of the previous item (items come in increasing chunk order)
-    int np = 0, n2 = 0;    // next item to load / next item of the second products
-    uint64_t idle_since = 0;
-    uint32_t idle_polls = 0;
-    while (n2 < my_items) {
-      bool progressed = false;
-      if (np < my_items && (np < 2 || mbar_test(bar(B_STG_EMPTY + (np & 1)), ((np >> 1) - 1) & 1))) {
-        const int n = np;
-        const long long it = blockIdx.x + static_cast<long long>(n) * gridDim.x;
-        const int gc = static_cast<int>(it / H), h = static_cast<int>(it - static_cast<long long>(gc) * H);
-        long long t0;
-        int len;
-        if (p.cu_seqlens != nullptr) {
-          int lo = seq, hi = p.N - 1;
-          while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (p.chunk_prefix[mid] <= gc) lo = mid; else hi = mid - 1;
-          }
-          seq = lo;
-          long long bos = p.cu_seqlens[lo], eos = p.cu_seqlens[lo + 1];
-          bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
-          eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
-          t0 = bos + static_cast<long long>(gc - p.chunk_prefix[lo]) * kChunk;
-          const long long rem = eos - t0;
-          len = rem < kChunk ? static_cast<int>(rem) : kChunk;
-        } else {
-          const int sq = gc / cps, lc = gc - sq * cps;
-          t0 = static_cast<long long>(sq) * p.T + static_cast<long long>(lc) * kChunk;
-          const long long rem = p.T - static_cast<long long>(lc) * kChunk;
-          len = rem < kChunk ? static_cast<int>(rem) : kChunk;
-        }
-        const int slot = n & 1;
-        PTRACE(n, 0);
-        ItemInfo* info = info_of(n);
-        info->t0 = t0;
-        info->len = len;
-        info->h = h;
-        info->gc = gc;
-        const uint32_t full = bar(B_STG_FULL + slot);
-        mbar_arrive_expect_tx(full, kStgBytes);
-        const uint32_t dst = sbase + kSmStg + slot * kStgBytes;
-        const int tc = static_cast<int>(t0);
-        tma_load_3d(dst, tm_q_, 0, h, tc, full);
-        tma_load_3d(dst + 4096, tm_q_, 64, h, tc, full);
-        tma_load_3d(dst + 8192, tm_k_, 0, h, tc, full);
-        tma_load_3d(dst + 12288, tm_k_, 64, h, tc, full);
-        tma_load_3d(dst + 16384, tm_g_, 0, h, tc, full);
-        tma_load_3d(dst + 20480, tm_g_, 64, h, tc, full);
-        tma_load_3d(dst + 24576, tm_v_, 0, h, tc, full);
-        tma_load_3d(dst + 28672, tm_v_, 64, h, tc, full);
-        ++np;
-        progressed = true;
-      }
-      if (n2 < np && mbar_test(bar(B_TBT_FULL + (n2 & 1)), (n2 >> 1) & 1) &&
-          (n2 < 2 || mbar_test(bar(B_D2_EMPTY + (n2 & 1)), ((n2 >> 1) - 1) & 1))) {
-        const int n = n2, slot = n & 1;
-        tc_fence_after();
-        // A read MN-major from the [32 tok'][128] core-layout tiles (channel-adjacent core matrices 128 B apart, token
-        // groups 2048 B), B = TB^T [32 tok'][32 tok] read MN-major (token-adjacent core matrices 128 B apart, tok' groups
-        // 512 B); the hi and lo parts of TB accumulate.
-        const uint32_t opb = sbase + kSmOpb + (n % 3) * kOpbBytes;
-        const uint64_t ak = umma_desc(opb, 2048, 128), av = umma_desc(opb + 16384, 2048, 128);
-        const uint64_t bt = umma_desc(sbase + kSmTbt + slot * kTbtBytes, 512, 128);
-        const uint32_t d = tmem + kColD2 + 64 * slot;
-#pragma unroll
-        for (int part = 0; part < 2; ++part)
-#pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {
-            umma_ss(d, ak + ks * 256, bt + part * 128 + ks * 64, idesc2, (part | ks) != 0);
-            umma_ss(d + 32, av + ks * 256, bt + part * 128 + ks * 64, idesc2, (part | ks) != 0);
-          }
-        umma_commit(bar(B_D2_FULL + slot));
-        umma_commit(bar(B_OPB_EMPTY + n % 3));
-        umma_commit(bar(B_TBT_EMPTY + slot));
-        PTRACE(n, 8);
-        ++n2;
-        progressed = true;
-      }
-      if (progressed) {
-        idle_since = 0;
-        idle_polls = 0;
-      } else {
-        // nothing ready: park (up to 100 ns) on the barrier that is due next
-        (void)mbar_try_wait_hint(bar(B_TBT_FULL + (n2 & 1)), (n2 >> 1) & 1, 100u);
-        if (((++idle_polls) & 63u) != 0u) continue;
-        const int f = *abort_flag;
-        if (f > 0) { failed = true; break; }
-        const uint64_t now = globaltimer_ns();
-        if (idle_since == 0) idle_since = now;
-        else if (now - idle_since > (f < 0 ? static_cast<uint64_t>(-f) * 1000ull : kWaitLimitNs)) {
-          *abort_flag = 1;
-          failed = true;
-          break;
-        }
-      }
-    }
-    if (failed || *abort_flag > 0) {
-      // wait (bounded) for loads still in flight so that the CTA does not exit under them
-      for (int n = np > 2 ? np - 2 : 0; n < np; ++n) {
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(bar(B_STG_FULL + (n & 1)), (n >> 1) & 1))
-          if (globaltimer_ns() - t0 > 20000000ull) break;
-      }
-    }
-    // the last commits' arrivals must have landed in shared memory before the CTA may exit
-    if (!failed && my_items > 0) {
-      const int n = my_items - 1;
-      if (!mbar_wait_parked(bar(B_TBT_EMPTY + (n & 1)), (n >> 1) & 1, abort_flag)) failed = true;
-      if (!failed && my_items > 1 && !mbar_wait_parked(bar(B_TBT_EMPTY + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag)) failed = true;
-    }
-  }
-  return failed;
-}
-
-__device__ __forceinline__ bool first_products(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
-  ROLE_PROLOGUE
-  (void)tmem;
-  // ===== first products, one thread ====================================================================================
-  if (lane == 0) {
-    constexpr uint32_t idesc1 = umma_idesc_bf16(128, 32, 0, 0);
-    for (int n = 0; n < my_items; ++n) {
-      const int slot = n & 1;
-      if (!mbar_wait_parked(bar(B_ELEM_DONE + slot), (n >> 1) & 1, abort_flag)) { failed = true; break; }
-      if (n >= 2 && !mbar_wait_parked(bar(B_D1_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
-      tc_fence_after();
-      // [A; M] = [KPm; QPm] KMm^T: rows 64-127 of the A operand are whatever follows QPm in shared memory and land in
-      // accumulator lanes nobody reads.  K = 128 as two chains of four K = 16 steps into two accumulators, issued
-      // alternately so that the chains overlap.
-      const uint64_t a = umma_desc(sbase + kSmOpb + (n % 3) * kOpbBytes, 128, 2048);
-      const uint64_t b = umma_desc(sbase + kSmOpa + slot * 8192, 128, 2048);
-      const uint32_t d = tmem + kColD1 + 64 * slot;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        umma_ss(d, a + i * 16, b + i * 16, idesc1, i > 0);
-        umma_ss(d + 32, a + (4 + i) * 16, b + (4 + i) * 16, idesc1, i > 0);
-      }
-      umma_commit(bar(B_D1_FULL + slot));
-      umma_commit(bar(B_OPA_EMPTY + slot));
-      PTRACE(n, 4);
-    }
-    if (!failed && my_items > 0) {
-      const int n = my_items - 1;
-      if (!mbar_wait_parked(bar(B_OPA_EMPTY + (n & 1)), (n >> 1) & 1, abort_flag)) failed = true;
-      if (!failed && my_items > 1 && !mbar_wait_parked(bar(B_OPA_EMPTY + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag)) failed = true;
-    }
-  }
-  return failed;
-}
-
-__device__ __forceinline__ bool inverse_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
-  ROLE_PROLOGUE
-  (void)tmem;
-  // ===== inverse warps (items of one parity each); they also take quadrant 0 of the output stage ===================
-  const int par = warp == 4 ? 1 : 0;
-  float* sA = reinterpret_cast<float*>(smem + kSmA32 + par * kA32Bytes);
-  for (int n = par; n < my_items; n += 2) {
-    const int slot = n & 1;
-    if (!warp_wait(bar(B_D1_FULL + slot), (n >> 1) & 1, abort_flag)) { failed = true; break; }
-    tc_fence_after();
-    if (lane == 0) PTRACE(n, 5);
-    {
-      uint32_t a0[32], a1[32];
-      tmem_ld32(tmem + kColD1 + 64 * slot, a0);
-      tmem_ld32(tmem + kColD1 + 64 * slot + 32, a1);
-      tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_D1_EMPTY + slot));
-      // row `lane` of A = tril(k+ k-^T, -1) scaled by beta of the row, stored transposed: sA[j][i] = A[i][j]
-      // (bank = (4 j + i) mod 32: conflict-free across the lanes i)
-      const float bi = info_of(n)->beta[lane];
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        sA[j * kLdA + lane] = (j < lane) ? (__uint_as_float(a0[j]) + __uint_as_float(a1[j])) * bi : 0.f;
-    }
-    __syncwarp();
-    if (lane == 0) PTRACE(n, 6);
-    // forward substitution, column `lane` of T = (I + A)^-1, right-looking: once x_j is final, every later row takes
-    // its term A_ij x_j.  The updates of one step are independent of each other and the loads (column j of A, four
-    // rows at a time, all lanes the same address) do not depend on the arithmetic.
-    float x[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = (i == lane) ? 1.f : 0.f;
-#pragma unroll
-    for (int j = 0; j < 31; ++j) {
-      const float xj = x[j];
-#pragma unroll
-      for (int i4 = 0; i4 < 8; ++i4) {
-        if (4 * i4 + 3 > j) {
-          const float4 a4 = *reinterpret_cast<const float4*>(sA + j * kLdA + 4 * i4);
-          if (4 * i4 + 0 > j) x[4 * i4 + 0] = fmaf(-a4.x, xj, x[4 * i4 + 0]);
-          if (4 * i4 + 1 > j) x[4 * i4 + 1] = fmaf(-a4.y, xj, x[4 * i4 + 1]);
-          if (4 * i4 + 2 > j) x[4 * i4 + 2] = fmaf(-a4.z, xj, x[4 * i4 + 2]);
-          if (4 * i4 + 3 > j) x[4 * i4 + 3] = fmaf(-a4.w, xj, x[4 * i4 + 3]);
-        }
-      }
-    }
-    __syncwarp();
-    if (n >= 2 && !warp_wait(bar(B_TBT_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
-    {
-      // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c, as bf16 hi + lo parts
-      const float bc = info_of(n)->beta[lane];
-      uint8_t* row = smem + kSmTbt + slot * kTbtBytes + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t hi[4], lo[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float v0 = x[8 * cb + 2 * e] * bc, v1 = x[8 * cb + 2 * e + 1] * bc;
-          hi[e] = pack_bf16(v0, v1);
-          lo[e] = pack_bf16(v0 - bf_lo(hi[e]), v1 - bf_hi(hi[e]));
-        }
-        *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(row + 2048 + cb * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-      }
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) { PTRACE(n, 7); mbar_arrive(bar(B_TBT_FULL + slot)); }
-    if (!output_quadrant(smem, tmem, 0, n, lane, abort_flag)) { failed = true; break; }
-  }
-  return failed;
-}
-
-__device__ __forceinline__ bool m_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
-  ROLE_PROLOGUE
-  (void)tmem;
-  // ===== M warp: tril(q+ k-^T) -> MQK ==============================================================================
-  for (int n = 0; n < my_items; ++n) {
-    const int slot = n & 1;
-    if (!warp_wait(bar(B_D1_FULL + slot), (n >> 1) & 1, abort_flag)) { failed = true; break; }
-    tc_fence_after();
-    uint32_t a0[32], a1[32];
-    const uint32_t tq = tmem + (32u << 16) + kColD1 + 64 * slot;
-    tmem_ld32(tq, a0);
-    tmem_ld32(tq + 32, a1);
-    tmem_wait_ld();
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar(B_D1_EMPTY + slot));
-    if (n >= 2 && !warp_wait(bar(B_OUT_FREE + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
-    uint8_t* row = smem + kSmOut + slot * kOutBytes + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-    for (int cb = 0; cb < 4; ++cb) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int c = 8 * cb + 2 * e;
-        const float v0 = (c <= lane) ? __uint_as_float(a0[c]) + __uint_as_float(a1[c]) : 0.f;
-        const float v1 = (c + 1 <= lane) ? __uint_as_float(a0[c + 1]) + __uint_as_float(a1[c + 1]) : 0.f;
-        w[e] = pack_bf16(v0, v1);
-      }
-      *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar(B_OUT_FULL + slot));
-  }
-  return failed;
-}
-
-__device__ __forceinline__ bool output_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
-  ROLE_PROLOGUE
-  (void)tmem;
-  // ===== output warps: quadrants 1-3 of (w')^T, (u')^T; warp 7 also sends MQK, WP, UP to the record ==================
-  const int q = warp & 3;
-  for (int n = 0; n < my_items; ++n) {
-    if (!output_quadrant(smem, tmem, q, n, lane, abort_flag)) { failed = true; break; }
-    if (warp == 7 && lane == 0) PTRACE(n, 9);
-    if (warp == 7 && lane == 0) {
-      const int slot = n & 1;
-      if (!mbar_wait_parked(bar(B_OUT_FULL + slot), (n >> 1) & 1, abort_flag)) { failed = true; }
-      else {
-        const ItemInfo* info = info_of(n);
-        uint8_t* rec = p.records + (static_cast<size_t>(info->h) * p.total_chunks + info->gc) * kRecBytes;
-        const uint32_t src = sbase + kSmOut + slot * kOutBytes;
-        bulk_s2g(rec + kRecMQK, src, 2048);
-        bulk_s2g(rec + kRecWP, src + 2048, 8192);
-        bulk_s2g(rec + kRecUP, src + 10240, 8192);
-        bulk_commit();
-        PTRACE(n, 10);
-        bulk_wait_read0();
-        PTRACE(n, 11);
-        mbar_arrive(bar(B_OUT_FREE + slot));
-      }
-    }
-    failed = __any_sync(0xffffffffu, failed);
-    if (failed) break;
-  }
-  return failed;
-}
-
-__device__ __forceinline__ bool element_warp(uint8_t* smem, uint32_t tmem, const Params& prm, int my_items) {
-  ROLE_PROLOGUE
-  (void)tmem;
-  // ===== element warps ================================================================================================
-  const int grp = (warp - kElemWarp0) >> 3;
-  const int t = tid - (kElemWarp0 + 8 * grp) * 32;          // 0..255 inside the group
-  const int wg = t >> 5;
-  const int r8 = t & 7, cm = t >> 3, j = cm & 15, sb = cm >> 4;   // rows sb*16 + r8 (+8), channels 8j .. 8j+7
-  const int row0 = sb * 16 + r8, row1 = row0 + 8;
-  const int hh = j >> 3, cj = j & 7;
-  const float hgs = 0.5f * p.gate_scale;
-  uint8_t* const selem = smem + kSmElem + grp * 4096;
-  for (int n = grp; n < my_items; n += 2) {
-    const int slot = n & 1, u = n >> 1;
-    float* s_ssq = reinterpret_cast<float*>(selem + (u & 1) * 2048);
-    float* s_ex = reinterpret_cast<float*>(selem + (u & 1) * 2048 + 1024);      // [2 sub-blocks][128] 2^(sub-block total)
-    // per-head constants: asked for before the wait for the tiles (the head follows from the item number)
-    const int h = static_cast<int>((blockIdx.x + static_cast<long long>(n) * gridDim.x) % H);
-    const float a_log = __ldg(p.A_log + h);
-    const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
-    const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
-    if (!warp_wait(bar(B_STG_FULL + slot), u & 1, abort_flag)) { failed = true; break; }
-    if (t == 0) PTRACE(n, 1);
-    ItemInfo* info = info_of(n);
-    const int len = info->len;
-    uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + info->gc) * kRecBytes;
-    float braw = 0.f;
-    if (t < kChunk && t < len) braw = __bfloat162float(p.beta[static_cast<size_t>(info->t0 + t) * H + h]);
-    // ---- staged tiles -> registers (16-byte chunks of a row are XOR-swizzled by the row index: conflict-free) -------
-    const uint8_t* stg = smem + kSmStg + slot * kStgBytes + hh * 4096;
-    const int sw = (cj ^ r8) << 4;
-    const bool valid0 = row0 < len, valid1 = row1 < len;
-    const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
-    uint4 qw[2], kw[2], gw[2], vw[2];
-    qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
-    qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
-    kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
-    kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
-    gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
-    gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
-    vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
-    vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
-    if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
-    if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar(B_STG_EMPTY + slot));
-    // ---- partial sums of squares, gate and its running sum inside the sub-block ------------------------------------
-    // gate: gamma = gate_scale sigmoid(a (g + bias)) = hgs tanh(ha g + ha bias) + hgs
-    float G[2][8];
-    {
-      const float ha = 0.5f * ex2f(a_log * kLog2e);
-      const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const int row = hf ? row1 : row0;
-        float f[8], sq = 0.f, sk = 0.f;
-        unpack8(qw[hf], f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sq = fmaf(f[i], f[i], sq);
-        unpack8(kw[hf], f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sk = fmaf(f[i], f[i], sk);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-        sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-        sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-        if (lane < 8) {
-          s_ssq[(0 * kChunk + row) * 4 + (wg & 3)] = sq;
-          s_ssq[(1 * kChunk + row) * 4 + (wg & 3)] = sk;
-        }
-        unpack8(gw[hf], f);
-        const bool valid = hf ? valid1 : valid0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float x = valid ? fmaf(tanh_approx(fmaf(f[i], ha, hab[i])), hgs, hgs) : 0.f;
-#pragma unroll
-          for (int d = 1; d < 8; d <<= 1) {
-            const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
-            if (r8 >= d) x += y;
-          }
-          G[hf][i] = x;
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
-    {
-      // the thread that holds the last row of the sub-block publishes 2^(sub-block total) per channel
-      float tot[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
-      if (sb == 0) {      // exponents of sub-block 0 become relative to its end
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
-      }
-      if (r8 == 7) {
-        const float4 e0 = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
-        const float4 e1 = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
-        *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = e0;
-        *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = e1;
-        if (sb == 0) {
-          *reinterpret_cast<float4*>(info->cfac + 8 * j) = e0;
-          *reinterpret_cast<float4*>(info->cfac + 8 * j + 4) = e1;
-        }
-      }
-    }
-    if (t < kChunk) info->beta[t] = t < len ? sigmoid_fast(braw) : 0.f;
-    // rendezvous of the group (a barrier with a bounded wait, so that a give-up elsewhere cannot strand a warp here)
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar(B_GROUP + grp));
-    if (!warp_wait(bar(B_GROUP + grp), u & 1, abort_flag)) { failed = true; break; }
-    if (t == 0) PTRACE(n, 2);
-    // ---- decayed operands --------------------------------------------------------------------------------------------
-    // With P = total of sub-block 0 and Q = total of sub-block 1 (per channel), the exponents held now are G - P in
-    // sub-block 0 and G in sub-block 1: the products' k+, q+, k- come straight from them, the record's q+ and
-    // k-to-the-end take 2^P and 2^Q on top.
-    if (n >= 3 && !warp_wait(bar(B_OPB_EMPTY + n % 3), ((n / 3) - 1) & 1, abort_flag)) { failed = true; break; }
-    if (n >= 2 && !warp_wait(bar(B_OPA_EMPTY + slot), ((n >> 1) - 1) & 1, abort_flag)) { failed = true; break; }
-    {
-      uint8_t* opb = smem + kSmOpb + (n % 3) * kOpbBytes;
-      uint8_t* opa = smem + kSmOpa + slot * 8192;
-      if (sb == 0 && r8 == 0) {
-        const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
-        const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
-        float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
-        *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
-        *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
-      }
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const int row = hf ? row1 : row0;
-        const int off = core_off(row, 8 * j, kD);
-        *reinterpret_cast<uint4*>(opb + 16384 + off) = vw[hf];       // v goes on to the products as it is
-        const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
-        const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
-        const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
-        const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
-        // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
-        const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
-        const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
-        __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
-          const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
-          const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
-          const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
-          const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
-          const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
-          const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
-          kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
-          qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
-          kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
-          qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
-          kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
-        }
-        auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
-          return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
-                            *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
-        };
-        *reinterpret_cast<uint4*>(opb + off) = as_u4(kpm);
-        *reinterpret_cast<uint4*>(opb + 8192 + off) = as_u4(qpm);
-        *reinterpret_cast<uint4*>(opa + off) = as_u4(kmm);
-        st_global_16(rec_dst + kRecQP + off, as_u4(qp));
-        st_global_16(rec_dst + kRecKR + off, as_u4(kr));
-      }
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (t == 0) PTRACE(n, 3);
-    if (lane == 0) mbar_arrive(bar(B_ELEM_DONE + slot));
-  }
-  return failed;
-}
-
-__global__ void __launch_bounds__(kThreads, 1)
-prepare_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v,
-                  const __grid_constant__ Params prm) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const uint32_t sbase = smem_u32(smem);
-  const PrepParams& p = prm.p;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
-  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
-
-  // items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... below the number of (chunk, head) pairs that exist
-  long long n_eff = prm.n_items_bound;
-  if (p.cu_seqlens != nullptr) n_eff = static_cast<long long>(p.chunk_prefix[p.N]) * p.H;
-  if (n_eff > prm.n_items_bound) n_eff = prm.n_items_bound;
-  const int my_items = n_eff > blockIdx.x ? static_cast<int>((n_eff - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
-
-  if (tid == 0) {
-    *abort_flag = 0;
-#pragma unroll
-    for (int i = 0; i < B_COUNT; ++i) {
-      const int count = (i >= B_STG_EMPTY && i < B_OPB_EMPTY) || i >= B_GROUP ? 8
-                        : (i >= B_D1_EMPTY && i < B_TBT_FULL)                 ? 2
-                        : (i >= B_D2_EMPTY && i < B_OUT_FULL)                 ? 4
-                        : (i >= B_OUT_FULL && i < B_OUT_FREE)                 ? 5
-                                                                              : 1;
-      mbar_init(bar(i), count);
-    }
-    fence_mbar_init();
-    prefetch_tensormap(&tm_q);
-    prefetch_tensormap(&tm_k);
-    prefetch_tensormap(&tm_g);
-    prefetch_tensormap(&tm_v);
-  }
-  if (warp == 3) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  bool failed;
-  if (warp == 2) failed = producer_and_second_products(smem, tmem, prm, &tm_q, &tm_k, &tm_g, &tm_v, my_items);
-  else if (warp == 3) failed = first_products(smem, tmem, prm, my_items);
-  else if (warp == 0 || warp == 4) failed = inverse_warp(smem, tmem, prm, my_items);
-  else if (warp == 1) failed = m_warp(smem, tmem, prm, my_items);
-  else if (warp < kElemWarp0) failed = output_warp(smem, tmem, prm, my_items);
-  else failed = element_warp(smem, tmem, prm, my_items);
-
-  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
-
-  // ---- common exit: every thread arrives here, tensor memory goes back ---------------------------------------------
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 3) {
-    tc_fence_after();
-    tmem_dealloc(tmem, kTmemCols);
-  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -797,10 +105,597 @@ bool make_map(CUtensorMap* map, const void* base, int64_t T_total, int H) {
 }  // namespace prep_tc
 
 // =====================================================================================================================
-// The same stage with the structure of the default kernel: one CTA of eight warps per (chunk, head) item, four CTAs per
-// SM, every warp doing element-wise work, phases separated by CTA-wide barriers -- and the data path of the kernel
-// above: TMA tile loads, the intra-chunk products and w' / u' on tcgen05 with TMEM accumulators (128 columns per CTA).
-// Other resident CTAs fill the waits of the serial part (first products -> inverse on one warp -> second products).
+// The pipelined kernel: a short software pipeline inside each CTA.  Eight element warps do every item's element-wise
+// work in lock step, and a ninth warp owns the serial part (A from tensor memory, T = (I + A)^-1, TB^T, issue of the
+// second products) of the item the element warps have just left.  Three CTAs per SM, each a loop over items
+// blockIdx.x, blockIdx.x + gridDim.x, ...; two 32 KB operand buffers per CTA alternate between consecutive items.
+//
+//   element warps, iteration i:  wait tiles(i) | sums of squares, gate, running sums | barrier | decayed operands over the
+//                                tiles, QP / KR / E to the record | barrier | one thread: first products(i) -> D1[i & 1]
+//                                | then item i - 1: wait D2 | WP, UP over the dead QPm / KMm of its buffer, MQK | barrier |
+//                                one thread: bulk stores(i - 1), then the tile loads of item i + 1 into that buffer
+//   matrix warp, item i:         decode item i + 2 and ask the L2 for its tiles | sigmoid(beta) | wait D1[i & 1] |
+//                                A -> T -> TB^T in the dead QPm / KMm of buffer i & 1 | second products(i) -> D2
+// What sets the speed is how many element warps of an SM have work at the same time, not the length of any one of
+// these chains: a ten-warp form with a warp of its own for every single-thread issue job, a form with three buffers
+// and two CTAs per SM, and one with two matrix warps all ran at the same 3.7 to 4.2 thousand cycles per item and SM.
+// Tensor memory: D1 twice (its M half is read one iteration later), D2 once (guarded by a "read" barrier).
+namespace prep_pipe {
+
+using prep_tc::tma_load_3d;
+using prep_tc::tma_prefetch_3d;
+using prep_tc::tmem_ld_16x256b_x4;
+using prep_tc::stsm_x4_trans;
+using prep_tc::st_global_16;
+
+constexpr int kElemThreads = 256;
+constexpr int kMatrixWarp = 8;
+constexpr int kThreads = 288;
+constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kColD1 = 0;            // 2 buffers x 32 columns: lanes 0-31 A, 32-63 M
+constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
+constexpr int kBufBytes = 32768;          // tiles q | k | g | v, then KPm | QPm | KMm | VC (8192 each)
+constexpr int kSmBuf = 0;
+constexpr int kLdA = 36;
+constexpr int kOffA = 8192;               // inside a buffer after the first products: fp32 A [32][36] over QPm
+constexpr int kOffT = 16384;              // fp32 T [32][36] over KMm
+constexpr int kOffTbt = 16384 + 6144;     // TB^T bf16 [32][32], core layout
+constexpr int kSmMqk = 2 * kBufBytes;     // MQK bf16 [32][32] on its way to the record
+constexpr int kSmSsq = kSmMqk + 2048;     // [2][32][4] partial sums of squares
+constexpr int kSmEx = kSmSsq + 1024;      // 2 items x [2][128] 2^(sub-block total)
+constexpr int kSmInfo = kSmEx + 2048;     // 4 items x {t0, len, h, gc, 2^A_log / 2}
+constexpr int kSmBias = kSmInfo + 128;    // 2 items x dt_bias[h][128] (arrives with the tiles)
+constexpr int kSmBars = kSmBias + 1024;
+constexpr int kSmMisc = kSmBars + 64;
+constexpr int kSmemBytes = 71 * 1024;
+static_assert(kSmMisc + 16 <= kSmemBytes, "shared memory plan");
+static_assert(3 * (kSmemBytes + 1024) <= 227 * 1024, "three CTAs per SM");
+static_assert(32 * kLdA * 4 <= 6144, "A and T fit before TB^T");
+enum { B_LOAD = 0 /*[2]*/, B_D1 = 2 /*[2]*/, B_D2 = 4, B_D2_READ = 5, B_COUNT = 6 };
+
+struct ItemInfo {
+  long long t0;
+  int len, h, gc, pad[3];
+};
+static_assert(sizeof(ItemInfo) == 32, "item info");
+
+__device__ __forceinline__ ItemInfo decode_item(const PrepParams& p, unsigned item) {
+  ItemInfo r;
+  r.h = static_cast<int>(item % static_cast<unsigned>(p.H));
+  r.gc = static_cast<int>(item / static_cast<unsigned>(p.H));
+  // half of exp(A_log[h]): the per-head factor of the gate, once per item instead of once per thread
+  r.pad[0] = __float_as_int(0.5f * ex2f(__ldg(p.A_log + r.h) * kLog2e));
+  r.pad[1] = r.pad[2] = 0;
+  if (p.cu_seqlens != nullptr) {
+    int lo = 0, hi = p.N - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.chunk_prefix[mid] <= r.gc) lo = mid; else hi = mid - 1;
+    }
+    long long bos = p.cu_seqlens[lo], eos = p.cu_seqlens[lo + 1];
+    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
+    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
+    r.t0 = bos + static_cast<long long>(r.gc - p.chunk_prefix[lo]) * kChunk;
+    const long long rem = eos - r.t0;
+    r.len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  } else {
+    const unsigned cps = static_cast<unsigned>((p.T + kChunk - 1) / kChunk);
+    const unsigned n = static_cast<unsigned>(r.gc) / cps, lc = static_cast<unsigned>(r.gc) - n * cps;
+    r.t0 = static_cast<long long>(n) * p.T + static_cast<long long>(lc) * kChunk;
+    const long long rem = p.T - static_cast<long long>(lc) * kChunk;
+    r.len = rem < kChunk ? static_cast<int>(rem) : kChunk;
+  }
+  return r;
+}
+
+// rendezvous of the element warps; returns whether any of them has given up
+__device__ __forceinline__ bool elem_barrier_any(bool failed) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(any)
+      : "r"(static_cast<uint32_t>(failed))
+      : "memory");
+  return any != 0;
+}
+
+__global__ void __launch_bounds__(kThreads, 3)
+prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p,
+                    long long* trace) {
+  (void)trace;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
+  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
+  auto info_of = [&](int it) { return reinterpret_cast<ItemInfo*>(smem + kSmInfo + (it & 3) * 32); };
+  float* s_ssq = reinterpret_cast<float*>(smem + kSmSsq);
+
+  const unsigned total_items = static_cast<unsigned>(p.cu_seqlens != nullptr ? p.chunk_prefix[p.N] : p.total_chunks) * static_cast<unsigned>(p.H);
+  if (blockIdx.x >= total_items) return;
+  const int n_it = static_cast<int>((total_items - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  if ((sbase & 1023u) != 0u) {       // the swizzled tiles need this alignment: report instead of computing garbage
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+    return;
+  }
+
+  // the tile loads of one item into one buffer (one thread)
+  auto issue_load = [&](int it) {
+    const ItemInfo* f = info_of(it);
+    const uint32_t full = bar(B_LOAD + (it & 1));
+    const uint32_t dst = sbase + kSmBuf + (it & 1) * kBufBytes;
+    const int tc = static_cast<int>(f->t0), h = f->h;
+    mbar_arrive_expect_tx(full, kBufBytes + 512);
+    bulk_g2s(sbase + kSmBias + (it & 1) * 512, p.dt_bias + static_cast<size_t>(h) * kD, 512, full);
+    tma_load_3d(dst, &tm_q, 0, h, tc, full);
+    tma_load_3d(dst + 4096, &tm_q, 64, h, tc, full);
+    tma_load_3d(dst + 8192, &tm_k, 0, h, tc, full);
+    tma_load_3d(dst + 12288, &tm_k, 64, h, tc, full);
+    tma_load_3d(dst + 16384, &tm_g, 0, h, tc, full);
+    tma_load_3d(dst + 20480, &tm_g, 64, h, tc, full);
+    tma_load_3d(dst + 24576, &tm_v, 0, h, tc, full);
+    tma_load_3d(dst + 28672, &tm_v, 64, h, tc, full);
+  };
+  // decode item `it` into its info slot and ask the L2 for its tiles (one thread, an iteration ahead of the load)
+  auto decode_and_prefetch = [&](int it) {
+    const ItemInfo f = decode_item(p, blockIdx.x + static_cast<unsigned>(it) * gridDim.x);
+    *info_of(it) = f;
+    const int tc = static_cast<int>(f.t0);
+    tma_prefetch_3d(&tm_q, 0, f.h, tc);
+    tma_prefetch_3d(&tm_q, 64, f.h, tc);
+    tma_prefetch_3d(&tm_k, 0, f.h, tc);
+    tma_prefetch_3d(&tm_k, 64, f.h, tc);
+    tma_prefetch_3d(&tm_g, 0, f.h, tc);
+    tma_prefetch_3d(&tm_g, 64, f.h, tc);
+    tma_prefetch_3d(&tm_v, 0, f.h, tc);
+    tma_prefetch_3d(&tm_v, 64, f.h, tc);
+  };
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(B_LOAD), 1);
+    mbar_init(bar(B_LOAD + 1), 1);
+    mbar_init(bar(B_D1), 1);
+    mbar_init(bar(B_D1 + 1), 1);
+    mbar_init(bar(B_D2), 1);
+    mbar_init(bar(B_D2_READ), 8);
+    fence_mbar_init();
+    *info_of(0) = decode_item(p, blockIdx.x);
+    issue_load(0);
+    if (n_it > 1) {
+      *info_of(1) = decode_item(p, blockIdx.x + gridDim.x);
+      issue_load(1);
+    }
+    if (n_it > 2) decode_and_prefetch(2);
+  }
+  if (warp == kMatrixWarp) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool failed = false;
+
+  if (warp == kMatrixWarp) {
+    // ===== matrix warp ====================================================================================================
+    int it = 0;
+    for (; it < n_it; ++it) {
+      const int b = it & 1;
+      uint8_t* buf = smem + kSmBuf + b * kBufBytes;
+      float* sA = reinterpret_cast<float*>(buf + kOffA);
+      float* sT = reinterpret_cast<float*>(buf + kOffT);
+      float* sX = sA + 16;
+      // the load barrier of this item has an arrival by the thread that wrote the item's info: acquire it
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
+      // this warp has time to spare: it decodes the item after next and asks the L2 for its tiles (its info slot was
+      // last read when item it - 2 went to the record, an iteration ago)
+      if (lane == 0 && it >= 1 && it + 2 < n_it) decode_and_prefetch(it + 2);
+      __syncwarp();
+      const ItemInfo f = *info_of(it);
+      const float bi = lane < f.len ? sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(f.t0 + lane) * p.H + f.h])) : 0.f;
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
+      tc_fence_after();
+      {
+        uint32_t a0[32];
+        tmem_ld32(tmem + kColD1 + 32 * b, a0);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          float4 r;
+          r.x = (4 * q4 + 0 < lane) ? __uint_as_float(a0[4 * q4 + 0]) * bi : 0.f;
+          r.y = (4 * q4 + 1 < lane) ? __uint_as_float(a0[4 * q4 + 1]) * bi : 0.f;
+          r.z = (4 * q4 + 2 < lane) ? __uint_as_float(a0[4 * q4 + 2]) * bi : 0.f;
+          r.w = (4 * q4 + 3 < lane) ? __uint_as_float(a0[4 * q4 + 3]) * bi : 0.f;
+          *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
+        }
+      }
+      __syncwarp();
+      {
+        // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
+        const int bb = lane >> 4, c = lane & 15;
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            if (4 * q4 < i) {
+              const float4 a4 = *reinterpret_cast<const float4*>(sA + (bb * 16 + i) * kLdA + bb * 16 + 4 * q4);
+              part[q4] = fmaf(a4.x, x[4 * q4], part[q4]);
+              part[q4] = fmaf(a4.y, x[4 * q4 + 1], part[q4]);
+              part[q4] = fmaf(a4.z, x[4 * q4 + 2], part[q4]);
+              part[q4] = fmaf(a4.w, x[4 * q4 + 3], part[q4]);
+            }
+          }
+          x[i] = ((i == c) ? 1.f : 0.f) - ((part[0] + part[1]) + (part[2] + part[3]));
+          sT[(bb * 16 + i) * kLdA + bb * 16 + c] = x[i];
+        }
+      }
+      __syncwarp();
+      {
+        // T_10 = -T_11 (A_10 T_00): two 16x16x16 products in tf32 on mma.sync, fp32 accumulation
+        const int g = lane >> 2, t4 = lane & 3;
+        auto small_product = [&](const float* A, const float* B, float* D, float sign) {
+          float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            const int k0 = 8 * ks;
+            const uint32_t f0 = to_tf32(A[g * kLdA + k0 + t4]), f1 = to_tf32(A[(g + 8) * kLdA + k0 + t4]);
+            const uint32_t f2 = to_tf32(A[g * kLdA + k0 + t4 + 4]), f3 = to_tf32(A[(g + 8) * kLdA + k0 + t4 + 4]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+              mma_tf32_1688(acc[nt], f0, f1, f2, f3, to_tf32(B[(k0 + t4) * kLdA + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLdA + 8 * nt + g]));
+          }
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            *reinterpret_cast<float2*>(D + g * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+            *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+          }
+        };
+        small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
+        __syncwarp();
+        small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
+      }
+      __syncwarp();
+      {
+        // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c (zero above the diagonal), bf16
+        uint8_t* row = buf + kOffTbt + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i0 = 8 * cb + 2 * e;
+            const float v0 = (i0 >= lane) ? sT[i0 * kLdA + lane] * bi : 0.f;
+            const float v1 = (i0 + 1 >= lane) ? sT[(i0 + 1) * kLdA + lane] * bi : 0.f;
+            w[e] = pack_bf16(v0, v1);
+          }
+          *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      // D2 still holds the previous item until the element warps have read it
+      if (it >= 1 && !__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D2_READ), (it - 1) & 1, abort_flag))) { failed = true; break; }
+      if (lane == 0) {
+        constexpr uint32_t idesc2 = umma_idesc_bf16(128, 32, 1, 1);
+        tc_fence_after();
+        const uint32_t bs = sbase + kSmBuf + b * kBufBytes;
+        const uint64_t ak = umma_desc(bs, 2048, 128), av = umma_desc(bs + 24576, 2048, 128);
+        const uint64_t bt = umma_desc(bs + kOffTbt, 512, 128);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          umma_ss(tmem + kColD2, ak + ks * 256, bt + ks * 64, idesc2, ks != 0);
+          umma_ss(tmem + kColD2 + 32, av + ks * 256, bt + ks * 64, idesc2, ks != 0);
+        }
+        umma_commit(bar(B_D2));
+      }
+      __syncwarp();
+    }
+    if (lane == 0 && it > 0 && (failed || *abort_flag > 0)) {
+      // (giving up; every way out of the loop lies before the issue, so items 0 .. it - 1 were issued) the second
+      // products issued last: their arrival must land before the barrier's memory goes away
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(bar(B_D2), (it - 1) & 1))
+        if (globaltimer_ns() - t0 > 20000000ull) break;
+    }
+  } else {
+    // ===== element warps ==================================================================================================
+    const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
+    const int row0 = sb * 16 + r8, row1 = row0 + 8;
+    const int hh = j >> 3, cj = j & 7;
+    const int q = warp & 3;
+    int loads_issued = n_it > 1 ? 2 : 1;     // (thread 0)
+
+    // item jt (the previous iteration's): WP, UP, MQK out of tensor memory, then to the record; the thread that stores
+    // them goes on to load the item after next into the buffer this frees
+    auto output = [&](int jt) {
+      const int pb = jt & 1;
+      uint8_t* buf = smem + kSmBuf + pb * kBufBytes;
+      const float* s_ex = reinterpret_cast<const float*>(smem + kSmEx + pb * 1024);
+      const bool ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(B_D2), jt & 1, abort_flag));
+      if (!ok) {
+        failed = true;
+      } else {
+        tc_fence_after();
+        const uint32_t tq = tmem + (static_cast<uint32_t>(q * 32) << 16) + kColD2;
+        if (warp < 4) {
+          uint32_t f0[16], f1[16];
+          tmem_ld_16x256b_x4(tq, f0);
+          tmem_ld_16x256b_x4(tq + (16u << 16), f1);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_D2_READ));
+          const uint32_t wp = sbase + kSmBuf + pb * kBufBytes + 8192;
+          const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t(&f)[16] = half ? f1 : f0;
+            const int k0 = 32 * q + 16 * half;
+            const float ca = s_ex[k0 + (lane >> 2)], cb = s_ex[k0 + 8 + (lane >> 2)];      // back from "relative to the sub-block boundary"
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp) {
+              uint32_t w[4];
+#pragma unroll
+              for (int jj = 0; jj < 2; ++jj) {
+                const int jt4 = 2 * jp + jj;
+                w[2 * jj] = pack_bf16(__uint_as_float(f[4 * jt4]) * ca, __uint_as_float(f[4 * jt4 + 1]) * ca);
+                w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * jt4 + 2]) * cb, __uint_as_float(f[4 * jt4 + 3]) * cb);
+              }
+              const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
+              stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
+            }
+          }
+        } else {
+          uint32_t u[32];
+          tmem_ld32(tq + 32, u);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_D2_READ));
+          const int v = 32 * q + lane;
+          uint8_t* row = buf + 16384 + (v >> 3) * 512 + (v & 7) * 16;
+#pragma unroll
+          for (int cb = 0; cb < 4; ++cb)
+            *reinterpret_cast<uint4*>(row + cb * 128) =
+                make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
+                           pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
+          if (warp == 5) {
+            // tril(q+ k-^T) -> MQK (lanes 32-63 of D1; complete since before the second products were issued)
+            if (__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + pb), (jt >> 1) & 1, abort_flag))) {
+              tc_fence_after();
+              tmem_ld32(tmem + (32u << 16) + kColD1 + 32 * pb, u);
+              tmem_wait_ld();
+              tc_fence_before();
+              uint8_t* mrow = smem + kSmMqk + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+              for (int cb = 0; cb < 4; ++cb) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int c = 8 * cb + 2 * e;
+                  w[e] = pack_bf16((c <= lane) ? __uint_as_float(u[c]) : 0.f, (c + 1 <= lane) ? __uint_as_float(u[c + 1]) : 0.f);
+                }
+                *reinterpret_cast<uint4*>(mrow + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+              failed = true;
+            }
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      const bool any = elem_barrier_any(failed);
+      if (tid == 0 && !any) {
+        const ItemInfo* f = info_of(jt);
+        uint8_t* const rec = p.records + (static_cast<size_t>(f->h) * p.total_chunks + f->gc) * kRecBytes;
+        const uint32_t bs = sbase + kSmBuf + pb * kBufBytes;
+        bulk_s2g(rec + kRecMQK, sbase + kSmMqk, 2048);
+        bulk_s2g(rec + kRecWP, bs + 8192, 8192);
+        bulk_s2g(rec + kRecUP, bs + 16384, 8192);
+        bulk_commit();
+        bulk_wait_read0();
+        if (jt + 2 < n_it) {
+          issue_load(jt + 2);
+          ++loads_issued;
+        }
+      }
+      return any;
+    };
+
+    bool any = false;
+    int it = 0;
+    for (; it <= n_it && !any; ++it) {
+      if (it < n_it) {
+      const int b = it & 1;
+      uint8_t* buf = smem + kSmBuf + b * kBufBytes;
+      float* s_ex = reinterpret_cast<float*>(smem + kSmEx + b * 1024);
+      if (!mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag)) failed = true;
+      const ItemInfo f = *info_of(it);
+      const int h = f.h, len = f.len;
+      const float ha = __int_as_float(f.pad[0]);
+      const float4 b0 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j);
+      const float4 b1 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j + 16);
+      uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + f.gc) * kRecBytes;
+
+      // ---- sums of squares, gate and its running sum ----------------------------------------------------------------
+      uint4 qw[2], kw[2], vw[2];
+      float G[2][8];
+      {
+        const uint8_t* stg = buf + hh * 4096;
+        const int sw = (cj ^ r8) << 4;
+        const bool valid0 = row0 < len, valid1 = row1 < len;
+        const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+        uint4 gw[2];
+        qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
+        qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
+        kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
+        kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
+        gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
+        gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
+        vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
+        vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
+        if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
+        if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
+        const float hgs = 0.5f * p.gate_scale;
+        const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int row = hf ? row1 : row0;
+          float e8[8], sq = 0.f, sk = 0.f;
+          unpack8(qw[hf], e8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sq = fmaf(e8[i], e8[i], sq);
+          unpack8(kw[hf], e8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sk = fmaf(e8[i], e8[i], sk);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+          sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+          sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+          if (lane < 8) {
+            s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
+            s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
+          }
+          unpack8(gw[hf], e8);
+          const bool valid = hf ? valid1 : valid0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float x = valid ? fmaf(tanh_approx(fmaf(e8[i], ha, hab[i])), hgs, hgs) : 0.f;
+#pragma unroll
+            for (int d = 1; d < 8; d <<= 1) {
+              const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
+              if (r8 >= d) x += y;
+            }
+            G[hf][i] = x;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
+        float tot[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
+        if (sb == 0) {      // exponents of sub-block 0 become relative to its end
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
+        }
+        if (r8 == 7) {      // 2^(sub-block total) per channel, once for the CTA
+          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
+          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
+        }
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");      // every thread holds its share of the tiles; sums and totals are complete
+
+      // ---- decayed operands over the tiles, record parts that are final now straight to global memory ---------------
+      {
+        if (sb == 0 && r8 == 0) {
+          const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
+          const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
+          float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
+          *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
+          *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
+        }
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int row = hf ? row1 : row0;
+          const int off = core_off(row, 8 * j, kD);
+          *reinterpret_cast<uint4*>(buf + 24576 + off) = vw[hf];       // v goes on to the products as it is
+          const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
+          const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
+          const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
+          const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
+          // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
+          const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
+          const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
+          __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
+            const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
+            const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
+            const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
+            const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
+            const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
+            const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
+            kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
+            qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
+            kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
+            qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
+            kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
+          }
+          auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
+            return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
+                              *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
+          };
+          *reinterpret_cast<uint4*>(buf + off) = as_u4(kpm);
+          *reinterpret_cast<uint4*>(buf + 8192 + off) = as_u4(qpm);
+          *reinterpret_cast<uint4*>(buf + 16384 + off) = as_u4(kmm);
+          st_global_16(rec_dst + kRecQP + off, as_u4(qp));
+          st_global_16(rec_dst + kRecKR + off, as_u4(kr));
+        }
+      }
+      fence_proxy_async_smem();
+      any = elem_barrier_any(failed);
+      if (any) break;
+      // ---- first products [A; M] = [KPm; QPm] KMm^T (rows 64-127 of the A operand are KMm and VC: lanes nobody reads) --
+      if (tid == 0) {
+        constexpr uint32_t idesc1 = umma_idesc_bf16(128, 32, 0, 0);
+        tc_fence_after();
+        const uint32_t bs = sbase + kSmBuf + b * kBufBytes;
+        const uint64_t a = umma_desc(bs, 128, 2048);
+        const uint64_t bd = umma_desc(bs + 16384, 128, 2048);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) umma_ss(tmem + kColD1 + 32 * b, a + i * 16, bd + i * 16, idesc1, i > 0);
+        umma_commit(bar(B_D1 + b));
+      }
+      }
+      if (it >= 1) any = output(it - 1);
+    }
+    if (any) failed = true;
+    if (tid == 0 && (failed || *abort_flag > 0)) {
+      // wait (bounded) for loads still in flight so that the CTA does not exit under them
+      for (int n = loads_issued > 2 ? loads_issued - 2 : 0; n < loads_issued; ++n) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar(B_LOAD + (n & 1)), (n >> 1) & 1))
+          if (globaltimer_ns() - t0 > 20000000ull) break;
+      }
+      // ... and for the first products issued last: their arrival must land before the barrier's memory goes away
+      // (leaving at the rendezvous, before the issue, keeps `it`; leaving after an output step has advanced it)
+      const int issued1 = it < n_it ? it : n_it;
+      if (issued1 > 0) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar(B_D1 + ((issued1 - 1) & 1)), ((issued1 - 1) >> 1) & 1))
+          if (globaltimer_ns() - t0 > 20000000ull) break;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
+  if (warp == kMatrixWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace prep_pipe
+
+// =====================================================================================================================
+// The one-CTA-per-item kernel: eight warps per (chunk, head) item, four CTAs per SM, every warp doing element-wise
+// work, phases separated by CTA-wide barriers, on the data path of the kernel above (TMA tile loads, the intra-chunk
+// products and w' / u' on tcgen05 with TMEM accumulators, 128 columns per CTA).  Other resident CTAs fill the waits
+// of the serial part (first products -> inverse on one warp -> second products).  About a tenth slower than the
+// pipelined kernel; no loop, no buffer reuse: the form to compare against.
 namespace prep_tc4 {
 
 using prep_tc::tma_load_3d;
@@ -812,7 +707,7 @@ using prep_tc::st_global_16;
 constexpr int kThreads = 256;
 constexpr uint32_t kTmemCols = 128;
 constexpr unsigned kGridY = 32768;        // chunks of a packed batch per grid row of the y dimension
-constexpr uint32_t kColD1 = 0;            // 2 accumulators x 32 columns: rows 0-31 A, 32-63 M
+constexpr uint32_t kColD1 = 0;            // 32 columns: lanes 0-31 A, 32-63 M
 constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
 // shared memory (bytes).  [0, 32768): the staged q, k, g, v tiles (two [32 tok][128 B] swizzled halves each), then, once
 // every thread holds its share in registers, KPm | QPm | KMm | VC (core layout [32][128], 8192 each); after the first
@@ -1069,10 +964,7 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint64_t a = umma_desc(sbase + kSmX, 128, 2048);
     const uint64_t b = umma_desc(sbase + kSmX + 16384, 128, 2048);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      umma_ss(tmem + kColD1, a + i * 16, b + i * 16, idesc1, i > 0);
-      umma_ss(tmem + kColD1 + 32, a + (4 + i) * 16, b + (4 + i) * 16, idesc1, i > 0);
-    }
+    for (int i = 0; i < 8; ++i) umma_ss(tmem + kColD1, a + i * 16, b + i * 16, idesc1, i > 0);
     umma_commit(bar(B_D1));
     P4TRACE(4);
   }
@@ -1084,17 +976,16 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (lane == 0) P4TRACE(5);
       const float bi = s_beta[lane];
       {
-        uint32_t a0[32], a1[32];
+        uint32_t a0[32];
         tmem_ld32(tmem + kColD1, a0);
-        tmem_ld32(tmem + kColD1 + 32, a1);
         tmem_wait_ld();
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
           float4 r;
-          r.x = (4 * q4 + 0 < lane) ? (__uint_as_float(a0[4 * q4 + 0]) + __uint_as_float(a1[4 * q4 + 0])) * bi : 0.f;
-          r.y = (4 * q4 + 1 < lane) ? (__uint_as_float(a0[4 * q4 + 1]) + __uint_as_float(a1[4 * q4 + 1])) * bi : 0.f;
-          r.z = (4 * q4 + 2 < lane) ? (__uint_as_float(a0[4 * q4 + 2]) + __uint_as_float(a1[4 * q4 + 2])) * bi : 0.f;
-          r.w = (4 * q4 + 3 < lane) ? (__uint_as_float(a0[4 * q4 + 3]) + __uint_as_float(a1[4 * q4 + 3])) * bi : 0.f;
+          r.x = (4 * q4 + 0 < lane) ? __uint_as_float(a0[4 * q4 + 0]) * bi : 0.f;
+          r.y = (4 * q4 + 1 < lane) ? __uint_as_float(a0[4 * q4 + 1]) * bi : 0.f;
+          r.z = (4 * q4 + 2 < lane) ? __uint_as_float(a0[4 * q4 + 2]) * bi : 0.f;
+          r.w = (4 * q4 + 3 < lane) ? __uint_as_float(a0[4 * q4 + 3]) * bi : 0.f;
           *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
         }
       }
@@ -1176,9 +1067,8 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const bool ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1), 0, abort_flag));
     if (ok) {
       tc_fence_after();
-      uint32_t a0[32], a1[32];
+      uint32_t a0[32];
       tmem_ld32(tmem + (32u << 16) + kColD1, a0);
-      tmem_ld32(tmem + (32u << 16) + kColD1 + 32, a1);
       tmem_wait_ld();
       uint8_t* row = smem + kSmMqk + (lane >> 3) * 512 + (lane & 7) * 16;
 #pragma unroll
@@ -1187,8 +1077,8 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = 8 * cb + 2 * e;
-          const float v0 = (c <= lane) ? __uint_as_float(a0[c]) + __uint_as_float(a1[c]) : 0.f;
-          const float v1 = (c + 1 <= lane) ? __uint_as_float(a0[c + 1]) + __uint_as_float(a1[c + 1]) : 0.f;
+          const float v0 = (c <= lane) ? __uint_as_float(a0[c]) : 0.f;
+          const float v1 = (c + 1 <= lane) ? __uint_as_float(a0[c + 1]) : 0.f;
           w[e] = pack_bf16(v0, v1);
         }
         *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -1282,573 +1172,6 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 }  // namespace prep_tc4
 
-// =====================================================================================================================
-// The same stage as a short software pipeline inside each CTA: eight element warps that do every item's element-wise
-// work in lock step, and a ninth warp that owns the serial part (A from tensor memory, T = (I + A)^-1, TB^T, issue of the
-// second products) of the item the element warps have just left.  Three CTAs per SM, each a loop over items
-// blockIdx.x, blockIdx.x + gridDim.x, ...; two 32 KB operand buffers per CTA alternate between consecutive items.
-//
-//   element warps, iteration i:  wait tiles(i) | sums of squares, gate, running sums | barrier | decayed operands over the
-//                                tiles, QP / KR / E to the record | barrier | one thread: first products(i) -> D1[i & 1]
-//                                | then item i - 1: wait D2 | WP, UP over the dead QPm / KMm of its buffer, MQK | barrier |
-//                                one thread: bulk stores(i - 1), then the tile loads of item i + 1 into that buffer and an
-//                                L2 prefetch of item i + 2
-//   matrix warp, item i:         sigmoid(beta) | wait D1[i & 1] | A -> T -> TB^T in the dead QPm / KMm of buffer i & 1 |
-//                                second products(i) -> D2
-// Tensor memory: D1 twice (its M half is read one iteration later), D2 once (guarded by a "read" barrier).
-namespace prep_pipe {
-
-using prep_tc::tma_load_3d;
-using prep_tc::tma_prefetch_3d;
-using prep_tc::tmem_ld_16x256b_x4;
-using prep_tc::stsm_x4_trans;
-using prep_tc::st_global_16;
-
-constexpr int kElemThreads = 256;
-constexpr int kMatrixWarp = 8;
-constexpr int kThreads = 288;
-constexpr uint32_t kTmemCols = 128;
-constexpr uint32_t kColD1 = 0;            // 2 buffers x 32 columns: lanes 0-31 A, 32-63 M
-constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
-constexpr int kBufBytes = 32768;          // tiles q | k | g | v, then KPm | QPm | KMm | VC (8192 each)
-constexpr int kSmBuf = 0;
-constexpr int kLdA = 36;
-constexpr int kOffA = 8192;               // inside a buffer after the first products: fp32 A [32][36] over QPm
-constexpr int kOffT = 16384;              // fp32 T [32][36] over KMm
-constexpr int kOffTbt = 16384 + 6144;     // TB^T bf16 [32][32], core layout
-constexpr int kSmMqk = 2 * kBufBytes;     // MQK bf16 [32][32] on its way to the record
-constexpr int kSmSsq = kSmMqk + 2048;     // [2][32][4] partial sums of squares
-constexpr int kSmEx = kSmSsq + 1024;      // 2 items x [2][128] 2^(sub-block total)
-constexpr int kSmInfo = kSmEx + 2048;     // 4 items x {t0, len, h, gc, 2^A_log / 2}
-constexpr int kSmBias = kSmInfo + 128;    // 2 items x dt_bias[h][128] (arrives with the tiles)
-constexpr int kSmBars = kSmBias + 1024;
-constexpr int kSmMisc = kSmBars + 64;
-constexpr int kSmemBytes = 71 * 1024;
-static_assert(kSmMisc + 16 <= kSmemBytes, "shared memory plan");
-static_assert(3 * (kSmemBytes + 1024) <= 227 * 1024, "three CTAs per SM");
-static_assert(32 * kLdA * 4 <= 6144, "A and T fit before TB^T");
-enum { B_LOAD = 0 /*[2]*/, B_D1 = 2 /*[2]*/, B_D2 = 4, B_D2_READ = 5, B_COUNT = 6 };
-
-struct ItemInfo {
-  long long t0;
-  int len, h, gc, pad[3];
-};
-static_assert(sizeof(ItemInfo) == 32, "item info");
-
-__device__ __forceinline__ ItemInfo decode_item(const PrepParams& p, unsigned item) {
-  ItemInfo r;
-  r.h = static_cast<int>(item % static_cast<unsigned>(p.H));
-  r.gc = static_cast<int>(item / static_cast<unsigned>(p.H));
-  // half of exp(A_log[h]): the per-head factor of the gate, once per item instead of once per thread
-  r.pad[0] = __float_as_int(0.5f * ex2f(__ldg(p.A_log + r.h) * kLog2e));
-  r.pad[1] = r.pad[2] = 0;
-  if (p.cu_seqlens != nullptr) {
-    int lo = 0, hi = p.N - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (p.chunk_prefix[mid] <= r.gc) lo = mid; else hi = mid - 1;
-    }
-    long long bos = p.cu_seqlens[lo], eos = p.cu_seqlens[lo + 1];
-    bos = bos < 0 ? 0 : (bos > p.T_total ? p.T_total : bos);
-    eos = eos < bos ? bos : (eos > p.T_total ? p.T_total : eos);
-    r.t0 = bos + static_cast<long long>(r.gc - p.chunk_prefix[lo]) * kChunk;
-    const long long rem = eos - r.t0;
-    r.len = rem < kChunk ? static_cast<int>(rem) : kChunk;
-  } else {
-    const unsigned cps = static_cast<unsigned>((p.T + kChunk - 1) / kChunk);
-    const unsigned n = static_cast<unsigned>(r.gc) / cps, lc = static_cast<unsigned>(r.gc) - n * cps;
-    r.t0 = static_cast<long long>(n) * p.T + static_cast<long long>(lc) * kChunk;
-    const long long rem = p.T - static_cast<long long>(lc) * kChunk;
-    r.len = rem < kChunk ? static_cast<int>(rem) : kChunk;
-  }
-  return r;
-}
-
-// rendezvous of the element warps; returns whether any of them has given up
-__device__ __forceinline__ bool elem_barrier_any(bool failed) {
-  uint32_t any;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 p, %1, 0;\n\t"
-      "bar.red.or.pred q, 1, 256, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(any)
-      : "r"(static_cast<uint32_t>(failed))
-      : "memory");
-  return any != 0;
-}
-
-__global__ void __launch_bounds__(kThreads, 3)
-prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p,
-                    long long* trace) {
-  (void)trace;
-  extern __shared__ __align__(1024) uint8_t smem[];
-  const uint32_t sbase = smem_u32(smem);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmMisc + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmMisc);
-  auto bar = [&](int i) { return sbase + kSmBars + 8 * i; };
-  auto info_of = [&](int it) { return reinterpret_cast<ItemInfo*>(smem + kSmInfo + (it & 3) * 32); };
-  float* s_ssq = reinterpret_cast<float*>(smem + kSmSsq);
-
-  const unsigned total_items = static_cast<unsigned>(p.cu_seqlens != nullptr ? p.chunk_prefix[p.N] : p.total_chunks) * static_cast<unsigned>(p.H);
-  if (blockIdx.x >= total_items) return;
-  const int n_it = static_cast<int>((total_items - blockIdx.x + gridDim.x - 1) / gridDim.x);
-  if ((sbase & 1023u) != 0u) {       // the swizzled tiles need this alignment: report instead of computing garbage
-    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
-    return;
-  }
-
-  // the tile loads of one item into one buffer (one thread)
-  auto issue_load = [&](int it) {
-    const ItemInfo* f = info_of(it);
-    const uint32_t full = bar(B_LOAD + (it & 1));
-    const uint32_t dst = sbase + kSmBuf + (it & 1) * kBufBytes;
-    const int tc = static_cast<int>(f->t0), h = f->h;
-    mbar_arrive_expect_tx(full, kBufBytes + 512);
-    bulk_g2s(sbase + kSmBias + (it & 1) * 512, p.dt_bias + static_cast<size_t>(h) * kD, 512, full);
-    tma_load_3d(dst, &tm_q, 0, h, tc, full);
-    tma_load_3d(dst + 4096, &tm_q, 64, h, tc, full);
-    tma_load_3d(dst + 8192, &tm_k, 0, h, tc, full);
-    tma_load_3d(dst + 12288, &tm_k, 64, h, tc, full);
-    tma_load_3d(dst + 16384, &tm_g, 0, h, tc, full);
-    tma_load_3d(dst + 20480, &tm_g, 64, h, tc, full);
-    tma_load_3d(dst + 24576, &tm_v, 0, h, tc, full);
-    tma_load_3d(dst + 28672, &tm_v, 64, h, tc, full);
-  };
-  // decode item `it` into its info slot and ask the L2 for its tiles (one thread, an iteration ahead of the load)
-  auto decode_and_prefetch = [&](int it) {
-    const ItemInfo f = decode_item(p, blockIdx.x + static_cast<unsigned>(it) * gridDim.x);
-    *info_of(it) = f;
-    const int tc = static_cast<int>(f.t0);
-    tma_prefetch_3d(&tm_q, 0, f.h, tc);
-    tma_prefetch_3d(&tm_q, 64, f.h, tc);
-    tma_prefetch_3d(&tm_k, 0, f.h, tc);
-    tma_prefetch_3d(&tm_k, 64, f.h, tc);
-    tma_prefetch_3d(&tm_g, 0, f.h, tc);
-    tma_prefetch_3d(&tm_g, 64, f.h, tc);
-    tma_prefetch_3d(&tm_v, 0, f.h, tc);
-    tma_prefetch_3d(&tm_v, 64, f.h, tc);
-  };
-
-  if (tid == 0) {
-    *abort_flag = 0;
-    mbar_init(bar(B_LOAD), 1);
-    mbar_init(bar(B_LOAD + 1), 1);
-    mbar_init(bar(B_D1), 1);
-    mbar_init(bar(B_D1 + 1), 1);
-    mbar_init(bar(B_D2), 1);
-    mbar_init(bar(B_D2_READ), 8);
-    fence_mbar_init();
-    *info_of(0) = decode_item(p, blockIdx.x);
-    issue_load(0);
-    if (n_it > 1) {
-      *info_of(1) = decode_item(p, blockIdx.x + gridDim.x);
-      issue_load(1);
-    }
-    if (n_it > 2) decode_and_prefetch(2);
-  }
-  if (warp == kMatrixWarp) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  bool failed = false;
-
-  if (warp == kMatrixWarp) {
-    // ===== matrix warp ====================================================================================================
-    for (int it = 0; it < n_it; ++it) {
-      const int b = it & 1;
-      uint8_t* buf = smem + kSmBuf + b * kBufBytes;
-      float* sA = reinterpret_cast<float*>(buf + kOffA);
-      float* sT = reinterpret_cast<float*>(buf + kOffT);
-      float* sX = sA + 16;
-      // the load barrier of this item has an arrival by the thread that wrote the item's info: acquire it
-      if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
-      // this warp has time to spare: it decodes the item after next and asks the L2 for its tiles (its info slot was
-      // last read when item it - 2 went to the record, an iteration ago)
-      if (lane == 0 && it >= 1 && it + 2 < n_it) decode_and_prefetch(it + 2);
-      __syncwarp();
-      const ItemInfo f = *info_of(it);
-      const float bi = lane < f.len ? sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(f.t0 + lane) * p.H + f.h])) : 0.f;
-      if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
-      tc_fence_after();
-      {
-        uint32_t a0[32];
-        tmem_ld32(tmem + kColD1 + 32 * b, a0);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          float4 r;
-          r.x = (4 * q4 + 0 < lane) ? __uint_as_float(a0[4 * q4 + 0]) * bi : 0.f;
-          r.y = (4 * q4 + 1 < lane) ? __uint_as_float(a0[4 * q4 + 1]) * bi : 0.f;
-          r.z = (4 * q4 + 2 < lane) ? __uint_as_float(a0[4 * q4 + 2]) * bi : 0.f;
-          r.w = (4 * q4 + 3 < lane) ? __uint_as_float(a0[4 * q4 + 3]) * bi : 0.f;
-          *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
-        }
-      }
-      __syncwarp();
-      {
-        // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
-        const int bb = lane >> 4, c = lane & 15;
-        float x[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            if (4 * q4 < i) {
-              const float4 a4 = *reinterpret_cast<const float4*>(sA + (bb * 16 + i) * kLdA + bb * 16 + 4 * q4);
-              part[q4] = fmaf(a4.x, x[4 * q4], part[q4]);
-              part[q4] = fmaf(a4.y, x[4 * q4 + 1], part[q4]);
-              part[q4] = fmaf(a4.z, x[4 * q4 + 2], part[q4]);
-              part[q4] = fmaf(a4.w, x[4 * q4 + 3], part[q4]);
-            }
-          }
-          x[i] = ((i == c) ? 1.f : 0.f) - ((part[0] + part[1]) + (part[2] + part[3]));
-          sT[(bb * 16 + i) * kLdA + bb * 16 + c] = x[i];
-        }
-      }
-      __syncwarp();
-      {
-        // T_10 = -T_11 (A_10 T_00): two 16x16x16 products in tf32 on mma.sync, fp32 accumulation
-        const int g = lane >> 2, t4 = lane & 3;
-        auto small_product = [&](const float* A, const float* B, float* D, float sign) {
-          float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {
-            const int k0 = 8 * ks;
-            const uint32_t f0 = to_tf32(A[g * kLdA + k0 + t4]), f1 = to_tf32(A[(g + 8) * kLdA + k0 + t4]);
-            const uint32_t f2 = to_tf32(A[g * kLdA + k0 + t4 + 4]), f3 = to_tf32(A[(g + 8) * kLdA + k0 + t4 + 4]);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-              mma_tf32_1688(acc[nt], f0, f1, f2, f3, to_tf32(B[(k0 + t4) * kLdA + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLdA + 8 * nt + g]));
-          }
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            *reinterpret_cast<float2*>(D + g * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
-            *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
-          }
-        };
-        small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
-        __syncwarp();
-        small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
-      }
-      __syncwarp();
-      {
-        // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c (zero above the diagonal), bf16
-        uint8_t* row = buf + kOffTbt + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i0 = 8 * cb + 2 * e;
-            const float v0 = (i0 >= lane) ? sT[i0 * kLdA + lane] * bi : 0.f;
-            const float v1 = (i0 + 1 >= lane) ? sT[(i0 + 1) * kLdA + lane] * bi : 0.f;
-            w[e] = pack_bf16(v0, v1);
-          }
-          *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      // D2 still holds the previous item until the element warps have read it
-      if (it >= 1 && !__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D2_READ), (it - 1) & 1, abort_flag))) { failed = true; break; }
-      if (lane == 0) {
-        constexpr uint32_t idesc2 = umma_idesc_bf16(128, 32, 1, 1);
-        tc_fence_after();
-        const uint32_t bs = sbase + kSmBuf + b * kBufBytes;
-        const uint64_t ak = umma_desc(bs, 2048, 128), av = umma_desc(bs + 24576, 2048, 128);
-        const uint64_t bt = umma_desc(bs + kOffTbt, 512, 128);
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-          umma_ss(tmem + kColD2, ak + ks * 256, bt + ks * 64, idesc2, ks != 0);
-          umma_ss(tmem + kColD2 + 32, av + ks * 256, bt + ks * 64, idesc2, ks != 0);
-        }
-        umma_commit(bar(B_D2));
-      }
-      __syncwarp();
-    }
-  } else {
-    // ===== element warps ==================================================================================================
-    const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
-    const int row0 = sb * 16 + r8, row1 = row0 + 8;
-    const int hh = j >> 3, cj = j & 7;
-    const int q = warp & 3;
-    int loads_issued = n_it > 1 ? 2 : 1;     // (thread 0)
-
-    // item jt (the previous iteration's): WP, UP, MQK out of tensor memory, then to the record; the thread that stores
-    // them goes on to load the item after next into the buffer this frees
-    auto output = [&](int jt) {
-      const int pb = jt & 1;
-      uint8_t* buf = smem + kSmBuf + pb * kBufBytes;
-      const float* s_ex = reinterpret_cast<const float*>(smem + kSmEx + pb * 1024);
-      const bool ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(B_D2), jt & 1, abort_flag));
-      if (!ok) {
-        failed = true;
-      } else {
-        tc_fence_after();
-        const uint32_t tq = tmem + (static_cast<uint32_t>(q * 32) << 16) + kColD2;
-        if (warp < 4) {
-          uint32_t f0[16], f1[16];
-          tmem_ld_16x256b_x4(tq, f0);
-          tmem_ld_16x256b_x4(tq + (16u << 16), f1);
-          tmem_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(B_D2_READ));
-          const uint32_t wp = sbase + kSmBuf + pb * kBufBytes + 8192;
-          const int m = lane >> 3, r = lane & 7;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const uint32_t(&f)[16] = half ? f1 : f0;
-            const int k0 = 32 * q + 16 * half;
-            const float ca = s_ex[k0 + (lane >> 2)], cb = s_ex[k0 + 8 + (lane >> 2)];      // back from "relative to the sub-block boundary"
-#pragma unroll
-            for (int jp = 0; jp < 2; ++jp) {
-              uint32_t w[4];
-#pragma unroll
-              for (int jj = 0; jj < 2; ++jj) {
-                const int jt4 = 2 * jp + jj;
-                w[2 * jj] = pack_bf16(__uint_as_float(f[4 * jt4]) * ca, __uint_as_float(f[4 * jt4 + 1]) * ca);
-                w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * jt4 + 2]) * cb, __uint_as_float(f[4 * jt4 + 3]) * cb);
-              }
-              const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
-              stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
-            }
-          }
-        } else {
-          uint32_t u[32];
-          tmem_ld32(tq + 32, u);
-          tmem_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(B_D2_READ));
-          const int v = 32 * q + lane;
-          uint8_t* row = buf + 16384 + (v >> 3) * 512 + (v & 7) * 16;
-#pragma unroll
-          for (int cb = 0; cb < 4; ++cb)
-            *reinterpret_cast<uint4*>(row + cb * 128) =
-                make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
-                           pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
-          if (warp == 5) {
-            // tril(q+ k-^T) -> MQK (lanes 32-63 of D1; complete since before the second products were issued)
-            if (__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + pb), (jt >> 1) & 1, abort_flag))) {
-              tc_fence_after();
-              tmem_ld32(tmem + (32u << 16) + kColD1 + 32 * pb, u);
-              tmem_wait_ld();
-              tc_fence_before();
-              uint8_t* mrow = smem + kSmMqk + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-              for (int cb = 0; cb < 4; ++cb) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int c = 8 * cb + 2 * e;
-                  w[e] = pack_bf16((c <= lane) ? __uint_as_float(u[c]) : 0.f, (c + 1 <= lane) ? __uint_as_float(u[c + 1]) : 0.f);
-                }
-                *reinterpret_cast<uint4*>(mrow + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            } else {
-              failed = true;
-            }
-          }
-        }
-      }
-      fence_proxy_async_smem();
-      const bool any = elem_barrier_any(failed);
-      if (tid == 0 && !any) {
-        const ItemInfo* f = info_of(jt);
-        uint8_t* const rec = p.records + (static_cast<size_t>(f->h) * p.total_chunks + f->gc) * kRecBytes;
-        const uint32_t bs = sbase + kSmBuf + pb * kBufBytes;
-        bulk_s2g(rec + kRecMQK, sbase + kSmMqk, 2048);
-        bulk_s2g(rec + kRecWP, bs + 8192, 8192);
-        bulk_s2g(rec + kRecUP, bs + 16384, 8192);
-        bulk_commit();
-        bulk_wait_read0();
-        if (jt + 2 < n_it) {
-          issue_load(jt + 2);
-          ++loads_issued;
-        }
-      }
-      return any;
-    };
-
-    bool any = false;
-    for (int it = 0; it <= n_it && !any; ++it) {
-      if (it < n_it) {
-      const int b = it & 1;
-      uint8_t* buf = smem + kSmBuf + b * kBufBytes;
-      float* s_ex = reinterpret_cast<float*>(smem + kSmEx + b * 1024);
-      if (!mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag)) failed = true;
-      const ItemInfo f = *info_of(it);
-      const int h = f.h, len = f.len;
-      const float ha = __int_as_float(f.pad[0]);
-      const float4 b0 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j);
-      const float4 b1 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j + 16);
-      uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + f.gc) * kRecBytes;
-
-      // ---- sums of squares, gate and its running sum ----------------------------------------------------------------
-      uint4 qw[2], kw[2], vw[2];
-      float G[2][8];
-      {
-        const uint8_t* stg = buf + hh * 4096;
-        const int sw = (cj ^ r8) << 4;
-        const bool valid0 = row0 < len, valid1 = row1 < len;
-        const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
-        uint4 gw[2];
-        qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
-        qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
-        kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
-        kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
-        gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
-        gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
-        vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
-        vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
-        if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
-        if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
-        const float hgs = 0.5f * p.gate_scale;
-        const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int row = hf ? row1 : row0;
-          float e8[8], sq = 0.f, sk = 0.f;
-          unpack8(qw[hf], e8);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sq = fmaf(e8[i], e8[i], sq);
-          unpack8(kw[hf], e8);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sk = fmaf(e8[i], e8[i], sk);
-          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-          sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-          sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-          sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-          if (lane < 8) {
-            s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
-            s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
-          }
-          unpack8(gw[hf], e8);
-          const bool valid = hf ? valid1 : valid0;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float x = valid ? fmaf(tanh_approx(fmaf(e8[i], ha, hab[i])), hgs, hgs) : 0.f;
-#pragma unroll
-            for (int d = 1; d < 8; d <<= 1) {
-              const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
-              if (r8 >= d) x += y;
-            }
-            G[hf][i] = x;
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
-        float tot[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
-        if (sb == 0) {      // exponents of sub-block 0 become relative to its end
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
-        }
-        if (r8 == 7) {      // 2^(sub-block total) per channel, once for the CTA
-          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
-          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
-        }
-      }
-      asm volatile("bar.sync 1, 256;" ::: "memory");      // every thread holds its share of the tiles; sums and totals are complete
-
-      // ---- decayed operands over the tiles, record parts that are final now straight to global memory ---------------
-      {
-        if (sb == 0 && r8 == 0) {
-          const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
-          const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
-          float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
-          *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
-          *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
-        }
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int row = hf ? row1 : row0;
-          const int off = core_off(row, 8 * j, kD);
-          *reinterpret_cast<uint4*>(buf + 24576 + off) = vw[hf];       // v goes on to the products as it is
-          const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
-          const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
-          const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
-          const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
-          // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
-          const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
-          const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
-          __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
-#pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
-            const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
-            const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
-            const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
-            const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
-            const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
-            const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
-            kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
-            qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
-            kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
-            qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
-            kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
-          }
-          auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
-            return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
-                              *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
-          };
-          *reinterpret_cast<uint4*>(buf + off) = as_u4(kpm);
-          *reinterpret_cast<uint4*>(buf + 8192 + off) = as_u4(qpm);
-          *reinterpret_cast<uint4*>(buf + 16384 + off) = as_u4(kmm);
-          st_global_16(rec_dst + kRecQP + off, as_u4(qp));
-          st_global_16(rec_dst + kRecKR + off, as_u4(kr));
-        }
-      }
-      fence_proxy_async_smem();
-      any = elem_barrier_any(failed);
-      if (any) break;
-      // ---- first products [A; M] = [KPm; QPm] KMm^T (rows 64-127 of the A operand are KMm and VC: lanes nobody reads) --
-      if (tid == 0) {
-        constexpr uint32_t idesc1 = umma_idesc_bf16(128, 32, 0, 0);
-        tc_fence_after();
-        const uint32_t bs = sbase + kSmBuf + b * kBufBytes;
-        const uint64_t a = umma_desc(bs, 128, 2048);
-        const uint64_t bd = umma_desc(bs + 16384, 128, 2048);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) umma_ss(tmem + kColD1 + 32 * b, a + i * 16, bd + i * 16, idesc1, i > 0);
-        umma_commit(bar(B_D1 + b));
-      }
-      }
-      if (it >= 1) any = output(it - 1);
-    }
-    if (any) failed = true;
-    if (tid == 0 && (failed || *abort_flag > 0)) {
-      // wait (bounded) for loads still in flight so that the CTA does not exit under them
-      for (int n = loads_issued > 2 ? loads_issued - 2 : 0; n < loads_issued; ++n) {
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(bar(B_LOAD + (n & 1)), (n >> 1) & 1))
-          if (globaltimer_ns() - t0 > 20000000ull) break;
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (failed || *abort_flag > 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeout);
-  if (warp == kMatrixWarp) {
-    tc_fence_after();
-    tmem_dealloc(tmem, kTmemCols);
-  }
-}
-
-}  // namespace prep_pipe
-
 cudaError_t launch_prepare_pipe(const PrepParams& p, cudaStream_t stream) {
   if (p.total_chunks == 0 || p.H == 0 || p.T_total == 0) return cudaSuccess;
   CUtensorMap tq, tk, tg, tv;
@@ -1907,29 +1230,5 @@ cudaError_t launch_prepare_tc4(const PrepParams& p, cudaStream_t stream) {
 #ifdef FKDA_TUNING
 void set_prepare_trace(long long* buf) { prep_tc::g_trace = buf; }
 #endif
-
-cudaError_t launch_prepare_tc(const PrepParams& p, cudaStream_t stream) {
-  if (p.total_chunks == 0 || p.H == 0 || p.T_total == 0) return cudaSuccess;
-  CUtensorMap tq, tk, tg, tv;
-  if (!prep_tc::make_map(&tq, p.q, p.T_total, p.H) || !prep_tc::make_map(&tk, p.k, p.T_total, p.H) ||
-      !prep_tc::make_map(&tg, p.g, p.T_total, p.H) || !prep_tc::make_map(&tv, p.v, p.T_total, p.H))
-    return cudaErrorInvalidValue;
-  static SmemOptIn opt_in;
-  cudaError_t e = opt_in.ensure(prep_tc::prepare_tc_kernel, prep_tc::kSmemBytes);
-  if (e != cudaSuccess) return e;
-  prep_tc::Params prm;
-  prm.p = p;
-  const long long items = static_cast<long long>(p.total_chunks) * p.H;
-  prm.n_items_bound = static_cast<int>(items);
-#ifdef FKDA_TUNING
-  prm.trace = prep_tc::g_trace;
-#else
-  prm.trace = nullptr;
-#endif
-  const int sms = device_sm_count();
-  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
-  prep_tc::prepare_tc_kernel<<<grid, prep_tc::kThreads, prep_tc::kSmemBytes, stream>>>(tq, tk, tg, tv, prm);
-  return cudaGetLastError();
-}
 
 }  // namespace fkda

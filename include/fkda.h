@@ -47,18 +47,14 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
  * complete forward pass, just slower than the two-kernel path beyond that; the flag exists so that tests can walk
  * many blocks with it). */
 #define FKDA_FLAG_FUSED_ANY_T 0x40u
-/* The token-parallel stage runs on the TMA + tcgen05 kernel (csrc/fkda_prepare_tc.cu: tile loads by TMA, the
- * intra-chunk products on tcgen05 with accumulators in tensor memory, four CTAs per SM) whenever its grid can hold the
- * call (at most 65535 sequences of at most 65535 chunks each for equal lengths); this flag makes that a requirement
- * (the call fails instead of taking the mma.sync kernel). */
+/* The token-parallel stage runs on the pipelined TMA + tcgen05 kernel (csrc/fkda_prepare_tc.cu: tile loads by TMA, the
+ * intra-chunk products on tcgen05 with accumulators in tensor memory; three CTAs per SM, each a loop over (chunk, head)
+ * items with the serial part of an item on a ninth warp while the other eight are on the next item).  This flag selects
+ * the one-CTA-per-item form of that kernel instead (four CTAs per SM; at most 65535 sequences of at most 65535 chunks
+ * each for equal lengths, else the call fails).  Same operand records. */
 #define FKDA_FLAG_PREPARE_TCGEN05 0x80u
-/* The same stage on the persistent, warp-specialised form of that kernel (one CTA per SM; slower, kept for comparison). */
-#define FKDA_FLAG_PREPARE_TCGEN05_PERSISTENT 0x10000u
 /* The same stage on the earlier kernel (vectorised global loads, mma.sync products).  Same operand records. */
 #define FKDA_FLAG_PREPARE_MMA_SYNC 0x20000u
-/* The same stage on the pipelined form of the TMA + tcgen05 kernel (three CTAs per SM, each a loop over items with the
- * serial part of an item on a ninth warp while the other eight are on the next item). */
-#define FKDA_FLAG_PREPARE_PIPELINED 0x40000u
 /* Cut every sequence of the batch into n (2..255) runs walked in parallel, whatever the planner would
  * choose; the workspace must then be sized with fkda_get_workspace_size_flags.  Together with FKDA_FLAG_SCAN_PLAIN or
  * FKDA_FLAG_SCAN_LOOKAHEAD both passes over the runs use that recurrence kernel (otherwise each pass picks the faster

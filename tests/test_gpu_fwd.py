@@ -73,14 +73,14 @@ def test_golden_cases(name, flags):
     assert d_out <= (1e-2 if big else OUT_MAX_ABS) and d_st <= STATE_REL
 
 
-OTHER_PREPARE_KERNELS = {"mma_sync": F.FLAG_PREPARE_MMA_SYNC, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT}
+OTHER_PREPARE_KERNELS = {"mma_sync": F.FLAG_PREPARE_MMA_SYNC, "tcgen05_cta_per_item": F.FLAG_PREPARE_TCGEN05}
 
 
 @pytest.mark.parametrize("kernel", list(OTHER_PREPARE_KERNELS))
 @pytest.mark.parametrize("name", golden_names())
 def test_golden_cases_on_the_other_token_parallel_kernels(name, kernel):
-    """The token-parallel stage on the mma.sync kernel and on the persistent form of the TMA + tcgen05 kernel (the
-    default is the four-CTAs-per-SM TMA + tcgen05 kernel): same golden cases."""
+    """The token-parallel stage on the mma.sync kernel and on the one-CTA-per-item form of the TMA + tcgen05 kernel
+    (the default is the pipelined TMA + tcgen05 kernel): same golden cases."""
     x, ref_out, ref_fin = load_golden(name)
     fin_dtype = None if ref_fin is None else ref_fin.dtype
     out, fin = run_gpu(x, fin_dtype, OTHER_PREPARE_KERNELS[kernel] | F.FLAG_NO_FUSED_SHORT)
@@ -88,22 +88,21 @@ def test_golden_cases_on_the_other_token_parallel_kernels(name, kernel):
     check_against_f64(x, out, fin, f"{name}[{kernel} prepare]", big_state=big)
 
 
-def test_required_tcgen05_kernel_is_the_default_one():
-    """FLAG_PREPARE_TCGEN05 only turns the default choice into a requirement: same bits."""
+def test_the_two_tcgen05_kernels_write_the_same_bits():
+    """The pipelined kernel and the one-CTA-per-item kernel do the same arithmetic in the same order."""
     x = make_inputs(Workload("req", H=4, B=2, T=300, state_in="fp32", state_out="fp32", seed=65))
     o0, s0 = run_gpu(x, torch.float32)
     o1, s1 = run_gpu(x, torch.float32, F.FLAG_PREPARE_TCGEN05)
     assert torch.equal(o0.view(torch.int16), o1.view(torch.int16)) and torch.equal(s0, s1)
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_persistent", "tcgen05_pipelined"])
+@pytest.mark.parametrize("kernel", ["tcgen05_pipelined", "tcgen05_cta_per_item"])
 @pytest.mark.parametrize("case", ["fixed_tails", "varlen_ragged", "many_items", "long_repeat"])
 def test_tma_tcgen05_token_parallel_kernel_shapes(case, kernel):
     """Shapes that stress the TMA + tcgen05 kernels: ragged last chunks, many short sequences (items of every
     length), more items than one pass of the CTAs holds, and repeated calls that must be bit-reproducible; each
     against the fp64 oracle and against the mma.sync kernel."""
-    tc_flag = {"tcgen05": F.FLAG_PREPARE_TCGEN05, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT,
-               "tcgen05_pipelined": F.FLAG_PREPARE_PIPELINED}[kernel]
+    tc_flag = {"tcgen05_pipelined": 0, "tcgen05_cta_per_item": F.FLAG_PREPARE_TCGEN05}[kernel]
     if case == "fixed_tails":
         w = Workload("tc1", H=3, B=5, T=32 * 3 + 17, state_in="fp32", state_out="fp32", state_std=0.5, seed=61)
     elif case == "varlen_ragged":

@@ -86,7 +86,7 @@ FORMS = {
     "segmented_compact": F.FLAG_SCAN_PLAIN | F.FLAG_SEGMENTS(3),
     "simt": F.FLAG_SCAN_SIMT,
     "mma_sync_prepare": F.FLAG_PREPARE_MMA_SYNC,
-    "tcgen05_persistent_prepare": F.FLAG_PREPARE_TCGEN05_PERSISTENT,
+    "tcgen05_cta_per_item_prepare": F.FLAG_PREPARE_TCGEN05,
     "reference_rounding": F.FLAG_REFERENCE_ROUNDING,
 }
 

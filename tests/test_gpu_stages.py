@@ -47,13 +47,12 @@ def test_prologue_kernel():
     assert (bact.cpu().double() - br).abs().max() < 1e-3
 
 
-@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05", "tcgen05_persistent", "tcgen05_pipelined"])
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05_cta_per_item", "tcgen05_pipelined"])
 @pytest.mark.parametrize("case", ["fixed", "varlen", "strong_decay"])
 def test_prepare_records_match_fp64_operands(case, kernel):
-    """Operand records of the three token-parallel kernels (the default TMA + tcgen05 one, its persistent form and
-    the mma.sync one) against the fp64 chunk operands of the oracle."""
-    flags = {"mma_sync": F.FLAG_PREPARE_MMA_SYNC, "tcgen05": F.FLAG_PREPARE_TCGEN05, "tcgen05_persistent": F.FLAG_PREPARE_TCGEN05_PERSISTENT,
-             "tcgen05_pipelined": F.FLAG_PREPARE_PIPELINED}[kernel]
+    """Operand records of the three token-parallel kernels (the default pipelined TMA + tcgen05 one, its
+    one-CTA-per-item form and the mma.sync one) against the fp64 chunk operands of the oracle."""
+    flags = {"mma_sync": F.FLAG_PREPARE_MMA_SYNC, "tcgen05_cta_per_item": F.FLAG_PREPARE_TCGEN05, "tcgen05_pipelined": 0}[kernel]
     if case == "fixed":
         w = Workload("f", H=2, B=2, T=80, seed=11)
     elif case == "varlen":

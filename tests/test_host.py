@@ -129,7 +129,6 @@ def test_flag_constants_match_the_header():
     assert values["FKDA_FLAG_REFERENCE_ROUNDING"] == F.FLAG_REFERENCE_ROUNDING
     assert values["FKDA_FLAG_FUSED_ANY_T"] == F.FLAG_FUSED_ANY_T
     assert values["FKDA_FLAG_PREPARE_TCGEN05"] == F.FLAG_PREPARE_TCGEN05
-    assert values["FKDA_FLAG_PREPARE_TCGEN05_PERSISTENT"] == F.FLAG_PREPARE_TCGEN05_PERSISTENT
     assert values["FKDA_FLAG_PREPARE_MMA_SYNC"] == F.FLAG_PREPARE_MMA_SYNC
     assert F.FLAG_SEGMENTS(5) == 5 << 8 and "FKDA_FLAG_SEGMENTS(n)" in text
 
