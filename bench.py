@@ -605,7 +605,9 @@ def main():
 # DRAM bytes per token-head of each kernel, from ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum per launch / token-heads of the captured case).
 SHORT16_TRAFFIC_BYTES_PER_CHAIN = 140_400   # profiles/short16_kernel_B128xT16xH32.md (T = 16, fp32 state in and out), scaled by chains
-TRAFFIC_BYTES_PER_TOKEN_HEAD = {"prepare": 1866, "scan": 1313}   # profiles/prepare_kernel_scan2_kernel_B8xT1024xH16.md, scaled by token-heads
+# ncu dram bytes per token-head: profiles/prepare_pipe_kernel_prepare_tc4_kernel_B8xT1024xH16.md (prepare) and
+# profiles/prepare_kernel_scan2_kernel_B8xT1024xH16.md (scan), scaled by token-heads
+TRAFFIC_BYTES_PER_TOKEN_HEAD = {"prepare": 1774, "scan": 1313}
 
 if __name__ == "__main__":
     main()

@@ -204,9 +204,7 @@ __device__ __forceinline__ bool elem_barrier_any(bool failed) {
 
 __global__ void __launch_bounds__(kThreads, 3)
 prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p,
-                    long long* trace) {
-  (void)trace;
+                    const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_v, const PrepParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1184,12 +1182,7 @@ cudaError_t launch_prepare_pipe(const PrepParams& p, cudaStream_t stream) {
   const long long items = static_cast<long long>(p.total_chunks) * p.H;
   const long long slots = 3ll * device_sm_count();
   const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
-#ifdef FKDA_TUNING
-  long long* trace = prep_tc::g_trace;
-#else
-  long long* trace = nullptr;
-#endif
-  prep_pipe::prepare_pipe_kernel<<<grid, prep_pipe::kThreads, prep_pipe::kSmemBytes, stream>>>(tq, tk, tg, tv, p, trace);
+  prep_pipe::prepare_pipe_kernel<<<grid, prep_pipe::kThreads, prep_pipe::kSmemBytes, stream>>>(tq, tk, tg, tv, p);
   return cudaGetLastError();
 }
 
