@@ -73,6 +73,8 @@ def lib():
         L.fkda_debug_tmem_layout_probe.restype = ci
         L.fkda_debug_scan_giveup.argtypes = [ctypes.POINTER(FwdParams), ci, ci, vp]
         L.fkda_debug_scan_giveup.restype = ci
+        L.fkda_debug_prepare_giveup.argtypes = [ctypes.POINTER(FwdParams), ci, vp]
+        L.fkda_debug_prepare_giveup.restype = ci
         if hasattr(L, "fkda_debug_umma_bench"):        # builds made with -DFKDA_TUNING only
             L.fkda_debug_umma_bench.argtypes = [ci, ci, ci, ci, ci, vp, vp, vp]
             L.fkda_debug_umma_bench.restype = ci
@@ -303,6 +305,14 @@ def scan_giveup(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initi
                     cu_seqlens, workspace, 0)
     with torch.cuda.device(q.device):
         _check(lib().fkda_debug_scan_giveup(ctypes.byref(p), int(stop_copies_after), int(wait_limit_us), _stream(q)))
+
+
+def prepare_giveup(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, cu_seqlens=None, *, workspace, wait_limit_us=3000):
+    """Test aid: the token-parallel stage on the pipelined kernel with CTAs that load the tiles of their first item
+    only and waits that give up after `wait_limit_us` microseconds (include/fkda_testing.h)."""
+    p, ws = _params(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, None, None, cu_seqlens, workspace, 0)
+    with torch.cuda.device(q.device):
+        _check(lib().fkda_debug_prepare_giveup(ctypes.byref(p), int(wait_limit_us), _stream(q)))
 
 
 def umma_bench(issuers=1, reps=64, ksteps=8, n=64, a_in_tmem=True, device="cuda"):

@@ -150,7 +150,7 @@ int validate(const fkda_fwd_params* p, Layout* L) {
   return FKDA_OK;
 }
 
-int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
+int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream, int wait_limit_us = 0, int first_load_only = 0) {
   uint8_t* ws = static_cast<uint8_t*>(p->workspace);
   int* status = reinterpret_cast<int*>(ws);
   int* prefix = reinterpret_cast<int*>(ws + L.prefix_off);
@@ -179,6 +179,8 @@ int do_prepare(const fkda_fwd_params* p, const Layout& L, cudaStream_t stream) {
   q.total_chunks = static_cast<int>(L.chunks_per_head);
   q.scale = p->scale;
   q.gate_scale = static_cast<float>(static_cast<double>(p->lower_bound) * 1.4426950408889634);
+  q.wait_limit_us = wait_limit_us;
+  q.first_load_only = first_load_only;
 #ifdef FKDA_TUNING
   {
     static const char* dbg_env = getenv("FKDA_PREPARE_SKIP");   // phase-skip timing of the prepare kernel (results are wrong when set)
@@ -396,6 +398,16 @@ int fkda_debug_scan_giveup(const fkda_fwd_params* p, int stop_copies_after, int 
   cudaError_t e = fkda::launch_scan2(s, stream);
   if (e != cudaSuccess) return cuda_fail(e, "scan launch");
   return FKDA_OK;
+}
+
+int fkda_debug_prepare_giveup(const fkda_fwd_params* p, int wait_limit_us, void* cuda_stream) {
+  Layout L;
+  int rc = validate(p, &L);
+  if (rc != FKDA_OK) return rc;
+  if (wait_limit_us < 1 || wait_limit_us > 1000000) return fail(FKDA_ERR_INVALID_ARGUMENT, "1 <= wait_limit_us <= 1000000 required");
+  if (p->flags & (FKDA_FLAG_PREPARE_TCGEN05 | FKDA_FLAG_PREPARE_MMA_SYNC))
+    return fail(FKDA_ERR_INVALID_ARGUMENT, "the give-up aid drives the pipelined kernel: no kernel-selection flag");
+  return do_prepare(p, L, static_cast<cudaStream_t>(cuda_stream), wait_limit_us, 1);
 }
 
 #ifdef FKDA_TUNING

@@ -391,6 +391,8 @@ struct PrepParams {
   float scale;
   float gate_scale;            // lower_bound * log2(e)
   int dbg;                     // tuning aid: bit mask of phases to skip (0 in production)
+  int wait_limit_us;           // 0: the waits give up after kWaitLimitNs; else after this many microseconds (test aid)
+  int first_load_only;         // 0: normal; 1: a CTA of the pipelined kernel loads the tiles of its first item only (test aid)
 };
 
 struct ScanParams {

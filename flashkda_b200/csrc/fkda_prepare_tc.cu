@@ -255,7 +255,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   };
 
   if (tid == 0) {
-    *abort_flag = 0;
+    *abort_flag = p.wait_limit_us > 0 ? -p.wait_limit_us : 0;
     mbar_init(bar(B_LOAD), 1);
     mbar_init(bar(B_LOAD + 1), 1);
     mbar_init(bar(B_D1), 1);
@@ -267,7 +267,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     issue_load(0);
     if (n_it > 1) {
       *info_of(1) = decode_item(p, blockIdx.x + gridDim.x);
-      issue_load(1);
+      if (!p.first_load_only) issue_load(1);      // (test aid: else a wait that nothing completes)
     }
     if (n_it > 2) decode_and_prefetch(2);
   }
@@ -503,7 +503,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         bulk_s2g(rec + kRecUP, bs + 16384, 8192);
         bulk_commit();
         bulk_wait_read0();
-        if (jt + 2 < n_it) {
+        if (jt + 2 < n_it && !p.first_load_only) {
           issue_load(jt + 2);
           ++loads_issued;
         }

@@ -32,6 +32,12 @@ int fkda_debug_tmem_layout_probe(void* out, void* cuda_stream);
  * Nothing is in flight when the wait runs out.  Read the outcome with fkda_read_status. */
 int fkda_debug_scan_giveup(const fkda_fwd_params* p, int stop_copies_after, int wait_limit_us, void* cuda_stream);
 
+/* The same for the token-parallel stage: fkda_prepare on the pipelined kernel, in which every CTA loads the tiles of
+ * its first item only and every wait gives up after `wait_limit_us` microseconds.  A CTA with a second item waits for
+ * tiles that nothing will bring; it must record status 2, wait for what it still has in flight, release its tensor
+ * memory and return.  (A CTA has a second item once the call has more than three (chunk, head) items per SM.) */
+int fkda_debug_prepare_giveup(const fkda_fwd_params* p, int wait_limit_us, void* cuda_stream);
+
 #ifdef FKDA_TUNING
 /* The following exist only in builds made with -DFKDA_TUNING (FKDA_NVCC_EXTRA=-DFKDA_TUNING python -m
  * flashkda_b200.build --force). */

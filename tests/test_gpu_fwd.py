@@ -278,6 +278,31 @@ def test_bounded_wait_gives_up_and_the_context_stays_usable():
     check_against_f64(x, out, fin2, "after a give-up")
 
 
+def test_bounded_wait_of_the_token_parallel_kernel_gives_up_and_the_context_stays_usable():
+    """The same for the pipelined token-parallel kernel: every CTA loads the tiles of its first item only and the waits
+    are given three milliseconds.  With 600 (chunk, head) items some CTAs have a second item whose tiles never come:
+    the call must return, status 2, tensor memory released (a normal call right afterwards passes); with fewer items
+    than CTAs nobody meets the missing load and the status stays 0.  Nothing faults, and what a CTA still has in
+    flight when it gives up (its first item's products) has landed before it leaves."""
+    w = Workload("pgiveup", H=1, B=1, T=32 * 600, state_in="fp32", state_out="fp32", seed=6)
+    x = make_inputs(w)
+    xc = to_cuda(x)
+    ws = torch.empty(F.get_workspace_size(32 * 600, 1, 1), dtype=torch.uint8, device="cuda")
+    F.prepare_giveup(xc["q"], xc["k"], xc["v"], xc["g"], xc["beta"], x["scale"], xc["out"], xc["A_log"], xc["dt_bias"],
+                     x["lower_bound"], workspace=ws, wait_limit_us=3000)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        F.read_status(ws)
+    torch.cuda.synchronize()
+    w1 = Workload("pgiveup1", H=1, B=1, T=32 * 100, state_in="fp32", state_out="fp32", seed=6)
+    x1 = make_inputs(w1)
+    x1c = to_cuda(x1)
+    F.prepare_giveup(x1c["q"], x1c["k"], x1c["v"], x1c["g"], x1c["beta"], x1["scale"], x1c["out"], x1c["A_log"], x1c["dt_bias"],
+                     x1["lower_bound"], workspace=ws, wait_limit_us=3000)
+    assert F.read_status(ws) == 0
+    out, fin = run_gpu(x, torch.float32)
+    check_against_f64(x, out, fin, "after a give-up of the token-parallel kernel")
+
+
 def test_deterministic_and_tail_rows_untouched():
     w = Workload("d", H=2, seq_lens=[45, 3], state_in="bf16", state_out="bf16", seed=4)
     x = make_inputs(w)

@@ -96,6 +96,37 @@ def test_prepare_records_match_fp64_operands(case, kernel):
     assert worst["mqk"] < 2e-2 and worst["wp"] < 3e-2 and worst["up"] < 3e-2, worst
 
 
+@pytest.mark.parametrize("case", ["fixed_many_iterations", "varlen_many_sequences", "tails"])
+def test_pipelined_kernel_writes_the_records_of_the_cta_per_item_kernel_bit_for_bit(case):
+    """The pipelined token-parallel kernel reuses two operand buffers, two accumulators and its barriers over many
+    items per CTA; the one-CTA-per-item kernel does the same arithmetic with nothing reused.  Their operand records
+    must be the same bytes: a stale tile, a buffer overwritten too early or a lost phase would show here, on shapes
+    with up to 74 items per CTA, ragged sequences and repeated calls."""
+    if case == "fixed_many_iterations":
+        w = Workload("p1", H=32, B=4, T=8192, seed=21)
+    elif case == "varlen_many_sequences":
+        import random
+        rnd = random.Random(5)
+        w = Workload("p2", H=8, seq_lens=[rnd.choice([0, 1, 7, 31, 32, 33, 63, 64, 65, 100, 257, 1000]) for _ in range(300)], seed=22)
+    else:
+        w = Workload("p3", H=5, B=7, T=32 * 40 + 3, seed=23)
+    x = make_inputs(w, device="cuda")
+    args = (x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], x["out"], x["A_log"], x["dt_bias"], x["lower_bound"])
+    B, T = x["q"].shape[:2]
+    size = F.get_workspace_size(B * T, w.H, w.N)
+
+    def records(flags):      # (zero-filled first: what a kernel does not write compares equal)
+        ws = torch.zeros(size, dtype=torch.uint8, device="cuda")
+        F.prepare(*args, cu_seqlens=x["cu_seqlens"], workspace=ws, flags=flags)
+        assert F.read_status(ws) == 0
+        return ws[256:]
+
+    ref = records(F.FLAG_PREPARE_TCGEN05)
+    assert int(ref.count_nonzero()) > size // 2
+    for _ in range(3):
+        assert torch.equal(records(0), ref)
+
+
 def test_tmem_16_lane_fragment_shapes():
     """tcgen05.ld/st with the 16-lane shapes (16x256b.x8, 16x128b.x8) follow the mma accumulator fragment map that
     the helpers in csrc/fkda_common.cuh document: thread t, register 4j+q <-> lane t/4 + 8(q/2), column 8j + 2(t%4) + q%2."""
