@@ -68,6 +68,292 @@ __device__ __forceinline__ void st_global_16(void* p, const uint4& v) {
   asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// ---- the stages that both kernels of this file run on their warps ---------------------------------------------------------
+
+constexpr int kLdA = 36;      // floats per row of the fp32 A and T matrices of the inverse
+
+// A thread's share of an item between the two element phases: two (row, 8 channel) pieces of q, k, v (raw bf16) and of
+// the running log2 decay G (relative to the boundary between the two 16-token sub-blocks).
+struct ElementPieces {
+  uint4 qw[2], kw[2], vw[2];
+  float G[2][8];
+};
+// thread -> pieces: rows sb * 16 + r8 and + 8 of sub-block sb, channels 8 j .. 8 j + 7
+struct ElementMap {
+  int r8, j, sb, row0, row1, hh, cj;
+  __device__ __forceinline__ explicit ElementMap(int tid) {
+    const int cm = tid >> 3;
+    r8 = tid & 7;
+    j = cm & 15;
+    sb = cm >> 4;
+    row0 = sb * 16 + r8;
+    row1 = row0 + 8;
+    hh = j >> 3;
+    cj = j & 7;
+  }
+};
+
+// First element phase: the swizzled tiles q | k | g | v (8192 bytes each, two [32 tok][128 B] halves) -> registers, partial
+// sums of squares to s_ssq [2][32][4], the gate and its running sum, 2^(sub-block total) to s_ex [2][128].  A rendezvous
+// of the eight warps must follow.  `ha` = exp(A_log[h]) / 2, b0 / b1 = dt_bias[h][8 j ..].
+__device__ __forceinline__ void element_phase1(const uint8_t* tiles, float* s_ssq, float* s_ex, const ElementMap& m, int lane, int warp,
+                                               int len, float ha, const float4& b0, const float4& b1, float gate_scale, ElementPieces& pc) {
+  const int r8 = m.r8, j = m.j, sb = m.sb, row0 = m.row0, row1 = m.row1, hh = m.hh, cj = m.cj;
+  {
+    const uint8_t* stg = tiles + hh * 4096;
+    const int sw = (cj ^ r8) << 4;
+    const bool valid0 = row0 < len, valid1 = row1 < len;
+    const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+    uint4 gw[2];
+    pc.qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
+    pc.qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
+    pc.kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
+    pc.kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
+    gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
+    gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
+    pc.vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
+    pc.vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
+    if (!valid0) { pc.qw[0] = z4; pc.kw[0] = z4; gw[0] = z4; pc.vw[0] = z4; }      // rows past the sequence end belong to somebody else
+    if (!valid1) { pc.qw[1] = z4; pc.kw[1] = z4; gw[1] = z4; pc.vw[1] = z4; }
+    const float hgs = 0.5f * gate_scale;
+    const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;
+      float e8[8], sq = 0.f, sk = 0.f;
+      unpack8(pc.qw[hf], e8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq = fmaf(e8[i], e8[i], sq);
+      unpack8(pc.kw[hf], e8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sk = fmaf(e8[i], e8[i], sk);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+      if (lane < 8) {
+        s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
+        s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
+      }
+      unpack8(gw[hf], e8);
+      const bool valid = hf ? valid1 : valid0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float x = valid ? fmaf(tanh_approx(fmaf(e8[i], ha, hab[i])), hgs, hgs) : 0.f;
+#pragma unroll
+        for (int d = 1; d < 8; d <<= 1) {
+          const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
+          if (r8 >= d) x += y;
+        }
+        pc.G[hf][i] = x;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pc.G[1][i] += __shfl_sync(0xffffffffu, pc.G[0][i], 7, 8);
+    float tot[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, pc.G[1][i], 7, 8);
+    if (sb == 0) {      // exponents of sub-block 0 become relative to its end
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { pc.G[0][i] -= tot[i]; pc.G[1][i] -= tot[i]; }
+    }
+    if (r8 == 7) {      // 2^(sub-block total) per channel, once for the CTA
+      *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
+      *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
+    }
+  }
+}
+
+// Second element phase: the decayed operands KPm | QPm | KMm | VC (bf16, core-matrix layout [32][128], 8192 bytes each) over
+// the tiles at `ops`, and the record parts that are final at this point (QP, KR, E) straight to global memory.
+__device__ __forceinline__ void element_phase2(uint8_t* ops, const float* s_ssq, const float* s_ex, uint8_t* rec_dst, const ElementMap& m,
+                                               float scale, const ElementPieces& pc) {
+  const int r8 = m.r8, j = m.j, sb = m.sb, row0 = m.row0, row1 = m.row1;
+  {
+    if (sb == 0 && r8 == 0) {
+      const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
+      const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
+      float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
+      *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
+      *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
+    }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = hf ? row1 : row0;
+      const int off = core_off(row, 8 * j, kD);
+      *reinterpret_cast<uint4*>(ops + 24576 + off) = pc.vw[hf];       // v goes on to the products as it is
+      const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
+      const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
+      const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * scale;
+      const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
+      // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
+      const uint32_t qraw[4] = {pc.qw[hf].x, pc.qw[hf].y, pc.qw[hf].z, pc.qw[hf].w};
+      const uint32_t kraw[4] = {pc.kw[hf].x, pc.kw[hf].y, pc.kw[hf].z, pc.kw[hf].w};
+      __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
+        const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
+        const float pw0 = ex2f(pc.G[hf][2 * m]), pw1 = ex2f(pc.G[hf][2 * m + 1]);
+        const float ip0 = ex2f(-pc.G[hf][2 * m]), ip1 = ex2f(-pc.G[hf][2 * m + 1]);
+        const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
+        const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
+        const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
+        kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
+        qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
+        kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
+        qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
+        kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
+      }
+      auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
+        return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
+                          *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
+      };
+      *reinterpret_cast<uint4*>(ops + off) = as_u4(kpm);
+      *reinterpret_cast<uint4*>(ops + 8192 + off) = as_u4(qpm);
+      *reinterpret_cast<uint4*>(ops + 16384 + off) = as_u4(kmm);
+      st_global_16(rec_dst + kRecQP + off, as_u4(qp));
+      st_global_16(rec_dst + kRecKR + off, as_u4(kr));
+    }
+  }
+}
+
+// The serial part on one warp: A (lanes 0-31 of tensor memory at taddr_a, 32 columns) -> fp32 A beta in sA -> T = (I + A)^-1
+// in sT (both [32][kLdA]; the upper right block of sA is scratch) -> TB^T bf16 [32][32] in core layout at tbt.
+__device__ __forceinline__ void inverse_to_tbt(uint32_t taddr_a, float* sA, float* sT, uint8_t* tbt, float bi, int lane) {
+  float* sX = sA + 16;
+  {
+    uint32_t a0[32];
+    tmem_ld32(taddr_a, a0);
+    tmem_wait_ld();
+#pragma unroll
+    for (int q4 = 0; q4 < 8; ++q4) {
+      float4 r;
+      r.x = (4 * q4 + 0 < lane) ? __uint_as_float(a0[4 * q4 + 0]) * bi : 0.f;
+      r.y = (4 * q4 + 1 < lane) ? __uint_as_float(a0[4 * q4 + 1]) * bi : 0.f;
+      r.z = (4 * q4 + 2 < lane) ? __uint_as_float(a0[4 * q4 + 2]) * bi : 0.f;
+      r.w = (4 * q4 + 3 < lane) ? __uint_as_float(a0[4 * q4 + 3]) * bi : 0.f;
+      *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
+    }
+  }
+  __syncwarp();
+  {
+    // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
+    const int bb = lane >> 4, c = lane & 15;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        if (4 * q4 < i) {
+          const float4 a4 = *reinterpret_cast<const float4*>(sA + (bb * 16 + i) * kLdA + bb * 16 + 4 * q4);
+          part[q4] = fmaf(a4.x, x[4 * q4], part[q4]);
+          part[q4] = fmaf(a4.y, x[4 * q4 + 1], part[q4]);
+          part[q4] = fmaf(a4.z, x[4 * q4 + 2], part[q4]);
+          part[q4] = fmaf(a4.w, x[4 * q4 + 3], part[q4]);
+        }
+      }
+      x[i] = ((i == c) ? 1.f : 0.f) - ((part[0] + part[1]) + (part[2] + part[3]));
+      sT[(bb * 16 + i) * kLdA + bb * 16 + c] = x[i];
+    }
+  }
+  __syncwarp();
+  {
+    // T_10 = -T_11 (A_10 T_00): two 16x16x16 products in tf32 on mma.sync, fp32 accumulation
+    const int g = lane >> 2, t4 = lane & 3;
+    auto small_product = [&](const float* A, const float* B, float* D, float sign) {
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        const int k0 = 8 * ks;
+        const uint32_t f0 = to_tf32(A[g * kLdA + k0 + t4]), f1 = to_tf32(A[(g + 8) * kLdA + k0 + t4]);
+        const uint32_t f2 = to_tf32(A[g * kLdA + k0 + t4 + 4]), f3 = to_tf32(A[(g + 8) * kLdA + k0 + t4 + 4]);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+          mma_tf32_1688(acc[nt], f0, f1, f2, f3, to_tf32(B[(k0 + t4) * kLdA + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLdA + 8 * nt + g]));
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        *reinterpret_cast<float2*>(D + g * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+        *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+      }
+    };
+    small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
+    __syncwarp();
+    small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
+  }
+  __syncwarp();
+  {
+    // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c (zero above the diagonal), bf16
+    uint8_t* row = tbt + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+    for (int cb = 0; cb < 4; ++cb) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i0 = 8 * cb + 2 * e;
+        const float v0 = (i0 >= lane) ? sT[i0 * kLdA + lane] * bi : 0.f;
+        const float v1 = (i0 + 1 >= lane) ? sT[(i0 + 1) * kLdA + lane] * bi : 0.f;
+        w[e] = pack_bf16(v0, v1);
+      }
+      *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+// tril of the 32 fp32 columns a lane read from the M half of the first products -> row `lane` of MQK (bf16, core layout)
+__device__ __forceinline__ void mqk_row(const uint32_t (&u)[32], uint8_t* mqk, int lane) {
+  uint8_t* mrow = mqk + (lane >> 3) * 512 + (lane & 7) * 16;
+#pragma unroll
+  for (int cb = 0; cb < 4; ++cb) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int c = 8 * cb + 2 * e;
+      w[e] = pack_bf16((c <= lane) ? __uint_as_float(u[c]) : 0.f, (c + 1 <= lane) ? __uint_as_float(u[c + 1]) : 0.f);
+    }
+    *reinterpret_cast<uint4*>(mrow + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// (w')^T of channels 32 q .. + 31 (two 16-lane fragments f0, f1: lanes = channels, columns = tokens) -> WP [32 tok][128 k]
+// at shared address wp: scaled back from "relative to the sub-block boundary" by s_ex, rounded, transposed by the store
+__device__ __forceinline__ void wp_quadrant(const uint32_t (&f0)[16], const uint32_t (&f1)[16], uint32_t wp, const float* s_ex, int q, int lane) {
+  const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const uint32_t(&f)[16] = half ? f1 : f0;
+    const int k0 = 32 * q + 16 * half;
+    const float ca = s_ex[k0 + (lane >> 2)], cb = s_ex[k0 + 8 + (lane >> 2)];
+#pragma unroll
+    for (int jp = 0; jp < 2; ++jp) {
+      uint32_t w[4];
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int jt = 2 * jp + jj;
+        w[2 * jj] = pack_bf16(__uint_as_float(f[4 * jt]) * ca, __uint_as_float(f[4 * jt + 1]) * ca);
+        w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * jt + 2]) * cb, __uint_as_float(f[4 * jt + 3]) * cb);
+      }
+      const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
+      stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+// (u')^T of v channel 32 q + lane (32 fp32 columns = tokens) -> its row of UP [128 v][32 tok] (bf16, core layout) at up
+__device__ __forceinline__ void up_row(const uint32_t (&u)[32], uint8_t* up, int q, int lane) {
+  const int v = 32 * q + lane;
+  uint8_t* row = up + (v >> 3) * 512 + (v & 7) * 16;
+#pragma unroll
+  for (int cb = 0; cb < 4; ++cb)
+    *reinterpret_cast<uint4*>(row + cb * 128) =
+        make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
+                   pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -122,11 +408,7 @@ bool make_map(CUtensorMap* map, const void* base, int64_t T_total, int H) {
 // Tensor memory: D1 twice (its M half is read one iteration later), D2 once (guarded by a "read" barrier).
 namespace prep_pipe {
 
-using prep_tc::tma_load_3d;
-using prep_tc::tma_prefetch_3d;
-using prep_tc::tmem_ld_16x256b_x4;
-using prep_tc::stsm_x4_trans;
-using prep_tc::st_global_16;
+using namespace prep_tc;
 
 constexpr int kElemThreads = 256;
 constexpr int kMatrixWarp = 8;
@@ -136,7 +418,6 @@ constexpr uint32_t kColD1 = 0;            // 2 buffers x 32 columns: lanes 0-31 
 constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
 constexpr int kBufBytes = 32768;          // tiles q | k | g | v, then KPm | QPm | KMm | VC (8192 each)
 constexpr int kSmBuf = 0;
-constexpr int kLdA = 36;
 constexpr int kOffA = 8192;               // inside a buffer after the first products: fp32 A [32][36] over QPm
 constexpr int kOffT = 16384;              // fp32 T [32][36] over KMm
 constexpr int kOffTbt = 16384 + 6144;     // TB^T bf16 [32][32], core layout
@@ -289,7 +570,6 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       uint8_t* buf = smem + kSmBuf + b * kBufBytes;
       float* sA = reinterpret_cast<float*>(buf + kOffA);
       float* sT = reinterpret_cast<float*>(buf + kOffT);
-      float* sX = sA + 16;
       // the load barrier of this item has an arrival by the thread that wrote the item's info: acquire it
       if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_LOAD + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
       // this warp has time to spare: it decodes the item after next and asks the L2 for its tiles (its info slot was
@@ -300,86 +580,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const float bi = lane < f.len ? sigmoid_fast(__bfloat162float(p.beta[static_cast<size_t>(f.t0 + lane) * p.H + f.h])) : 0.f;
       if (!__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + b), (it >> 1) & 1, abort_flag))) { failed = true; break; }
       tc_fence_after();
-      {
-        uint32_t a0[32];
-        tmem_ld32(tmem + kColD1 + 32 * b, a0);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          float4 r;
-          r.x = (4 * q4 + 0 < lane) ? __uint_as_float(a0[4 * q4 + 0]) * bi : 0.f;
-          r.y = (4 * q4 + 1 < lane) ? __uint_as_float(a0[4 * q4 + 1]) * bi : 0.f;
-          r.z = (4 * q4 + 2 < lane) ? __uint_as_float(a0[4 * q4 + 2]) * bi : 0.f;
-          r.w = (4 * q4 + 3 < lane) ? __uint_as_float(a0[4 * q4 + 3]) * bi : 0.f;
-          *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
-        }
-      }
-      __syncwarp();
-      {
-        // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
-        const int bb = lane >> 4, c = lane & 15;
-        float x[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            if (4 * q4 < i) {
-              const float4 a4 = *reinterpret_cast<const float4*>(sA + (bb * 16 + i) * kLdA + bb * 16 + 4 * q4);
-              part[q4] = fmaf(a4.x, x[4 * q4], part[q4]);
-              part[q4] = fmaf(a4.y, x[4 * q4 + 1], part[q4]);
-              part[q4] = fmaf(a4.z, x[4 * q4 + 2], part[q4]);
-              part[q4] = fmaf(a4.w, x[4 * q4 + 3], part[q4]);
-            }
-          }
-          x[i] = ((i == c) ? 1.f : 0.f) - ((part[0] + part[1]) + (part[2] + part[3]));
-          sT[(bb * 16 + i) * kLdA + bb * 16 + c] = x[i];
-        }
-      }
-      __syncwarp();
-      {
-        // T_10 = -T_11 (A_10 T_00): two 16x16x16 products in tf32 on mma.sync, fp32 accumulation
-        const int g = lane >> 2, t4 = lane & 3;
-        auto small_product = [&](const float* A, const float* B, float* D, float sign) {
-          float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {
-            const int k0 = 8 * ks;
-            const uint32_t f0 = to_tf32(A[g * kLdA + k0 + t4]), f1 = to_tf32(A[(g + 8) * kLdA + k0 + t4]);
-            const uint32_t f2 = to_tf32(A[g * kLdA + k0 + t4 + 4]), f3 = to_tf32(A[(g + 8) * kLdA + k0 + t4 + 4]);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-              mma_tf32_1688(acc[nt], f0, f1, f2, f3, to_tf32(B[(k0 + t4) * kLdA + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLdA + 8 * nt + g]));
-          }
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            *reinterpret_cast<float2*>(D + g * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
-            *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
-          }
-        };
-        small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
-        __syncwarp();
-        small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
-      }
-      __syncwarp();
-      {
-        // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c (zero above the diagonal), bf16
-        uint8_t* row = buf + kOffTbt + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i0 = 8 * cb + 2 * e;
-            const float v0 = (i0 >= lane) ? sT[i0 * kLdA + lane] * bi : 0.f;
-            const float v1 = (i0 + 1 >= lane) ? sT[(i0 + 1) * kLdA + lane] * bi : 0.f;
-            w[e] = pack_bf16(v0, v1);
-          }
-          *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
+      inverse_to_tbt(tmem + kColD1 + 32 * b, sA, sT, buf + kOffTbt, bi, lane);
       fence_proxy_async_smem();
       __syncwarp();
       // D2 still holds the previous item until the element warps have read it
@@ -408,9 +609,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
   } else {
     // ===== element warps ==================================================================================================
-    const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
-    const int row0 = sb * 16 + r8, row1 = row0 + 8;
-    const int hh = j >> 3, cj = j & 7;
+    const ElementMap em(tid);
     const int q = warp & 3;
     int loads_issued = n_it > 1 ? 2 : 1;     // (thread 0)
 
@@ -434,26 +633,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(B_D2_READ));
-          const uint32_t wp = sbase + kSmBuf + pb * kBufBytes + 8192;
-          const int m = lane >> 3, r = lane & 7;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const uint32_t(&f)[16] = half ? f1 : f0;
-            const int k0 = 32 * q + 16 * half;
-            const float ca = s_ex[k0 + (lane >> 2)], cb = s_ex[k0 + 8 + (lane >> 2)];      // back from "relative to the sub-block boundary"
-#pragma unroll
-            for (int jp = 0; jp < 2; ++jp) {
-              uint32_t w[4];
-#pragma unroll
-              for (int jj = 0; jj < 2; ++jj) {
-                const int jt4 = 2 * jp + jj;
-                w[2 * jj] = pack_bf16(__uint_as_float(f[4 * jt4]) * ca, __uint_as_float(f[4 * jt4 + 1]) * ca);
-                w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * jt4 + 2]) * cb, __uint_as_float(f[4 * jt4 + 3]) * cb);
-              }
-              const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
-              stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
-            }
-          }
+          wp_quadrant(f0, f1, sbase + kSmBuf + pb * kBufBytes + 8192, s_ex, q, lane);
         } else {
           uint32_t u[32];
           tmem_ld32(tq + 32, u);
@@ -461,13 +641,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(B_D2_READ));
-          const int v = 32 * q + lane;
-          uint8_t* row = buf + 16384 + (v >> 3) * 512 + (v & 7) * 16;
-#pragma unroll
-          for (int cb = 0; cb < 4; ++cb)
-            *reinterpret_cast<uint4*>(row + cb * 128) =
-                make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
-                           pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
+          up_row(u, buf + 16384, q, lane);
           if (warp == 5) {
             // tril(q+ k-^T) -> MQK (lanes 32-63 of D1; complete since before the second products were issued)
             if (__all_sync(0xffffffffu, mbar_wait_parked(bar(B_D1 + pb), (jt >> 1) & 1, abort_flag))) {
@@ -475,17 +649,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               tmem_ld32(tmem + (32u << 16) + kColD1 + 32 * pb, u);
               tmem_wait_ld();
               tc_fence_before();
-              uint8_t* mrow = smem + kSmMqk + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-              for (int cb = 0; cb < 4; ++cb) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int c = 8 * cb + 2 * e;
-                  w[e] = pack_bf16((c <= lane) ? __uint_as_float(u[c]) : 0.f, (c + 1 <= lane) ? __uint_as_float(u[c + 1]) : 0.f);
-                }
-                *reinterpret_cast<uint4*>(mrow + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
+              mqk_row(u, smem + kSmMqk, lane);
             } else {
               failed = true;
             }
@@ -522,126 +686,17 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const ItemInfo f = *info_of(it);
       const int h = f.h, len = f.len;
       const float ha = __int_as_float(f.pad[0]);
-      const float4 b0 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j);
-      const float4 b1 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * j + 16);
+      const float4 b0 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * em.j);
+      const float4 b1 = *reinterpret_cast<const float4*>(smem + kSmBias + b * 512 + 32 * em.j + 16);
       uint8_t* const rec_dst = p.records + (static_cast<size_t>(h) * p.total_chunks + f.gc) * kRecBytes;
 
       // ---- sums of squares, gate and its running sum ----------------------------------------------------------------
-      uint4 qw[2], kw[2], vw[2];
-      float G[2][8];
-      {
-        const uint8_t* stg = buf + hh * 4096;
-        const int sw = (cj ^ r8) << 4;
-        const bool valid0 = row0 < len, valid1 = row1 < len;
-        const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
-        uint4 gw[2];
-        qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
-        qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
-        kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
-        kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
-        gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
-        gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
-        vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
-        vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
-        if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
-        if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
-        const float hgs = 0.5f * p.gate_scale;
-        const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int row = hf ? row1 : row0;
-          float e8[8], sq = 0.f, sk = 0.f;
-          unpack8(qw[hf], e8);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sq = fmaf(e8[i], e8[i], sq);
-          unpack8(kw[hf], e8);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sk = fmaf(e8[i], e8[i], sk);
-          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-          sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-          sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-          sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-          if (lane < 8) {
-            s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
-            s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
-          }
-          unpack8(gw[hf], e8);
-          const bool valid = hf ? valid1 : valid0;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float x = valid ? fmaf(tanh_approx(fmaf(e8[i], ha, hab[i])), hgs, hgs) : 0.f;
-#pragma unroll
-            for (int d = 1; d < 8; d <<= 1) {
-              const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
-              if (r8 >= d) x += y;
-            }
-            G[hf][i] = x;
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
-        float tot[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
-        if (sb == 0) {      // exponents of sub-block 0 become relative to its end
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
-        }
-        if (r8 == 7) {      // 2^(sub-block total) per channel, once for the CTA
-          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
-          *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
-        }
-      }
+      ElementPieces pc;
+      element_phase1(buf, s_ssq, s_ex, em, lane, warp, len, ha, b0, b1, p.gate_scale, pc);
       asm volatile("bar.sync 1, 256;" ::: "memory");      // every thread holds its share of the tiles; sums and totals are complete
 
       // ---- decayed operands over the tiles, record parts that are final now straight to global memory ---------------
-      {
-        if (sb == 0 && r8 == 0) {
-          const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
-          const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
-          float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
-          *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
-          *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
-        }
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int row = hf ? row1 : row0;
-          const int off = core_off(row, 8 * j, kD);
-          *reinterpret_cast<uint4*>(buf + 24576 + off) = vw[hf];       // v goes on to the products as it is
-          const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
-          const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
-          const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
-          const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
-          // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
-          const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
-          const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
-          __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
-#pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
-            const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
-            const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
-            const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
-            const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
-            const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
-            const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
-            kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
-            qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
-            kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
-            qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
-            kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
-          }
-          auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
-            return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
-                              *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
-          };
-          *reinterpret_cast<uint4*>(buf + off) = as_u4(kpm);
-          *reinterpret_cast<uint4*>(buf + 8192 + off) = as_u4(qpm);
-          *reinterpret_cast<uint4*>(buf + 16384 + off) = as_u4(kmm);
-          st_global_16(rec_dst + kRecQP + off, as_u4(qp));
-          st_global_16(rec_dst + kRecKR + off, as_u4(kr));
-        }
-      }
+      element_phase2(buf, s_ssq, s_ex, rec_dst, em, p.scale, pc);
       fence_proxy_async_smem();
       any = elem_barrier_any(failed);
       if (any) break;
@@ -696,11 +751,7 @@ prepare_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 // pipelined kernel; no loop, no buffer reuse: the form to compare against.
 namespace prep_tc4 {
 
-using prep_tc::tma_load_3d;
-using prep_tc::prefetch_tensormap;
-using prep_tc::tmem_ld_16x256b_x4;
-using prep_tc::stsm_x4_trans;
-using prep_tc::st_global_16;
+using namespace prep_tc;
 
 constexpr int kThreads = 256;
 constexpr uint32_t kTmemCols = 128;
@@ -711,7 +762,6 @@ constexpr uint32_t kColD2 = 64;           // (w')^T 32 | (u')^T 32
 // every thread holds its share in registers, KPm | QPm | KMm | VC (core layout [32][128], 8192 each); after the first
 // products the QPm and KMm regions receive WP and UP.
 constexpr int kSmX = 0;
-constexpr int kLdA = 36;
 constexpr int kSmA = 32768;                              // fp32 A [32][36]; its unused upper right block holds the merge scratch
 constexpr int kSmT = kSmA + 32 * kLdA * 4;               // fp32 T [32][36]
 constexpr int kSmTbt = kSmT + 32 * kLdA * 4;             // TB^T bf16 [32][32], core layout
@@ -754,16 +804,15 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   float* s_beta = reinterpret_cast<float*>(smem + kSmBeta);
   float* sA = reinterpret_cast<float*>(smem + kSmA);
   float* sT = reinterpret_cast<float*>(smem + kSmT);
-  float* sX = sA + 16;
 
   // grid: x = head (consecutive CTAs take consecutive heads of the same chunk: adjacent rows in memory); equal
   // lengths: y = chunk of the sequence, z = sequence; cu_seqlens: y + kGridY z = chunk of the packed batch.  No division
   // on the way to the first load: everything up to the set-up barrier is latency that every item pays.
   const int h = static_cast<int>(blockIdx.x);
   const float a_log = __ldg(p.A_log + h);
-  const int r8 = tid & 7, cm = tid >> 3, j = cm & 15, sb = cm >> 4;
-  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j));
-  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * j + 4));
+  const ElementMap em(tid);
+  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * em.j));
+  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.dt_bias + h * kD + 8 * em.j + 4));
   int gc;
   int64_t t0;
   int len;
@@ -820,9 +869,6 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
-  // thread -> two (row, 8-column) pieces of one sub-block, as in the default kernel
-  const int row0 = sb * 16 + r8, row1 = row0 + 8;
-  const int hh = j >> 3, cj = j & 7;
   if (warp == 2) s_beta[lane] = lane < len ? sigmoid_fast(beta_raw) : 0.f;
   tc_fence_before();
   __syncthreads();
@@ -832,125 +878,15 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (tid == 0) P4TRACE(13);
 
   // ---- P1: staged tiles -> registers, partial sums of squares, gate and its running sum ----------------------------
-  uint4 qw[2], kw[2], vw[2];
-  float G[2][8];
-  {
-    if (!mbar_wait_parked(bar(B_LOAD), 0, abort_flag)) failed = true;
-    if (tid == 0) P4TRACE(1);
-    const uint8_t* stg = smem + kSmX + hh * 4096;
-    const int sw = (cj ^ r8) << 4;
-    const bool valid0 = row0 < len, valid1 = row1 < len;
-    const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
-    uint4 gw[2];
-    qw[0] = *reinterpret_cast<const uint4*>(stg + row0 * 128 + sw);
-    qw[1] = *reinterpret_cast<const uint4*>(stg + row1 * 128 + sw);
-    kw[0] = *reinterpret_cast<const uint4*>(stg + 8192 + row0 * 128 + sw);
-    kw[1] = *reinterpret_cast<const uint4*>(stg + 8192 + row1 * 128 + sw);
-    gw[0] = *reinterpret_cast<const uint4*>(stg + 16384 + row0 * 128 + sw);
-    gw[1] = *reinterpret_cast<const uint4*>(stg + 16384 + row1 * 128 + sw);
-    vw[0] = *reinterpret_cast<const uint4*>(stg + 24576 + row0 * 128 + sw);
-    vw[1] = *reinterpret_cast<const uint4*>(stg + 24576 + row1 * 128 + sw);
-    if (!valid0) { qw[0] = z4; kw[0] = z4; gw[0] = z4; vw[0] = z4; }      // rows past the sequence end belong to somebody else
-    if (!valid1) { qw[1] = z4; kw[1] = z4; gw[1] = z4; vw[1] = z4; }
-    const float hgs = 0.5f * p.gate_scale;
-    const float ha = 0.5f * ex2f(a_log * kLog2e);
-    const float hab[8] = {ha * b0.x, ha * b0.y, ha * b0.z, ha * b0.w, ha * b1.x, ha * b1.y, ha * b1.z, ha * b1.w};
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const int row = hf ? row1 : row0;
-      float f[8], sq = 0.f, sk = 0.f;
-      unpack8(qw[hf], f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) sq = fmaf(f[i], f[i], sq);
-      unpack8(kw[hf], f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) sk = fmaf(f[i], f[i], sk);
-      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-      sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-      sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-      sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-      if (lane < 8) {
-        s_ssq[(0 * kChunk + row) * 4 + (warp & 3)] = sq;
-        s_ssq[(1 * kChunk + row) * 4 + (warp & 3)] = sk;
-      }
-      unpack8(gw[hf], f);
-      const bool valid = hf ? valid1 : valid0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float x = valid ? fmaf(tanh_approx(fmaf(f[i], ha, hab[i])), hgs, hgs) : 0.f;
-#pragma unroll
-        for (int d = 1; d < 8; d <<= 1) {
-          const float y = __shfl_up_sync(0xffffffffu, x, d, 8);
-          if (r8 >= d) x += y;
-        }
-        G[hf][i] = x;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) G[1][i] += __shfl_sync(0xffffffffu, G[0][i], 7, 8);
-    float tot[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) tot[i] = __shfl_sync(0xffffffffu, G[1][i], 7, 8);
-    if (sb == 0) {      // exponents of sub-block 0 become relative to its end
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { G[0][i] -= tot[i]; G[1][i] -= tot[i]; }
-    }
-    if (r8 == 7) {      // 2^(sub-block total) per channel, once for the CTA
-      *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j) = make_float4(ex2f(tot[0]), ex2f(tot[1]), ex2f(tot[2]), ex2f(tot[3]));
-      *reinterpret_cast<float4*>(s_ex + sb * kD + 8 * j + 4) = make_float4(ex2f(tot[4]), ex2f(tot[5]), ex2f(tot[6]), ex2f(tot[7]));
-    }
-  }
+  if (!mbar_wait_parked(bar(B_LOAD), 0, abort_flag)) failed = true;
+  if (tid == 0) P4TRACE(1);
+  ElementPieces pc;
+  element_phase1(smem + kSmX, s_ssq, s_ex, em, lane, warp, len, 0.5f * ex2f(a_log * kLog2e), b0, b1, p.gate_scale, pc);
   __syncthreads();      // every thread holds its share of the tiles; sums of squares and sub-block totals are complete
   if (tid == 0) P4TRACE(2);
 
   // ---- P2: decayed operands over the staging area, record parts that are final now straight to global memory ------
-  {
-    if (sb == 0 && r8 == 0) {
-      const float4 p0 = *reinterpret_cast<const float4*>(s_ex + 8 * j), p1 = *reinterpret_cast<const float4*>(s_ex + 8 * j + 4);
-      const float4 q0 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j), q1 = *reinterpret_cast<const float4*>(s_ex + kD + 8 * j + 4);
-      float* e = reinterpret_cast<float*>(rec_dst + kRecE) + 8 * j;
-      *reinterpret_cast<float4*>(e) = make_float4(p0.x * q0.x, p0.y * q0.y, p0.z * q0.z, p0.w * q0.w);
-      *reinterpret_cast<float4*>(e + 4) = make_float4(p1.x * q1.x, p1.y * q1.y, p1.z * q1.z, p1.w * q1.w);
-    }
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const int row = hf ? row1 : row0;
-      const int off = core_off(row, 8 * j, kD);
-      *reinterpret_cast<uint4*>(smem + kSmX + 24576 + off) = vw[hf];       // v goes on to the products as it is
-      const float4 sq4 = *reinterpret_cast<const float4*>(s_ssq + (0 * kChunk + row) * 4);
-      const float4 sk4 = *reinterpret_cast<const float4*>(s_ssq + (1 * kChunk + row) * 4);
-      const float rq = rsqrtf(sq4.x + sq4.y + sq4.z + sq4.w + 1e-6f) * p.scale;
-      const float rk = rsqrtf(sk4.x + sk4.y + sk4.z + sk4.w + 1e-6f);
-      // each factor is formed in fp32, rounded to bf16 once and applied to the raw bf16 input with a packed multiply
-      const uint32_t qraw[4] = {qw[hf].x, qw[hf].y, qw[hf].z, qw[hf].w};
-      const uint32_t kraw[4] = {kw[hf].x, kw[hf].y, kw[hf].z, kw[hf].w};
-      __nv_bfloat162 kpm[4], qpm[4], kmm[4], qp[4], kr[4];
-#pragma unroll
-      for (int m = 0; m < 4; ++m) {
-        const float2 cq = *reinterpret_cast<const float2*>(s_ex + 8 * j + 2 * m);
-        const float2 cr = *reinterpret_cast<const float2*>(s_ex + kD + 8 * j + 2 * m);
-        const float pw0 = ex2f(G[hf][2 * m]), pw1 = ex2f(G[hf][2 * m + 1]);
-        const float ip0 = ex2f(-G[hf][2 * m]), ip1 = ex2f(-G[hf][2 * m + 1]);
-        const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kraw[m]);
-        const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&qraw[m]);
-        const float kp0 = rk * pw0, kp1 = rk * pw1, qp0 = rq * pw0, qp1 = rq * pw1, km0 = rk * ip0, km1 = rk * ip1;
-        kpm[m] = __hmul2(k2, __floats2bfloat162_rn(kp0, kp1));
-        qpm[m] = __hmul2(q2, __floats2bfloat162_rn(qp0, qp1));
-        kmm[m] = __hmul2(k2, __floats2bfloat162_rn(km0, km1));
-        qp[m] = __hmul2(q2, __floats2bfloat162_rn(qp0 * cq.x, qp1 * cq.y));
-        kr[m] = __hmul2(k2, __floats2bfloat162_rn(km0 * cr.x, km1 * cr.y));
-      }
-      auto as_u4 = [](const __nv_bfloat162(&x)[4]) {
-        return make_uint4(*reinterpret_cast<const uint32_t*>(&x[0]), *reinterpret_cast<const uint32_t*>(&x[1]),
-                          *reinterpret_cast<const uint32_t*>(&x[2]), *reinterpret_cast<const uint32_t*>(&x[3]));
-      };
-      *reinterpret_cast<uint4*>(smem + kSmX + off) = as_u4(kpm);
-      *reinterpret_cast<uint4*>(smem + kSmX + 8192 + off) = as_u4(qpm);
-      *reinterpret_cast<uint4*>(smem + kSmX + 16384 + off) = as_u4(kmm);
-      st_global_16(rec_dst + kRecQP + off, as_u4(qp));
-      st_global_16(rec_dst + kRecKR + off, as_u4(kr));
-    }
-  }
+  element_phase2(smem + kSmX, s_ssq, s_ex, rec_dst, em, p.scale, pc);
   fence_proxy_async_smem();
   __syncthreads();
   if (tid == 0) P4TRACE(3);
@@ -972,89 +908,7 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (ok) {
       tc_fence_after();
       if (lane == 0) P4TRACE(5);
-      const float bi = s_beta[lane];
-      {
-        uint32_t a0[32];
-        tmem_ld32(tmem + kColD1, a0);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          float4 r;
-          r.x = (4 * q4 + 0 < lane) ? __uint_as_float(a0[4 * q4 + 0]) * bi : 0.f;
-          r.y = (4 * q4 + 1 < lane) ? __uint_as_float(a0[4 * q4 + 1]) * bi : 0.f;
-          r.z = (4 * q4 + 2 < lane) ? __uint_as_float(a0[4 * q4 + 2]) * bi : 0.f;
-          r.w = (4 * q4 + 3 < lane) ? __uint_as_float(a0[4 * q4 + 3]) * bi : 0.f;
-          *reinterpret_cast<float4*>(sA + lane * kLdA + 4 * q4) = r;
-        }
-      }
-      __syncwarp();
-      if (lane == 0) P4TRACE(6);
-      {
-        // the two 16 x 16 diagonal blocks by forward substitution, one column of one block per lane
-        const int b = lane >> 4, c = lane & 15;
-        float x[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            if (4 * q4 < i) {
-              const float4 a4 = *reinterpret_cast<const float4*>(sA + (b * 16 + i) * kLdA + b * 16 + 4 * q4);
-              part[q4] = fmaf(a4.x, x[4 * q4], part[q4]);
-              part[q4] = fmaf(a4.y, x[4 * q4 + 1], part[q4]);
-              part[q4] = fmaf(a4.z, x[4 * q4 + 2], part[q4]);
-              part[q4] = fmaf(a4.w, x[4 * q4 + 3], part[q4]);
-            }
-          }
-          x[i] = ((i == c) ? 1.f : 0.f) - ((part[0] + part[1]) + (part[2] + part[3]));
-          sT[(b * 16 + i) * kLdA + b * 16 + c] = x[i];
-        }
-      }
-      __syncwarp();
-      {
-        // T_10 = -T_11 (A_10 T_00): two 16x16x16 products in tf32 on mma.sync, fp32 accumulation
-        const int g = lane >> 2, t4 = lane & 3;
-        auto small_product = [&](const float* A, const float* B, float* D, float sign) {
-          float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {
-            const int k0 = 8 * ks;
-            const uint32_t f0 = to_tf32(A[g * kLdA + k0 + t4]), f1 = to_tf32(A[(g + 8) * kLdA + k0 + t4]);
-            const uint32_t f2 = to_tf32(A[g * kLdA + k0 + t4 + 4]), f3 = to_tf32(A[(g + 8) * kLdA + k0 + t4 + 4]);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-              mma_tf32_1688(acc[nt], f0, f1, f2, f3, to_tf32(B[(k0 + t4) * kLdA + 8 * nt + g]), to_tf32(B[(k0 + t4 + 4) * kLdA + 8 * nt + g]));
-          }
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            *reinterpret_cast<float2*>(D + g * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
-            *reinterpret_cast<float2*>(D + (g + 8) * kLdA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
-          }
-        };
-        if (lane == 0) P4TRACE(7);
-        small_product(sA + 16 * kLdA, sT, sX, 1.f);                      // X = A_10 T_00
-        __syncwarp();
-        small_product(sT + 16 * kLdA + 16, sX, sT + 16 * kLdA, -1.f);    // T_10 = -T_11 X
-      }
-      __syncwarp();
-      {
-        // row `lane` of TB^T: TB^T[c][i] = T[i][c] beta_c (zero above the diagonal), bf16
-        uint8_t* row = smem + kSmTbt + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i0 = 8 * cb + 2 * e;
-            const float v0 = (i0 >= lane) ? sT[i0 * kLdA + lane] * bi : 0.f;
-            const float v1 = (i0 + 1 >= lane) ? sT[(i0 + 1) * kLdA + lane] * bi : 0.f;
-            w[e] = pack_bf16(v0, v1);
-          }
-          *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
+      inverse_to_tbt(tmem + kColD1, sA, sT, smem + kSmTbt, s_beta[lane], lane);
       fence_proxy_async_smem();
       if (lane == 0) P4TRACE(8);
     } else {
@@ -1068,19 +922,7 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       uint32_t a0[32];
       tmem_ld32(tmem + (32u << 16) + kColD1, a0);
       tmem_wait_ld();
-      uint8_t* row = smem + kSmMqk + (lane >> 3) * 512 + (lane & 7) * 16;
-#pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = 8 * cb + 2 * e;
-          const float v0 = (c <= lane) ? __uint_as_float(a0[c]) : 0.f;
-          const float v1 = (c + 1 <= lane) ? __uint_as_float(a0[c + 1]) : 0.f;
-          w[e] = pack_bf16(v0, v1);
-        }
-        *reinterpret_cast<uint4*>(row + cb * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+      mqk_row(a0, smem + kSmMqk, lane);
       fence_proxy_async_smem();
     } else {
       failed = true;
@@ -1113,40 +955,17 @@ prepare_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       failed = true;
     } else if (warp < 4) {
       tc_fence_after();
-      const uint32_t wp = sbase + kSmX + 8192;
-      const int m = lane >> 3, r = lane & 7;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t f[16];
-        tmem_ld_16x256b_x4(tq + (static_cast<uint32_t>(16 * half) << 16), f);
-        const int k0 = 32 * q + 16 * half;
-        const float ca = s_ex[k0 + (lane >> 2)], cb = s_ex[k0 + 8 + (lane >> 2)];      // back from "relative to the sub-block boundary"
-        tmem_wait_ld();
-#pragma unroll
-        for (int jp = 0; jp < 2; ++jp) {
-          uint32_t w[4];
-#pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const int jt = 2 * jp + jj;
-            w[2 * jj] = pack_bf16(__uint_as_float(f[4 * jt]) * ca, __uint_as_float(f[4 * jt + 1]) * ca);
-            w[2 * jj + 1] = pack_bf16(__uint_as_float(f[4 * jt + 2]) * cb, __uint_as_float(f[4 * jt + 3]) * cb);
-          }
-          const int tok = 8 * (2 * jp + (m >> 1)) + r, kc = k0 + 8 * (m & 1);
-          stsm_x4_trans(wp + (tok >> 3) * 2048 + (kc >> 3) * 128 + (tok & 7) * 16, w[0], w[1], w[2], w[3]);
-        }
-      }
+      uint32_t f0[16], f1[16];
+      tmem_ld_16x256b_x4(tq, f0);
+      tmem_ld_16x256b_x4(tq + (16u << 16), f1);
+      tmem_wait_ld();
+      wp_quadrant(f0, f1, sbase + kSmX + 8192, s_ex, q, lane);
     } else {
       tc_fence_after();
       uint32_t u[32];
       tmem_ld32(tq + 32, u);
       tmem_wait_ld();
-      const int v = 32 * q + lane;
-      uint8_t* row = smem + kSmX + 16384 + (v >> 3) * 512 + (v & 7) * 16;
-#pragma unroll
-      for (int cb = 0; cb < 4; ++cb)
-        *reinterpret_cast<uint4*>(row + cb * 128) =
-            make_uint4(pack_bf16(__uint_as_float(u[8 * cb]), __uint_as_float(u[8 * cb + 1])), pack_bf16(__uint_as_float(u[8 * cb + 2]), __uint_as_float(u[8 * cb + 3])),
-                       pack_bf16(__uint_as_float(u[8 * cb + 4]), __uint_as_float(u[8 * cb + 5])), pack_bf16(__uint_as_float(u[8 * cb + 6]), __uint_as_float(u[8 * cb + 7])));
+      up_row(u, smem + kSmX + 16384, q, lane);
     }
   }
   fence_proxy_async_smem();
