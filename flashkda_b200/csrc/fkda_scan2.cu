@@ -86,6 +86,15 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // use count of the X/Y buffers: chunk c >= 1 uses buffer c & 1
 __device__ __forceinline__ uint32_t xy_use(int c) { return (c & 1) ? (c >> 1) : (c >> 1) - 1; }
 
+// x[2i], x[2i+1] *= e.x, e.y as one packed fp32x2 multiply
+__device__ __forceinline__ void mul2(uint32_t& a, uint32_t& b, const float2& e) {
+  unsigned long long x, y, z;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "r"(a), "r"(b));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(y) : "f"(e.x), "f"(e.y));
+  asm("mul.f32x2 %0, %1, %2;" : "=l"(z) : "l"(x), "l"(y));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(z));
+}
+
 __device__ __forceinline__ void pack32(const uint32_t (&x)[32], uint32_t (&y)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
@@ -106,8 +115,8 @@ __device__ __noinline__ bool state_warp_loop(uint8_t* smem, uint32_t tq, int grp
     // The decay factors of the next chunk are the same for every lane.  Each lane fetches two of this group's
     // 64 factors now (before the state update lands) and they are handed round by shuffles below: no
     // shared-memory latency between the TMEM load and store, and no 64 extra registers.
-    const float* e = reinterpret_cast<const float*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 64 * grp;
-    const float e_lo = e[lane], e_hi = e[32 + lane];
+    // (every lane reads the same address: a broadcast, one wavefront per load; two factors per load and per multiply)
+    const float2* e2 = reinterpret_cast<const float2*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 32 * grp;
     if (!warp_wait(bar(BAR_SFULL), c & 1, abort_flag)) { failed = true; break; }
     const int trole = 2;
     const bool tr_on = (warp == 8) && lane == 0;
@@ -121,13 +130,13 @@ __device__ __noinline__ bool state_warp_loop(uint8_t* smem, uint32_t tq, int grp
     if (tr_on) FKDA_TRACE(trole, c, 2);
     // the bf16 copy first: the products that read it head the longest chain of the step
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x0[i] = __float_as_uint(__uint_as_float(x0[i]) * __shfl_sync(0xffffffffu, e_lo, i));
+    for (int i = 0; i < 16; ++i) mul2(x0[2 * i], x0[2 * i + 1], e2[i]);
     if (tr_on) FKDA_TRACE(trole, c, 6);
     pack32(x0, y);
     tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp, y);
     if (tr_on) FKDA_TRACE(trole, c, 7);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x1[i] = __float_as_uint(__uint_as_float(x1[i]) * __shfl_sync(0xffffffffu, e_hi, i));
+    for (int i = 0; i < 16; ++i) mul2(x1[2 * i], x1[2 * i + 1], e2[16 + i]);
     pack32(x1, y);
     tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp + 16, y);
     tmem_wait_st();
