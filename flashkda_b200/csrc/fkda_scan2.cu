@@ -14,8 +14,9 @@
 //
 // Warp roles (640 threads): 0 = bulk-copy producer; 1, 2, 3 = one MMA-issuing thread each (products on
 // U / on the decayed state / X,Y), ordered among each other through tcgen05.commit + mbarriers;
-// 4-7 = U warps (critical chain); 8-15 = state warps (two groups of four, 64 state columns each);
-// 16-19 = output warps (two of them also turn X, Y into bf16 operands).  Every wait is bounded; a wait that gives up raises an abort flag, records a
+// 4-7 = U warps (critical chain); 8-15 = state warps (two groups of four, 64 state columns each; kStateBlocks = 1 makes
+// it sixteen warps of 32 columns: a shorter decay, 1250 against 1580 cycles, at 72 registers, and the same step, which the
+// thread that issues the products on U sets by then); 16-19 = output warps (two of them also turn X, Y into bf16 operands).  Every wait is bounded; a wait that gives up raises an abort flag, records a
 // status code and lets all roles fall through to the common exit, where TMEM is released.
 #include "fkda_common.cuh"
 
@@ -37,7 +38,10 @@ static unsigned long long* g_trace = nullptr;
 #endif
 
 constexpr int kStages = 5;
-constexpr int kThreads = 20 * 32;
+constexpr int kStateBlocks = 2;                         // 32-column blocks of the state per state warp (2: eight warps; 1: sixteen)
+constexpr int kStateWarps = 16 / kStateBlocks;
+constexpr int kOutWarp0 = 8 + kStateWarps;              // first output warp
+constexpr int kThreads = (kOutWarp0 + 4) * 32;
 constexpr uint32_t kTmemCols = 512;
 // tensor-memory columns
 constexpr uint32_t kColS = 0;                   // 128: state accumulator S^T [v][k], fp32
@@ -112,39 +116,36 @@ __device__ __noinline__ bool state_warp_loop(uint8_t* smem, uint32_t tq, int grp
   bool failed = false;
   for (int c = 0; c + 1 < nchunks && !failed; ++c) {
     if (!warp_wait(full_bar(c + 1), full_par(c + 1), abort_flag)) { failed = true; break; }
-    // The decay factors of the next chunk are the same for every lane.  Each lane fetches two of this group's
-    // 64 factors now (before the state update lands) and they are handed round by shuffles below: no
-    // shared-memory latency between the TMEM load and store, and no 64 extra registers.
-    // (every lane reads the same address: a broadcast, one wavefront per load; two factors per load and per multiply)
-    const float2* e2 = reinterpret_cast<const float2*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 32 * grp;
+    // The decay factors of the next chunk are the same for every lane: every lane reads the same address (a broadcast,
+    // one wavefront per load), two factors per load and per packed fp32x2 multiply.
+    const float2* e2 = reinterpret_cast<const float2*>(smem + kSmStage + ((c + 1) % kStages) * kRecBytes + kRecE) + 16 * kStateBlocks * grp;
     if (!warp_wait(bar(BAR_SFULL), c & 1, abort_flag)) { failed = true; break; }
     const int trole = 2;
     const bool tr_on = (warp == 8) && lane == 0;
     if (tr_on) FKDA_TRACE(trole, c, 0);
     tc_fence_after();
     if (tr_on) FKDA_TRACE(trole, c, 1);
-    uint32_t x0[32], x1[32], y[16];
-    tmem_ld32(tq + kColS + 64 * grp, x0);
-    tmem_ld32(tq + kColS + 64 * grp + 32, x1);
+    uint32_t x[kStateBlocks][32], y[16];
+#pragma unroll
+    for (int blk = 0; blk < kStateBlocks; ++blk) tmem_ld32(tq + kColS + 32 * (kStateBlocks * grp + blk), x[blk]);
     tmem_wait_ld();
     if (tr_on) FKDA_TRACE(trole, c, 2);
     // the bf16 copy first: the products that read it head the longest chain of the step
 #pragma unroll
-    for (int i = 0; i < 16; ++i) mul2(x0[2 * i], x0[2 * i + 1], e2[i]);
-    if (tr_on) FKDA_TRACE(trole, c, 6);
-    pack32(x0, y);
-    tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp, y);
-    if (tr_on) FKDA_TRACE(trole, c, 7);
+    for (int blk = 0; blk < kStateBlocks; ++blk) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) mul2(x1[2 * i], x1[2 * i + 1], e2[16 + i]);
-    pack32(x1, y);
-    tmem_st16(tq + kColSbd + 64 * (c & 1) + 32 * grp + 16, y);
+      for (int i = 0; i < 16; ++i) mul2(x[blk][2 * i], x[blk][2 * i + 1], e2[16 * blk + i]);
+      if (tr_on && blk == 0) FKDA_TRACE(trole, c, 6);
+      pack32(x[blk], y);
+      tmem_st16(tq + kColSbd + 64 * (c & 1) + 16 * (kStateBlocks * grp + blk), y);
+      if (tr_on && blk == 0) FKDA_TRACE(trole, c, 7);
+    }
     tmem_wait_st();
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(bar(BAR_SBDREADY + ((c + 1) & 1)));
-    tmem_st32(tq + kColS + 64 * grp, x0);
-    tmem_st32(tq + kColS + 64 * grp + 32, x1);
+#pragma unroll
+    for (int blk = 0; blk < kStateBlocks; ++blk) tmem_st32(tq + kColS + 32 * (kStateBlocks * grp + blk), x[blk]);
     if (tr_on) FKDA_TRACE(trole, c, 4);
     tmem_wait_st();
     if (tr_on) FKDA_TRACE(trole, c, 5);
@@ -152,7 +153,7 @@ __device__ __noinline__ bool state_warp_loop(uint8_t* smem, uint32_t tq, int grp
     __syncwarp();
     if (lane == 0) {
       if (tr_on) FKDA_TRACE(trole, c, 3);
-      FKDA_TRACE(5, c, warp - 8);          // arrival time of each of the eight state warps
+      if (warp < 16) FKDA_TRACE(5, c, warp - 8);          // arrival time of the first eight state warps
       mbar_arrive(bar(BAR_SREADY));
       mbar_arrive(bar(BAR_EMPTY + (c + 1) % kStages));    // done with e of record c+1
     }
@@ -270,7 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     *abort_flag = p.wait_limit_us > 0 ? -p.wait_limit_us : 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(BAR_FULL + s), 1);
-      mbar_init(bar(BAR_EMPTY + s), 1 + 4 + 8);   // MMA commit + U warps + state warps
+      mbar_init(bar(BAR_EMPTY + s), 1 + 4 + kStateWarps);   // MMA commit + U warps + state warps
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(BAR_WFULL + b), 1);
@@ -284,9 +285,9 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     }
     mbar_init(bar(BAR_SFULL), 1);
     mbar_init(bar(BAR_UREADY), 4);
-    mbar_init(bar(BAR_SREADY), 8);
-    mbar_init(bar(BAR_SBDREADY + 0), 8);
-    mbar_init(bar(BAR_SBDREADY + 1), 8);
+    mbar_init(bar(BAR_SREADY), kStateWarps);
+    mbar_init(bar(BAR_SBDREADY + 0), kStateWarps);
+    mbar_init(bar(BAR_SBDREADY + 1), kStateWarps);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -455,8 +456,8 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         mbar_arrive(bar(BAR_EMPTY + c % kStages));   // this warp is done reading up[] of the record
       }
     }
-  } else if (warp < 16) {
-    // ===== state warps: two groups of four; group g owns state columns k in [64g, 64g+64) =====================
+  } else if (warp < kOutWarp0) {
+    // ===== state warps: groups of four; group g owns state columns k in [32 kStateBlocks g, + 32 kStateBlocks) ============
     const int grp = (warp - 8) >> 2;
     const int qd = warp & 3;
     const int v = qd * 32 + lane;
@@ -475,10 +476,10 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
 
     // ---- initial state: S <- e_0 S_init; bf16 copies of S_init (buffer 0) and e_0 S_init (buffer 1) --------
     // All global loads of this thread's 64 state values are issued before anything is waited for.
-    uint32_t xi[2][32];
+    uint32_t xi[kStateBlocks][32];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int cb = 2 * grp + half;     // 32-column block
+    for (int half = 0; half < kStateBlocks; ++half) {
+      const int cb = kStateBlocks * grp + half;     // 32-column block
       if (init_mode == 1 || init_mode == 2) {
         if (init_mode == 1) {
           const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(init_base) + row_off + cb * 32);
@@ -509,22 +510,16 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
     if (nchunks > 0) ok = warp_wait(full_bar(0), 0, abort_flag);
     if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 1);
     if (ok) {
-      float e_l = 1.f, e_h = 1.f;         // this lane's two of the group's 64 decay factors of chunk 0
-      if (nchunks > 0) {
-        const float* e0 = reinterpret_cast<const float*>(smem + kSmStage + kRecE) + 64 * grp;
-        e_l = e0[lane];
-        e_h = e0[32 + lane];
-      }
+      const float2* e0 = reinterpret_cast<const float2*>(smem + kSmStage + kRecE);      // decay factors of chunk 0
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int cb = 2 * grp + half;
+      for (int half = 0; half < kStateBlocks; ++half) {
+        const int cb = kStateBlocks * grp + half;
         uint32_t y[16];
         if (nchunks > 0) {
           pack32(xi[half], y);
           tmem_st16(tq + kColSbd + 0 + cb * 16, y);
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            xi[half][i] = __float_as_uint(__uint_as_float(xi[half][i]) * __shfl_sync(0xffffffffu, half ? e_h : e_l, i));
+          for (int i = 0; i < 16; ++i) mul2(xi[half][2 * i], xi[half][2 * i + 1], e0[16 * cb + i]);
           pack32(xi[half], y);
           tmem_st16(tq + kColSbd + 64 + cb * 16, y);
         }
@@ -564,8 +559,8 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         tc_fence_after();
         if (warp == 8 && lane == 0) FKDA_TRACE(2, 30, 3);
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          const int cb = 2 * grp + half;
+        for (int half = 0; half < kStateBlocks; ++half) {
+          const int cb = kStateBlocks * grp + half;
           uint32_t x[32];
           tmem_ld32(tq + kColS + cb * 32, x);
           tmem_wait_ld();
@@ -597,7 +592,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       if (qd >= 2) return true;
       if (!warp_wait(bar(BAR_XFULL + (c & 1)), xy_use(c) & 1u, abort_flag, 32)) return false;
       tc_fence_after();
-      if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 0);
+      if (warp == kOutWarp0 && lane == 0) FKDA_TRACE(3, c, 0);
       uint32_t x[32], y[16];
       tmem_ld32(tq + kColXA + 32 * (c & 1), x);
       tmem_wait_ld();
@@ -610,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        if (warp == 16) FKDA_TRACE(3, c, 1);
+        if (warp == kOutWarp0) FKDA_TRACE(3, c, 1);
         mbar_arrive(bar(BAR_XREADY + (c & 1)));
       }
       return true;
@@ -620,7 +615,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
       if (c + 2 < nchunks && !xy_epilogue(c + 2)) { failed = true; break; }
       if (!warp_wait(bar(BAR_OFULL + (c & 1)), (c >> 1) & 1, abort_flag, 32)) { failed = true; break; }
       tc_fence_after();
-      if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 2);
+      if (warp == kOutWarp0 && lane == 0) FKDA_TRACE(3, c, 2);
       uint32_t o[32];
       tmem_ld32(tq + kColO + 64 * (c & 1), o);
       tmem_wait_ld();
@@ -642,7 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
         }
       }
       __syncwarp();
-      if (warp == 16 && lane == 0) FKDA_TRACE(3, c, 3);
+      if (warp == kOutWarp0 && lane == 0) FKDA_TRACE(3, c, 3);
     }
   }
 
