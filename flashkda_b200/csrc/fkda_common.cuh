@@ -354,6 +354,15 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
 // ---- small helpers shared by the token-parallel kernels ---------------------------------------------
 // byte offset of 16-byte chunk `chunk` of token row `row` in a staged [rows][256 B] tile whose chunks are XOR-swizzled by
 // the row index (conflict-free for row-wise 16-byte reads and for ldmatrix over eight consecutive rows)
+// a, b (fp32 bit patterns) *= e.x, e.y as one packed fp32x2 multiply (same rounding as two scalar multiplies)
+__device__ __forceinline__ void mul2(uint32_t& a, uint32_t& b, const float2& e) {
+  unsigned long long x, y, z;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "r"(a), "r"(b));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(y) : "f"(e.x), "f"(e.y));
+  asm("mul.f32x2 %0, %1, %2;" : "=l"(z) : "l"(x), "l"(y));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(z));
+}
+
 __device__ __forceinline__ int stage_off(int row, int chunk) { return row * 256 + ((chunk ^ (row & 7)) << 4); }
 
 __device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {

@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
           for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
           tmem_st16(tq + kColSbd + cb * 16, y);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e0[cb * 32 + i]);
+          for (int i = 0; i < 16; ++i) mul2(x[2 * i], x[2 * i + 1], reinterpret_cast<const float2*>(e0)[cb * 16 + i]);
         }
         tmem_st32(tq + kColS + cb * 32, x);
       }
@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const ScanParams 
           for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
           tmem_st16(tq + kColSbd + cb * 16, y);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * e[cb * 32 + i]);
+          for (int i = 0; i < 16; ++i) mul2(x[2 * i], x[2 * i + 1], reinterpret_cast<const float2*>(e)[cb * 16 + i]);
           tmem_st32(tq + kColS + cb * 32, x);
         }
       }

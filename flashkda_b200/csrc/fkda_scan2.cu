@@ -90,15 +90,6 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // use count of the X/Y buffers: chunk c >= 1 uses buffer c & 1
 __device__ __forceinline__ uint32_t xy_use(int c) { return (c & 1) ? (c >> 1) : (c >> 1) - 1; }
 
-// x[2i], x[2i+1] *= e.x, e.y as one packed fp32x2 multiply
-__device__ __forceinline__ void mul2(uint32_t& a, uint32_t& b, const float2& e) {
-  unsigned long long x, y, z;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "r"(a), "r"(b));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(y) : "f"(e.x), "f"(e.y));
-  asm("mul.f32x2 %0, %1, %2;" : "=l"(z) : "l"(x), "l"(y));
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(z));
-}
-
 __device__ __forceinline__ void pack32(const uint32_t (&x)[32], uint32_t (&y)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) y[i] = pack_bf16(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
