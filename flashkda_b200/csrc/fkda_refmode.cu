@@ -1,10 +1,11 @@
-// Reference-rounding mode (flag FKDA_FLAG_REFERENCE_ROUNDING): a debugging aid that evaluates the forward pass the
-// way the reference does - tiles of 16 tokens, the state kept in bf16 between tiles, and a bf16 rounding at every
-// point where the reference's kernels round (restated from the reference's own oracle, tests/torch_ref.py:62-247, and
-// its kernels csrc/smxx/fwd_kernel1.cuh:265-508, fwd_kernel2.cuh:533-731) - instead of the chunk-32 / fp32-state form of
-// the production kernels.  With it the results agree with the reference's to the last bit for most elements (the
-// remaining differences come from the order in which the tensor cores add); it is several times slower than the
-// production path and exists so that a disagreement with the reference can be told apart from rounding.
+// Reference-rounding mode (flag FKDA_FLAG_REFERENCE_ROUNDING): the forward pass evaluated the way the reference does
+// - tiles of 16 tokens, the state kept in bf16 between tiles, a bf16 rounding at every point where the reference's
+// kernels round, the same hardware approximations (tanh.approx, ex2.approx, rsqrt.approx) in the same places and the
+// same mma.sync m16n8k16 products in the same k order (restated from the reference's own oracle,
+// tests/torch_ref.py:62-247, and its kernels csrc/smxx/fwd_kernel1.cuh:265-508, fwd_kernel2.cuh:533-731) - instead of
+// the chunk-32 / fp32-state form of the production kernels.  `out` and the final state are then the same bits as
+// those of the reference's CUDA kernels run on the same GPU (tests/test_gpu_reference_bits.py).  It is several times
+// slower than the production path and exists so that a disagreement with the reference can be told apart from rounding.
 //
 // One CTA of 256 threads per (sequence, head) chain walks the tiles; fixed-length batches and varlen alike.
 // Per tile (rows i = 0..15, channel k, G = running sum of the log2 gate):
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(kThreads, 1) refmode_kernel(const Params p) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) pp[i] = nx[i];
         }
-        inv[w] = __fdiv_rn(1.0f, __fsqrt_rn(pp[0] + 1e-6f));
+        inv[w] = rsqrtf(pp[0] + 1e-6f);      // the approximate reciprocal square root, as the reference's kernel takes it
       }
       const bool valid = row < len;
       uint32_t kd[4], qd[4], ki[4], kr[4];
@@ -350,9 +351,12 @@ __global__ void __launch_bounds__(kThreads, 1) refmode_kernel(const Params p) {
         const int tok = g + 8 * hh, vcol = 16 * warp + 8 * m + 2 * t4;
         const uint32_t vw = *reinterpret_cast<const uint32_t*>(smem + kStV + stage_off(tok, vcol >> 3) + (vcol & 7) * 2);
         const float bb = s_beta[16 + tok];
-        const float a0 = rbf(rbf(bf_lo(vw) - rbf(Wa[m][2 * hh])) * bb);
-        const float a1 = rbf(rbf(bf_hi(vw) - rbf(Wa[m][2 * hh + 1])) * bb);
-        Vt[m][hh] = movmatrix_trans(pack_bf16(a0, a1));
+        // bf16 arithmetic, one rounding per operation as the reference's bf16 operators have it (an fp32 difference
+        // rounded afterwards rounds twice where the operands' exponents lie more than sixteen apart)
+        const uint32_t w2 = pack_bf16(Wa[m][2 * hh], Wa[m][2 * hh + 1]);
+        const __nv_bfloat162 d2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&vw), *reinterpret_cast<const __nv_bfloat162*>(&w2));
+        const __nv_bfloat162 a2 = __hmul2(d2, __floats2bfloat162_rn(bb, bb));
+        Vt[m][hh] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&a2));
       }
     // U = bf(INV V')
     uint32_t Ut[2][2];
@@ -377,11 +381,11 @@ __global__ void __launch_bounds__(kThreads, 1) refmode_kernel(const Params p) {
         mma_bf16_16816(mu, a0, a1, a2, a3, Ut[m][0], Ut[m][1]);
         const int vcol = 16 * warp + 8 * m + 2 * t4;
         if (g < len)
-          *reinterpret_cast<uint32_t*>(p.out + (static_cast<size_t>(t0 + g) * p.H + h) * kD + vcol) =
-              pack_bf16(rbf(Oa[m][0]) + rbf(mu[0]), rbf(Oa[m][1]) + rbf(mu[1]));
+          *reinterpret_cast<__nv_bfloat162*>(p.out + (static_cast<size_t>(t0 + g) * p.H + h) * kD + vcol) =
+              __hadd2(__floats2bfloat162_rn(Oa[m][0], Oa[m][1]), __floats2bfloat162_rn(mu[0], mu[1]));
         if (g + 8 < len)
-          *reinterpret_cast<uint32_t*>(p.out + (static_cast<size_t>(t0 + g + 8) * p.H + h) * kD + vcol) =
-              pack_bf16(rbf(Oa[m][2]) + rbf(mu[2]), rbf(Oa[m][3]) + rbf(mu[3]));
+          *reinterpret_cast<__nv_bfloat162*>(p.out + (static_cast<size_t>(t0 + g + 8) * p.H + h) * kD + vcol) =
+              __hadd2(__floats2bfloat162_rn(Oa[m][2], Oa[m][3]), __floats2bfloat162_rn(mu[2], mu[3]));
       }
     }
     // S = bf(fma(S, 2^G15, kr^T U)), tile by tile

@@ -37,10 +37,10 @@ typedef enum fkda_state_dtype { FKDA_STATE_NONE = 0, FKDA_STATE_BF16 = 1, FKDA_S
 #define FKDA_FLAG_SCAN_PLAIN 0x2u /* tcgen05 recurrence without look-ahead (kept for cross-checking) */
 #define FKDA_FLAG_SCAN_LOOKAHEAD 0x4u /* always use the look-ahead recurrence kernel on whole sequences */
 #define FKDA_FLAG_NO_FUSED_SHORT 0x10u /* fixed-length T <= 32: use the two-kernel path instead of the fused short-sequence kernel */
-/* Debugging aid: evaluate fkda_fwd the way the reference does (tiles of 16 tokens, bf16 state between tiles, a bf16
- * rounding wherever the reference's kernels round, csrc/smxx/fwd_kernel1.cuh:265-508, fwd_kernel2.cuh:533-731), so
- * that results can be compared with the reference's almost bit for bit.  One slow kernel, any shape; honoured by
- * fkda_fwd only. */
+/* Bit-exact mode: evaluate fkda_fwd the way the reference does (tiles of 16 tokens, bf16 state between tiles, a bf16
+ * rounding wherever the reference's kernels round and the same hardware approximations in the same places,
+ * csrc/smxx/fwd_kernel1.cuh:265-508, fwd_kernel2.cuh:533-731): `out` and the final state are the same bits as those of
+ * the reference's CUDA kernels on the same GPU.  One slow kernel, any shape; honoured by fkda_fwd only. */
 #define FKDA_FLAG_REFERENCE_ROUNDING 0x20u
 #define FKDA_FLAG_SCAN_NO_SEGMENTS 0x8u /* never cut sequences into runs that are walked in parallel */
 /* Send a fixed-length call of any T to the fused short-sequence kernel, which by default takes T <= 32 only (it is a
