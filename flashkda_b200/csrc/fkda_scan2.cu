@@ -337,6 +337,13 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
           umma_ts(tmem + kColS, ut + 8, bk + 256, idesc_n128_bmn, 1);
           umma_commit(bar(BAR_SFULL));
         }
+        {  // O_c += U_c^T mqk_c^T (O_c's other terms were issued in earlier iterations / by issuer 2): before the products
+           // for W_{c+1}, whose inputs (the products on the decayed state) wait for this output buffer's predecessor to drain
+          const uint64_t bm = umma_desc(rec + kRecMQK, 128, 512);
+          umma_ts(tmem + kColO + 64 * (c & 1), ut, bm, idesc_n32, 1);
+          umma_ts(tmem + kColO + 64 * (c & 1), ut + 8, bm + 16, idesc_n32, 1);
+          umma_commit(bar(BAR_OFULL + (c & 1)));
+        }
         if (more) {
           // [W_{c+1} | O_{c+1}] += U_c^T [X_{c+1}; Y_{c+1}]^T : one N = 64 product per k-step, on top of the
           // products on the decayed state that issuer 2 placed there
@@ -348,12 +355,6 @@ __global__ void __launch_bounds__(kThreads, 1) scan2_kernel(const ScanParams p, 
           umma_ts(tmem + kColWO + 64 * ((c + 1) & 1), ut + 8, bx + 16, idesc_n64, 1);
           umma_commit(bar(BAR_WFULL + ((c + 1) & 1)));
         } else if (!mbar_wait(bar(BAR_AFULL + (c & 1)), (c >> 1) & 1, abort_flag)) { failed = true; break; }
-        {  // O_c += U_c^T mqk_c^T (O_c's other terms were issued in earlier iterations / by issuer 2)
-          const uint64_t bm = umma_desc(rec + kRecMQK, 128, 512);
-          umma_ts(tmem + kColO + 64 * (c & 1), ut, bm, idesc_n32, 1);
-          umma_ts(tmem + kColO + 64 * (c & 1), ut + 8, bm + 16, idesc_n32, 1);
-          umma_commit(bar(BAR_OFULL + (c & 1)));
-        }
         if (more) umma_commit(bar(BAR_XYFREE + ((c + 1) & 1)));
         umma_commit(bar(BAR_EMPTY + c % kStages));
         FKDA_TRACE(0, c, 1);
