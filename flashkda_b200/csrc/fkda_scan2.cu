@@ -12,11 +12,11 @@
 // products of operand records only and are computed ahead of time.  All products are tcgen05.mma
 // with M = 128; U^T and the bf16 copy of Sd are MMA A-operands read from tensor memory.
 //
-// Warp roles (640 threads): 0 = bulk-copy producer; 1, 2, 3 = one MMA-issuing thread each (products on
+// Warp roles (896 threads): 0 = bulk-copy producer; 1, 2, 3 = one MMA-issuing thread each (products on
 // U / on the decayed state / X,Y), ordered among each other through tcgen05.commit + mbarriers;
-// 4-7 = U warps (critical chain); 8-15 = state warps (two groups of four, 64 state columns each; kStateBlocks = 1 makes
-// it sixteen warps of 32 columns: a shorter decay, 1250 against 1580 cycles, at 72 registers, and the same step, which the
-// thread that issues the products on U sets by then); 16-19 = output warps (two of them also turn X, Y into bf16 operands).  Every wait is bounded; a wait that gives up raises an abort flag, records a
+// 4-7 = U warps (critical chain); 8-23 = state warps (four groups of four, 32 state columns each: the decay of a chunk takes
+// them about 1300 cycles; kStateBlocks = 2 makes it eight warps of 64 columns, 1580 cycles, 96 instead of 72 registers,
+// 1 % slower); 24-27 = output warps (two of them also turn X, Y into bf16 operands).  Every wait is bounded; a wait that gives up raises an abort flag, records a
 // status code and lets all roles fall through to the common exit, where TMEM is released.
 #include "fkda_common.cuh"
 
@@ -38,7 +38,7 @@ static unsigned long long* g_trace = nullptr;
 #endif
 
 constexpr int kStages = 5;
-constexpr int kStateBlocks = 2;                         // 32-column blocks of the state per state warp (2: eight warps; 1: sixteen)
+constexpr int kStateBlocks = 1;                         // 32-column blocks of the state per state warp (1: sixteen warps; 2: eight)
 constexpr int kStateWarps = 16 / kStateBlocks;
 constexpr int kOutWarp0 = 8 + kStateWarps;              // first output warp
 constexpr int kThreads = (kOutWarp0 + 4) * 32;
