@@ -1,4 +1,4 @@
-"""Bit-exact mode against the reference's own CUDA kernels (SURVEY f4; reference contract: tests/test_fwd_full.py:90-94,
+"""Bit-exact mode against the reference's own CUDA kernels (reference contract: tests/test_fwd_full.py:90-94,
 tests/test_fwd.py:260-261, `torch.equal` of the kernel's result with its torch restatement on the GPU).
 
 With FKDA_FLAG_REFERENCE_ROUNDING the forward pass uses the reference's 16-token tile, bf16 state between tiles, its
