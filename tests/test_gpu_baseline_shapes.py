@@ -98,6 +98,14 @@ def test_varlen_two_sequences_of_524288_tokens_H1():
     run_and_sample(w, [(1, 0)])
 
 
+def test_tensors_of_more_than_2_to_the_31_elements():
+    """q, k, v, g and out of 2 x 147 456 x 64 x 128 = 2.4 G elements each (4.8 GB): element and byte offsets beyond
+    32 bits in every kernel of the call.  The last chain sits at the highest addresses of all of them."""
+    w = Workload("big", H=64, B=2, T=147456, state_in="fp32", state_out="fp32", seed=45)
+    assert w.B * w.T * w.H * 128 > 2 ** 31
+    run_and_sample(w, [(0, 0), (1, 63)])
+
+
 def _rmse_ratio_case(name):
     """The reference's accuracy sweep (tests/test_fwd.py:45-68, 315-363): T = 8192, H = 1, A_log = 0, q, k, v ~ U(0,1),
     initial state ~ N(0,1) fp32, one of ten gate regimes."""
