@@ -106,6 +106,85 @@ def test_tensors_of_more_than_2_to_the_31_elements():
     run_and_sample(w, [(0, 0), (1, 63)])
 
 
+def _call(x, **over):
+    a = dict(x)
+    a.update(over)
+    out = torch.full_like(a["v"], float("nan"))
+    fin = None if a["final_state"] is None else torch.full_like(a["final_state"], float("nan"))
+    flash_kda.fwd(a["q"], a["k"], a["v"], a["g"], a["beta"], a["scale"], out, a["A_log"], a["dt_bias"], a["lower_bound"],
+                  initial_state=a["initial_state"], final_state=fin, cu_seqlens=a["cu_seqlens"])
+    torch.cuda.synchronize()
+    return out, fin
+
+
+@pytest.mark.parametrize("config", [1, 2, 4])
+def test_full_size_exact_properties(config):
+    """Properties that hold bit for bit at any size, checked on the whole result of the headline configurations
+    (the fp64 recurrence can only follow a few chains of them):
+
+    * `out` and the final state are linear in (v, initial state), and a factor of 4 commutes with every rounding on
+      the way (bf16 and fp32 roundings, tensor-core accumulation): the results must be exactly four times as large;
+    * heads are independent recurrences: with the head axis reversed in every input, the results come out reversed,
+      whichever CTA, SM or kernel of the dispatch walks a chain."""
+    w = baseline_workload(config)
+    x = make_inputs(w, device="cuda")
+    out, fin = _call(x)
+    assert not torch.isnan(out.float()).any() and not torch.isnan(fin.float()).any()
+
+    out4, fin4 = _call(x, v=(x["v"].float() * 4).to(x["v"].dtype), initial_state=x["initial_state"] * 4)
+    assert torch.equal(out4.float(), out.float() * 4)
+    assert torch.equal(fin4.float(), fin.float() * 4)
+    del out4, fin4
+
+    rev = lambda t, dim: t.flip(dim).contiguous()
+    outr, finr = _call(x, q=rev(x["q"], 2), k=rev(x["k"], 2), v=rev(x["v"], 2), g=rev(x["g"], 2), beta=rev(x["beta"], 2),
+                       A_log=rev(x["A_log"], 0), dt_bias=rev(x["dt_bias"], 0), initial_state=rev(x["initial_state"], 1))
+    assert torch.equal(outr.flip(2), out)
+    assert torch.equal(finr.flip(1), fin)
+
+
+def test_full_size_hand_off_and_run_boundaries():
+    """Two more whole-result comparisons at full size.  (1) Configuration 1 computed in two halves of 4096 tokens, the
+    fp32 state of the first handed to the second: same chunk grid and operands, but the recurrence rounds its bf16
+    state copy at other points around the seam (inside a chain the products of a chunk use the copy from two chunks
+    back plus a correction), so the halves agree with the single call closely, not exactly.  (2) One GPU's share of the long-context configuration walked as parallel runs
+    against the same chains walked whole (`FKDA_FLAG_SCAN_NO_SEGMENTS`): the two differ in where the state is rounded
+    (the run maps are chained in split tf32), so they agree closely but not exactly - on every token of every chain,
+    run boundaries included."""
+    w = baseline_workload(1)
+    x = make_inputs(w, device="cuda")
+    out, fin = _call(x)
+    half = w.T // 2
+    first = {k: x[k][:, :half].contiguous() for k in ("q", "k", "v", "g", "beta")}
+    second = {k: x[k][:, half:].contiguous() for k in ("q", "k", "v", "g", "beta")}
+    out_a, mid = _call(x, **first)
+    out_b, fin_b = _call(x, **second, initial_state=mid)
+    assert torch.equal(out_a, out[:, :half])
+    h_out = (out_b.float() - out[:, half:].float()).abs().max().item()
+    h_fin = ((fin_b - fin).norm() / fin.norm()).item()
+    print(f"two halves against one call: out max-abs diff {h_out:.3e}, final-state relative diff {h_fin:.3e}")
+    assert h_out <= 1e-3 and h_fin <= 1e-4
+    del x, out, fin, out_a, out_b, mid, fin_b
+
+    w = baseline_workload(3)
+    x = make_inputs(w, device="cuda", heads=range(8, 16))
+    runs, _ = F.plan_segments(8, w.T // 32)
+    assert runs > 1
+    res = []
+    for flags in (0, F.FLAG_SCAN_NO_SEGMENTS):
+        out = torch.full_like(x["v"], float("nan"))
+        fin = torch.full_like(x["final_state"], float("nan"))
+        ws = torch.empty(F.get_workspace_size(w.T, 8, 1, flags), dtype=torch.uint8, device="cuda")
+        flash_kda.fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["scale"], out, x["A_log"], x["dt_bias"], x["lower_bound"],
+                      initial_state=x["initial_state"], final_state=fin, workspace=ws, flags=flags)
+        assert F.read_status(ws) == 0
+        res.append((out.float(), fin.float()))
+    d_out = (res[0][0] - res[1][0]).abs().max().item()
+    d_fin = ((res[0][1] - res[1][1]).norm() / res[1][1].norm()).item()
+    print(f"runs against whole walk: out max-abs diff {d_out:.3e}, final-state relative diff {d_fin:.3e}")
+    assert d_out <= 1e-3 and d_fin <= 1e-4
+
+
 def _rmse_ratio_case(name):
     """The reference's accuracy sweep (tests/test_fwd.py:45-68, 315-363): T = 8192, H = 1, A_log = 0, q, k, v ~ U(0,1),
     initial state ~ N(0,1) fp32, one of ten gate regimes."""
